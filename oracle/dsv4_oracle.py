@@ -1,0 +1,446 @@
+"""CPU oracle for the DeepSeek-V4 decode-attention path (TEST INFRASTRUCTURE ONLY).
+
+This module restates, in numpy, the arithmetic of the reference project's
+PyTorch decode path.  It is the checker the CUDA kernels are compared with; it
+is never part of the shipped compute path.  Only the tests, the smoke check and
+the CPU-baseline leg of the benchmark may import it.
+
+Parity pin: `tests/golden/*.npz` hold outputs of the reference's own
+`hca_decode_forward` (bench/bench/reference.py:471-546) on the seeded inputs
+that `tests/golden/gen_golden.py` builds; `tests/test_oracle.py` checks every
+function here against them.  Semantics the reference does not define (paged
+pools, block tables, -1 padded index lists, per-128 FP32 scales, the LSE
+output) are pinned only by this restatement and are marked "unpinned by the
+reference" where they appear.
+
+Reference lines each function follows are cited in its docstring as
+`path:line` inside the reference project.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+# ── entry layout (one compressed-KV cache entry) ────────────────────────
+D_LATENT = 512            # FP8 e4m3 latent, also the value width d_v
+D_ROPE = 64               # BF16 RoPE tail
+D_QK = D_LATENT + D_ROPE  # 576
+SCALE_BLOCK = 128         # one FP32 absmax scale per 128 latent elements
+N_SCALES = D_LATENT // SCALE_BLOCK
+SCALE_OFF = D_LATENT                      # byte offset of the 4 FP32 scales
+ROPE_OFF = D_LATENT + 4 * N_SCALES        # byte offset of the 64 BF16 rope values
+ENTRY_BYTES = ROPE_OFF + 2 * D_ROPE       # 656
+PAGE_ENTRIES = 64
+E4M3_MAX = 448.0
+
+
+# ── bf16 / e4m3 scalar formats ──────────────────────────────────────────
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even float32 -> bfloat16 bit pattern (uint16)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = x.view(np.uint32).astype(np.uint64)
+    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    out = rounded.astype(np.uint16)
+    nan = np.isnan(x)
+    if nan.any():
+        out = np.where(nan, np.uint16(0x7FC0), out)
+    return out
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float32 -> nearest bfloat16, returned as float32."""
+    return bf16_bits_to_f32(f32_to_bf16_bits(x))
+
+
+def _build_e4m3_table() -> np.ndarray:
+    t = np.zeros(256, dtype=np.float32)
+    for byte in range(256):
+        s = -1.0 if byte & 0x80 else 1.0
+        e = (byte >> 3) & 0xF
+        m = byte & 0x7
+        if e == 0xF and m == 0x7:
+            v = float("nan")
+        elif e == 0:
+            v = s * (m / 8.0) * 2.0 ** (-6)
+        else:
+            v = s * (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        t[byte] = v
+    return t
+
+
+E4M3_TABLE = _build_e4m3_table()
+# Positive finite e4m3 magnitudes in increasing order (codes 0x00..0x7E).
+_E4M3_POS = E4M3_TABLE[:0x7F].astype(np.float64)
+# Midpoints between neighbours; ties go to the even code.
+_E4M3_MID = (_E4M3_POS[:-1] + _E4M3_POS[1:]) / 2.0
+
+
+def e4m3_to_f32(b: np.ndarray) -> np.ndarray:
+    return E4M3_TABLE[np.ascontiguousarray(b, dtype=np.uint8)]
+
+
+def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
+    """float32 -> e4m3 (fn variant) byte, round-to-nearest-even, saturating at
+    +-448.  Same result as `x.clamp(-448, 448).to(torch.float8_e4m3fn)`, the
+    conversion the reference's quantiser uses (bench/bench/decode.py:110-113)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    mag = np.minimum(np.abs(x.astype(np.float64)), E4M3_MAX)
+    # code = number of midpoints strictly below mag, ties resolved to even
+    code = np.searchsorted(_E4M3_MID, mag, side="left").astype(np.int64)
+    tie = (code < _E4M3_MID.size) & (mag == _E4M3_MID[np.minimum(code, _E4M3_MID.size - 1)])
+    # at a tie `code` is the lower neighbour; go up when the lower one is odd
+    code = np.where(tie & ((code & 1) == 1), code + 1, code)
+    out = code.astype(np.uint8)
+    out = np.where(np.signbit(x), out | 0x80, out).astype(np.uint8)
+    return out
+
+
+# ── quantise / pack / unpack of cache entries ───────────────────────────
+
+def quantize_latent(latent: np.ndarray):
+    """[..., 512] float32 -> (e4m3 bytes [..., 512], FP32 scales [..., 4]).
+
+    Follows the reference quantiser's recipe (bench/bench/decode.py:92-114:
+    per-tile absmax, value/scale clamped to +-448, e4m3 cast) with the tile and
+    scale type this library's cache uses: one FP32 scale = absmax/448 per 128
+    elements instead of a power-of-two byte per 64.  A block of zeros gets
+    scale 1 (unpinned by the reference)."""
+    latent = np.ascontiguousarray(latent, dtype=np.float32)
+    lead = latent.shape[:-1]
+    blk = latent.reshape(*lead, N_SCALES, SCALE_BLOCK)
+    absmax = np.abs(blk).max(axis=-1)
+    scale = (absmax / np.float32(E4M3_MAX)).astype(np.float32)
+    scale = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
+    q = f32_to_e4m3((blk / scale[..., None]).astype(np.float32))
+    return q.reshape(*lead, D_LATENT), scale
+
+
+def pack_entries(latent: np.ndarray, rope: np.ndarray) -> np.ndarray:
+    """float32 latent [..., 512] + rope [..., 64] -> uint8 [..., 656]."""
+    q, scale = quantize_latent(latent)
+    lead = q.shape[:-1]
+    out = np.empty((*lead, ENTRY_BYTES), dtype=np.uint8)
+    out[..., :D_LATENT] = q
+    out[..., SCALE_OFF:ROPE_OFF] = scale.view(np.uint8).reshape(*lead, 4 * N_SCALES)
+    out[..., ROPE_OFF:] = f32_to_bf16_bits(rope).view(np.uint8).reshape(*lead, 2 * D_ROPE)
+    return out
+
+
+def unpack_entries(entries: np.ndarray) -> np.ndarray:
+    """uint8 [..., 656] -> exactly dequantised float32 rows [..., 576].
+
+    Dequantisation is `fp8 value * scale` in float32, the exact dequant the
+    reference applies before its attention math
+    (bench/bench/reference.py:422-442, with this cache's FP32 scale)."""
+    entries = np.ascontiguousarray(entries, dtype=np.uint8)
+    lead = entries.shape[:-1]
+    lat = e4m3_to_f32(entries[..., :D_LATENT]).reshape(*lead, N_SCALES, SCALE_BLOCK)
+    scale = np.ascontiguousarray(entries[..., SCALE_OFF:ROPE_OFF]).view(np.float32)
+    lat = (lat * scale.reshape(*lead, N_SCALES, 1)).reshape(*lead, D_LATENT)
+    rope = bf16_bits_to_f32(np.ascontiguousarray(entries[..., ROPE_OFF:]).view(np.uint16))
+    return np.concatenate([lat, rope.reshape(*lead, D_ROPE)], axis=-1).astype(np.float32)
+
+
+# ── the attention core ─────────────────────────────────────────────────
+
+def attend(q: np.ndarray, kv: np.ndarray, sm_scale: float,
+           sink: Optional[np.ndarray] = None, d_v: int = D_LATENT):
+    """One query token against its (already gathered, dequantised) rows.
+
+    q  [H, d_qk] float32, kv [n, d_qk] float32 (n may be 0).
+    Returns (out [H, d_v] float32 before the final BF16 rounding, lse [H]).
+
+    Follows bench/bench/reference.py:516-545: logits = q.kv^T * sm_scale, a
+    max-subtracted exponential, a denominator that includes exp(sink - max)
+    when a sink is given, and out = attn . kv[:, :d_v].  The LSE (natural log,
+    sink excluded, -inf for an empty row) follows hca/sm100/combine.cu:59-81;
+    an empty row yields a zero output (combine.cu:96-100)."""
+    H = q.shape[0]
+    n = kv.shape[0]
+    if n == 0:
+        return np.zeros((H, d_v), np.float32), np.full((H,), -np.inf, np.float32)
+    logits = (q.astype(np.float32) @ kv.astype(np.float32).T) * np.float32(sm_scale)
+    lmax = logits.max(axis=-1, keepdims=True)
+    e = np.exp(logits - lmax)
+    ssum = e.sum(axis=-1, keepdims=True)
+    denom = ssum.copy()
+    if sink is not None:
+        denom = denom + np.exp(sink.astype(np.float32).reshape(H, 1) - lmax)
+    attn = e / denom
+    out = attn @ kv[:, :d_v].astype(np.float32)
+    lse = (lmax + np.log(ssum)).reshape(H)
+    return out.astype(np.float32), lse.astype(np.float32)
+
+
+def gather_rows(pool: np.ndarray, block_table_row: np.ndarray, idx: np.ndarray) -> np.ndarray:
+    """Select cache entries by logical index through one request's block table.
+
+    pool [num_pages, 64, 656] uint8; idx int (all >= 0).  Mirrors the gather
+    step of the reference's sparse layer (bench/bench/reference.py:576-580),
+    applied to a paged pool (paging is unpinned by the reference)."""
+    idx = np.asarray(idx, dtype=np.int64)
+    pages = np.asarray(block_table_row, dtype=np.int64)[idx // PAGE_ENTRIES]
+    return pool[pages, idx % PAGE_ENTRIES]
+
+
+def csa_sparse_decode(q, pool, block_table, indices, sm_scale, kv_len=None, sink=None):
+    """CSA sparse decode.
+
+    q [B, s_q, H, 576] float32 (BF16-representable), pool [P, 64, 656] uint8,
+    block_table [B, max_pages] int32, indices [B, s_q, topk] int32 with -1 =
+    padding, kv_len optional [B, s_q] int32: entries with index >= kv_len are
+    not visible to that query token (the causal rule of
+    bench/bench/reference.py:197-201 for speculative tokens).
+    Returns (out uint16 bf16 bits [B, s_q, H, 512], lse float32 [B, s_q, H])."""
+    B, s_q, H, _ = q.shape
+    out = np.zeros((B, s_q, H, D_LATENT), np.uint16)
+    lse = np.zeros((B, s_q, H), np.float32)
+    for b in range(B):
+        for j in range(s_q):
+            idx = np.asarray(indices[b, j], dtype=np.int64)
+            ok = idx >= 0
+            if kv_len is not None:
+                ok &= idx < int(kv_len[b, j])
+            rows = gather_rows(pool, block_table[b], idx[ok])
+            o, l = attend(q[b, j], unpack_entries(rows), sm_scale, sink)
+            out[b, j] = f32_to_bf16_bits(o)
+            lse[b, j] = l
+    return out, lse
+
+
+def hca_dense_decode(q, pool, block_table, kv_len, win, win_len, sm_scale, sink=None):
+    """HCA dense decode: every compressed entry [0, kv_len) of a request plus
+    its sliding window, in one softmax.
+
+    q [B, s_q, H, 576]; pool/block_table as above; kv_len, win_len int32
+    [B, s_q] (per query token, so speculative tokens can see different
+    lengths); win [B, W, 656] uint8.  The concatenation order (compressed
+    entries, then window) follows bench/bench/reference.py:512-514."""
+    B, s_q, H, _ = q.shape
+    out = np.zeros((B, s_q, H, D_LATENT), np.uint16)
+    lse = np.zeros((B, s_q, H), np.float32)
+    for b in range(B):
+        for j in range(s_q):
+            n = int(kv_len[b, j])
+            w = int(win_len[b, j])
+            rows = gather_rows(pool, block_table[b], np.arange(n))
+            rows = np.concatenate([rows, win[b, :w]], axis=0)
+            o, l = attend(q[b, j], unpack_entries(rows), sm_scale, sink)
+            out[b, j] = f32_to_bf16_bits(o)
+            lse[b, j] = l
+    return out, lse
+
+
+# ── split-KV merge ─────────────────────────────────────────────────────
+
+def combine(partial_o, partial_lse2, sink=None):
+    """LSE-weighted merge of split partials.
+
+    partial_o [S, N, H, D] float32 (each split's output already divided by its
+    own denominator), partial_lse2 [S, N, H] float32 in log2 units, -inf for an
+    empty split.  Follows hca/sm100/combine.cu:59-101: lse = log2 sum 2^lse_i;
+    with a sink (natural-log units) the denominator becomes
+    lse + log2(1 + 2^(sink*log2e - lse)); out = sum 2^(lse_i - denom) * o_i;
+    returned LSE is natural log without the sink, -inf for an empty row, whose
+    output is zero.  Returns (out bf16 bits [N, H, D], lse [N, H])."""
+    po = np.asarray(partial_o, np.float32)
+    pl = np.asarray(partial_lse2, np.float64)
+    mx = pl.max(axis=0)
+    safe = np.where(np.isfinite(mx), mx, 0.0)
+    ssum = np.exp2(pl - safe).sum(axis=0)
+    has = ssum > 0
+    with np.errstate(divide="ignore"):
+        glse = np.where(has, np.log2(np.where(has, ssum, 1.0)) + safe, -np.inf)
+    denom = glse.copy()
+    if sink is not None:
+        s2 = np.asarray(sink, np.float64).reshape(1, -1) * math.log2(math.e)
+        s2 = np.broadcast_to(s2, glse.shape)
+        denom = np.where(has, glse + np.log2(1.0 + np.exp2(s2 - np.where(has, glse, 0.0))), s2)
+    w = np.where(np.isfinite(pl) & np.isfinite(denom)[None], np.exp2(pl - np.where(np.isfinite(denom), denom, 0.0)[None]), 0.0)
+    out = (w[..., None] * po.astype(np.float64)).sum(axis=0)
+    lse = np.where(has, glse * math.log(2.0), -np.inf).astype(np.float32)
+    return f32_to_bf16_bits(out.astype(np.float32)), lse
+
+
+# ── the reference's own cache layout (448 e4m3 + 7 UE8M0 + 64 bf16) ─────
+
+def quantize_ue8m0(x: np.ndarray, tile: int = 64):
+    """[..., c] float32 (BF16-representable) -> (e4m3 bytes [..., c], UE8M0
+    bytes [..., c/tile]).  Restates bench/bench/decode.py:92-114 line by line:
+    scale = next power of two >= absmax/448, stored as its biased exponent."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    lead, c = x.shape[:-1], x.shape[-1]
+    nb = c // tile
+    blk = x.reshape(*lead, nb, tile)
+    ratio = (np.abs(blk).max(axis=-1) / np.float32(448.0)).astype(np.float32)
+    bits = ratio.view(np.int32)
+    e = (bits >> 23) & 0xFF
+    bump = ((bits & 0x7FFFFF) != 0).astype(np.int32)
+    e_byte = np.clip(e + bump, 0, 254).astype(np.uint8)
+    deq = (e_byte.astype(np.int32) << 23).view(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        scaled = blk / deq[..., None]
+    scaled = np.nan_to_num(scaled, nan=0.0, posinf=448.0, neginf=-448.0)
+    return f32_to_e4m3(scaled.astype(np.float32)).reshape(*lead, c), e_byte
+
+
+def dequant_ue8m0(q: np.ndarray, e_byte: np.ndarray, tile: int = 64) -> np.ndarray:
+    """e4m3 bytes + UE8M0 bytes -> float32; bench/bench/reference.py:422-442
+    (the BF16 multiply there is exact because the scale is a power of two, as
+    long as the product stays in BF16's normal range)."""
+    lead, c = q.shape[:-1], q.shape[-1]
+    nb = c // tile
+    deq = (e_byte.astype(np.int32) << 23).view(np.float32)
+    v = e4m3_to_f32(q).reshape(*lead, nb, tile) * deq.reshape(*lead, nb, 1)
+    return bf16_round(v.reshape(*lead, c).astype(np.float32))
+
+
+def hca_decode_ref_layout(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink, sm_scale):
+    """The reference's decode step in its own cache layout, K exactly
+    dequantised ("fp8_dequant" mode of bench/bench/reference.py:471-546).
+
+    Q [B, H, c+r] float32; Kc [B, M, c] e4m3 bytes, Kc_s [B, M, c/64] UE8M0,
+    Kc_rope [B, M, r] float32 (BF16-representable); Kswa* the same with W rows;
+    sink [H] float32 or None.  V is the full c+r wide row
+    (reference.py:543-545).  Returns (out bf16 bits [B, H, c+r], lse [B, H])."""
+    B, H, dq = Q.shape
+    out = np.zeros((B, H, dq), np.uint16)
+    lse = np.zeros((B, H), np.float32)
+    for b in range(B):
+        kc = np.concatenate([dequant_ue8m0(Kc[b], Kc_s[b]), Kc_rope[b]], axis=-1)
+        ks = np.concatenate([dequant_ue8m0(Kswa[b], Kswa_s[b]), Kswa_rope[b]], axis=-1)
+        kv = np.concatenate([kc, ks], axis=0)
+        o, l = attend(Q[b], kv, sm_scale, sink, d_v=dq)
+        out[b] = f32_to_bf16_bits(o)
+        lse[b] = l
+    return out, lse
+
+
+# ── seeded synthetic inputs (shared by tests, smoke and the CPU baseline) ──
+
+@dataclass
+class CsaCase:
+    q: np.ndarray            # [B, s_q, H, 576] float32, BF16-representable
+    pool: np.ndarray         # [P, 64, 656] uint8
+    block_table: np.ndarray  # [B, max_pages] int32
+    indices: np.ndarray      # [B, s_q, topk] int32
+    kv_len: np.ndarray       # [B, s_q] int32
+    sm_scale: float
+
+
+def make_csa_case(seed, B, s_q, H, n_entries, topk, ragged=False) -> CsaCase:
+    """Draw order (numpy PCG64, fixed): q, latent, rope, page permutation, then
+    per (request, token) a permutation of the visible entries.
+
+    n_entries may be an int or a length-B sequence.  With ragged=True a query
+    token whose visible context is shorter than topk gets -1 padding."""
+    rng = np.random.default_rng(seed)
+    n_ent = np.broadcast_to(np.asarray(n_entries, dtype=np.int64), (B,)).copy()
+    pages_per = (n_ent + PAGE_ENTRIES - 1) // PAGE_ENTRIES
+    max_pages = int(pages_per.max())
+    P = int(pages_per.sum())
+    q = bf16_round(rng.standard_normal((B, s_q, H, D_QK), dtype=np.float32))
+    latent = rng.standard_normal((P, PAGE_ENTRIES, D_LATENT), dtype=np.float32)
+    rope = rng.standard_normal((P, PAGE_ENTRIES, D_ROPE), dtype=np.float32)
+    pool = pack_entries(latent, rope)
+    perm = rng.permutation(P).astype(np.int32)
+    bt = np.zeros((B, max_pages), np.int32)
+    off = 0
+    for b in range(B):
+        bt[b, :pages_per[b]] = perm[off:off + pages_per[b]]
+        off += pages_per[b]
+    indices = np.full((B, s_q, topk), -1, np.int32)
+    kv_len = np.zeros((B, s_q), np.int32)
+    for b in range(B):
+        for j in range(s_q):
+            vis = int(n_ent[b]) - (s_q - 1 - j)   # later tokens see one entry more
+            vis = max(vis, 0)
+            kv_len[b, j] = vis
+            k = min(topk, vis)
+            assert ragged or k == topk, "context shorter than topk needs ragged=True"
+            indices[b, j, :k] = rng.permutation(vis)[:k].astype(np.int32)
+    return CsaCase(q, pool, bt, indices, kv_len, 1.0 / math.sqrt(D_QK))
+
+
+@dataclass
+class HcaCase:
+    q: np.ndarray
+    pool: np.ndarray
+    block_table: np.ndarray
+    kv_len: np.ndarray       # [B, s_q]
+    win: np.ndarray          # [B, W, 656]
+    win_len: np.ndarray      # [B, s_q]
+    sink: Optional[np.ndarray]
+    sm_scale: float
+
+
+def make_hca_case(seed, B, s_q, H, kv_len, win_len, W=128, with_sink=False) -> HcaCase:
+    """Draw order: q, latent, rope, window latent, window rope, page
+    permutation, sink.  kv_len / win_len: int or length-B sequences; query
+    token j of s_q sees `win_len - (s_q-1-j)` window rows."""
+    rng = np.random.default_rng(seed)
+    kvl = np.broadcast_to(np.asarray(kv_len, dtype=np.int64), (B,)).copy()
+    wl = np.broadcast_to(np.asarray(win_len, dtype=np.int64), (B,)).copy()
+    pages_per = np.maximum((kvl + PAGE_ENTRIES - 1) // PAGE_ENTRIES, 1)
+    max_pages = int(pages_per.max())
+    P = int(pages_per.sum())
+    q = bf16_round(rng.standard_normal((B, s_q, H, D_QK), dtype=np.float32))
+    pool = pack_entries(rng.standard_normal((P, PAGE_ENTRIES, D_LATENT), dtype=np.float32),
+                        rng.standard_normal((P, PAGE_ENTRIES, D_ROPE), dtype=np.float32))
+    win = pack_entries(rng.standard_normal((B, W, D_LATENT), dtype=np.float32),
+                       rng.standard_normal((B, W, D_ROPE), dtype=np.float32))
+    perm = rng.permutation(P).astype(np.int32)
+    bt = np.zeros((B, max_pages), np.int32)
+    off = 0
+    for b in range(B):
+        bt[b, :pages_per[b]] = perm[off:off + pages_per[b]]
+        off += pages_per[b]
+    sink = (rng.standard_normal(H).astype(np.float32) * np.float32(0.5)) if with_sink else None
+    kv2 = np.repeat(kvl[:, None], s_q, axis=1).astype(np.int32)
+    w2 = np.zeros((B, s_q), np.int32)
+    for j in range(s_q):
+        w2[:, j] = np.maximum(wl - (s_q - 1 - j), 0)
+    return HcaCase(q, pool, bt, kv2, win, w2, sink, 1.0 / math.sqrt(D_QK))
+
+
+@dataclass
+class RefLayoutCase:
+    Q: np.ndarray
+    Kc: np.ndarray
+    Kc_s: np.ndarray
+    Kc_rope: np.ndarray
+    Kswa: np.ndarray
+    Kswa_s: np.ndarray
+    Kswa_rope: np.ndarray
+    sink: np.ndarray
+    sm_scale: float
+
+
+def make_ref_layout_case(seed, B, H, M_cur, swa_len, c=448, r=64) -> RefLayoutCase:
+    """Inputs in the reference harness's distribution (bench/bench/decode.py:
+    164-188: N(0, 0.5^2) rounded to BF16, sink N(0, 0.1^2), sm_scale =
+    1/sqrt(c+r)); RoPE rotation is omitted because the kernel boundary takes
+    already-rotated tensors and a rotation does not change the distribution."""
+    rng = np.random.default_rng(seed)
+
+    def rn(*shape):
+        return bf16_round(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.5))
+
+    Q = rn(B, H, c + r)
+    kc = rn(B, M_cur, c)
+    ks = rn(B, swa_len, c)
+    Kc_rope = rn(B, M_cur, r)
+    Kswa_rope = rn(B, swa_len, r)
+    sink = (rng.standard_normal(H).astype(np.float32) * np.float32(0.1))
+    Kc, Kc_s = quantize_ue8m0(kc)
+    Kswa, Kswa_s = quantize_ue8m0(ks)
+    return RefLayoutCase(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink, 1.0 / math.sqrt(c + r))

@@ -1,0 +1,156 @@
+"""Generate the golden fixtures in this directory from the reference project.
+
+Run where the reference checkout is available:
+
+    python tests/golden/gen_golden.py --reference /path/to/reference
+
+It imports the reference's PyTorch decode path (`bench.reference`), feeds it
+the seeded inputs built by `oracle/dsv4_oracle.py`, and stores the reference's
+OUTPUTS (plus a hash of the inputs) as small `.npz` files.  The tests rebuild
+the inputs from the same seeds, so the fixtures stay small and the reference
+checkout is not needed to run the tests.
+
+What each fixture pins:
+  csa_cfg0 / csa_ragged / hca_small: gather (reference.py:576-580, torch.gather
+      on the un-paged, exactly dequantised pool) followed by
+      hca_decode_forward(dtype="fp32") (reference.py:471-546), first 512 output
+      columns.
+  ref_layout: hca_decode_forward(dtype="fp8_dequant") and dtype="fp8" on the
+      reference's own 448+7+64 cache layout.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+
+from oracle import dsv4_oracle as orc  # noqa: E402
+
+
+def sha(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def bf16_bits(t):
+    import torch
+    return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+def ref_attend(ref, q, rows, sm_scale, sink):
+    """q [H,576] f32, rows [n,576] f32 -> reference output bits [H,512]."""
+    import torch
+    H = q.shape[0]
+    Q = torch.from_numpy(q).to(torch.bfloat16).unsqueeze(0)
+    kv = torch.from_numpy(rows).unsqueeze(0)
+    empty = torch.zeros(1, 0, orc.D_LATENT)
+    empty_r = torch.zeros(1, 0, orc.D_ROPE)
+    s = torch.full((H,), float("-inf")) if sink is None else torch.from_numpy(sink)
+    inp = ref.HCADecodeInputs(
+        Q=Q, Kc=kv[..., :orc.D_LATENT].contiguous(), Kc_rope=kv[..., orc.D_LATENT:].contiguous(),
+        Kc_scales=None, Kswa=empty, Kswa_rope=empty_r, Kswa_scales=None,
+        sink_logits=s, sm_scale=sm_scale)
+    o = ref.hca_decode_forward(inp, dtype="fp32")
+    return bf16_bits(o[0, :, :orc.D_LATENT])
+
+
+def gen_csa(ref, name, **kw):
+    import torch
+    case = orc.make_csa_case(**kw)
+    B, s_q, H, _ = case.q.shape
+    out = np.zeros((B, s_q, H, orc.D_LATENT), np.uint16)
+    for b in range(B):
+        # un-page this request's cache, as the reference has no paging
+        n_pages = case.block_table.shape[1]
+        flat = case.pool[case.block_table[b]].reshape(n_pages * orc.PAGE_ENTRIES, orc.ENTRY_BYTES)
+        deq = torch.from_numpy(orc.unpack_entries(flat))
+        for j in range(s_q):
+            idx = case.indices[b, j]
+            ok = (idx >= 0) & (idx < case.kv_len[b, j])
+            sel = torch.from_numpy(idx[ok].astype(np.int64))
+            # the reference's gather step (reference.py:576-580)
+            rows = torch.gather(deq, 0, sel.unsqueeze(-1).expand(-1, deq.shape[-1]))
+            out[b, j] = ref_attend(ref, case.q[b, j], rows.numpy(), case.sm_scale, None)
+    np.savez_compressed(HERE / f"{name}.npz", out=out,
+                        inputs_sha=sha(case.q, case.pool, case.block_table, case.indices),
+                        kwargs=repr(kw))
+    print(name, out.shape)
+
+
+def gen_hca(ref, name, **kw):
+    case = orc.make_hca_case(**kw)
+    B, s_q, H, _ = case.q.shape
+    out = np.zeros((B, s_q, H, orc.D_LATENT), np.uint16)
+    for b in range(B):
+        for j in range(s_q):
+            n, w = int(case.kv_len[b, j]), int(case.win_len[b, j])
+            rows = orc.gather_rows(case.pool, case.block_table[b], np.arange(n))
+            rows = np.concatenate([rows, case.win[b, :w]], axis=0)
+            out[b, j] = ref_attend(ref, case.q[b, j], orc.unpack_entries(rows), case.sm_scale, case.sink)
+    np.savez_compressed(HERE / f"{name}.npz", out=out,
+                        inputs_sha=sha(case.q, case.pool, case.block_table, case.win),
+                        kwargs=repr(kw))
+    print(name, out.shape)
+
+
+def gen_ref_layout(ref, name, **kw):
+    import torch
+    c = orc.make_ref_layout_case(**kw)
+    t = lambda a, dt=None: torch.from_numpy(np.ascontiguousarray(a)) if dt is None else torch.from_numpy(np.ascontiguousarray(a)).to(dt)
+    inp = ref.HCADecodeInputs(
+        Q=t(c.Q, torch.bfloat16),
+        Kc=t(c.Kc).view(torch.float8_e4m3fn), Kc_rope=t(c.Kc_rope, torch.bfloat16), Kc_scales=t(c.Kc_s),
+        Kswa=t(c.Kswa).view(torch.float8_e4m3fn), Kswa_rope=t(c.Kswa_rope, torch.bfloat16), Kswa_scales=t(c.Kswa_s),
+        sink_logits=t(c.sink), sm_scale=c.sm_scale)
+    o_deq = bf16_bits(ref.hca_decode_forward(inp, dtype="fp8_dequant"))
+    o_fp8 = bf16_bits(ref.hca_decode_forward(inp, dtype="fp8"))
+    np.savez_compressed(HERE / f"{name}.npz", out_fp8_dequant=o_deq, out_fp8=o_fp8,
+                        inputs_sha=sha(c.Q, c.Kc, c.Kc_s, c.Kc_rope, c.Kswa, c.Kswa_s, c.Kswa_rope, c.sink),
+                        kwargs=repr(kw))
+    print(name, o_deq.shape)
+
+
+# The cases; tests/test_oracle.py rebuilds the inputs from the same kwargs.
+CSA_CASES = {
+    "csa_cfg0": dict(seed=0, B=2, s_q=1, H=16, n_entries=1024, topk=256),
+    "csa_ragged": dict(seed=1, B=3, s_q=2, H=16, n_entries=[100, 300, 37], topk=128, ragged=True),
+}
+HCA_CASES = {
+    "hca_small": dict(seed=2, B=2, s_q=1, H=16, kv_len=[150, 70], win_len=[128, 5], with_sink=True),
+    "hca_nosink": dict(seed=3, B=2, s_q=2, H=8, kv_len=[64, 1], win_len=[2, 128]),
+}
+REF_CASES = {
+    "ref_layout": dict(seed=4, B=1, H=128, M_cur=192, swa_len=64),
+    "ref_layout_ragged": dict(seed=5, B=2, H=32, M_cur=77, swa_len=19),
+}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default=os.environ.get("DSV4_REFERENCE", "/root/reference"))
+    args = ap.parse_args()
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, str(Path(args.reference) / "bench"))
+    from bench import reference as ref  # the reference's own module
+
+    for name, kw in CSA_CASES.items():
+        gen_csa(ref, name, **kw)
+    for name, kw in HCA_CASES.items():
+        gen_hca(ref, name, **kw)
+    for name, kw in REF_CASES.items():
+        gen_ref_layout(ref, name, **kw)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
