@@ -1,0 +1,86 @@
+"""ctypes binding of libdsv4_attn.so (the C ABI declared in include/dsv4_attn.h).
+
+The library is the only compute path: if the shared object is missing the
+import of this module raises, there is no fallback."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+
+
+class LibraryNotBuilt(ImportError):
+    pass
+
+
+def library_path() -> Path:
+    explicit = os.environ.get("DSV4_ATTN_SO")
+    return Path(explicit) if explicit else _HERE / "libdsv4_attn.so"
+
+
+class CsaSparseDecodeParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("s_q", C.c_int32), ("H", C.c_int32), ("topk", C.c_int32),
+        ("max_pages", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float),
+        ("reserved0", C.c_int32), ("num_pages", C.c_int64),
+        ("q", C.c_void_p), ("kv_pool", C.c_void_p), ("block_table", C.c_void_p),
+        ("indices", C.c_void_p), ("kv_len", C.c_void_p), ("attn_sink", C.c_void_p),
+        ("out", C.c_void_p), ("lse", C.c_void_p), ("partial_o", C.c_void_p),
+        ("partial_lse", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
+class HcaDenseDecodeParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("s_q", C.c_int32), ("H", C.c_int32), ("max_pages", C.c_int32),
+        ("win_cap", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float),
+        ("reserved0", C.c_int32), ("num_pages", C.c_int64),
+        ("q", C.c_void_p), ("kv_pool", C.c_void_p), ("block_table", C.c_void_p),
+        ("kv_len", C.c_void_p), ("win_pool", C.c_void_p), ("win_len", C.c_void_p),
+        ("attn_sink", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
+class CombineParams(C.Structure):
+    _fields_ = [
+        ("N", C.c_int32), ("H", C.c_int32), ("D", C.c_int32), ("num_splits", C.c_int32),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("attn_sink", C.c_void_p),
+        ("stride_po_split", C.c_int64), ("stride_po_n", C.c_int64), ("stride_po_h", C.c_int64),
+        ("stride_pl_split", C.c_int64), ("stride_pl_n", C.c_int64),
+        ("stride_out_n", C.c_int64), ("stride_out_h", C.c_int64), ("stride_lse_n", C.c_int64),
+    ]
+
+
+def _load() -> C.CDLL:
+    path = library_path()
+    if not path.exists():
+        raise LibraryNotBuilt(
+            f"{path} not found: build it with `python -m dsv4_attn_b200.build` "
+            "(needs nvcc; the library has no CPU or PyTorch fallback)")
+    lib = C.CDLL(str(path))
+    P = C.POINTER
+    lib.dsv4_attn_version.restype = C.c_int
+    lib.dsv4_attn_version.argtypes = []
+    for name, st in (("dsv4_csa_sparse_decode_fwd", CsaSparseDecodeParams),
+                     ("dsv4_csa_sparse_decode_simt", CsaSparseDecodeParams),
+                     ("dsv4_hca_dense_decode_fwd", HcaDenseDecodeParams),
+                     ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
+                     ("dsv4_attn_combine", CombineParams)):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [P(st), C.c_void_p]
+    lib.dsv4_attn_plan_splits.restype = C.c_int
+    lib.dsv4_attn_plan_splits.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.dsv4_attn_workspace_bytes.restype = C.c_int64
+    lib.dsv4_attn_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, P(C.c_int64)]
+    # same argument list as the reference binding (bench/bench/candidates/hca_custom_decode.py:60-73)
+    lib.hca_decode_fwd.restype = C.c_int
+    lib.hca_decode_fwd.argtypes = [C.c_void_p] * 11 + [C.c_float] + [C.c_int] * 6 + [C.c_void_p]
+    return lib
+
+
+LIB = _load()

@@ -1,0 +1,215 @@
+"""Host-side operator surface: torch tensors in, torch tensors out.
+
+Each function follows the pattern of the reference's operator boundary
+(csa/interface.h:21-85): check device / dtype / rank / contiguity / shape, fill
+a plain parameter struct with raw device pointers, launch on the current
+CUDA stream, return tensors the callee allocated (unless the caller passes
+them).  The arithmetic is done by libdsv4_attn.so only; nothing here computes
+on the host and nothing falls back to PyTorch ops."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .layout import D_QK, D_LATENT, ENTRY_BYTES, PAGE_ENTRIES
+
+MAX_SPLITS = 64
+
+
+class Dsv4Error(RuntimeError):
+    """A library call returned a non-zero cudaError_t."""
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _cuda_contig(t: torch.Tensor, name: str, dtype, ndim: Optional[int] = None) -> None:
+    _check(isinstance(t, torch.Tensor), f"{name} must be a tensor")
+    _check(t.is_cuda, f"{name} must be on cuda")
+    _check(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+    _check(t.is_contiguous(), f"{name} must be contiguous")
+    if ndim is not None:
+        _check(t.dim() == ndim, f"{name} must have {ndim} dims, got {t.dim()}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise Dsv4Error(f"{what} failed: cudaError={rc}")
+
+
+def plan_splits(rows: int, H: int, max_len: int, num_sms: int = 0) -> int:
+    """Split count the library's cost model picks (host arithmetic only)."""
+    s = _lib.LIB.dsv4_attn_plan_splits(int(rows), int(H), int(max_len), int(num_sms))
+    if s < 1:
+        raise Dsv4Error(f"dsv4_attn_plan_splits failed: cudaError={-s}")
+    return s
+
+
+def alloc_workspace(rows: int, H: int, num_splits: int, device) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """(partial_o [S, rows, H, 512] f32, partial_lse [S, rows, H] f32) or (None, None)."""
+    if num_splits <= 1:
+        return None, None
+    po = torch.empty(num_splits, rows, H, D_LATENT, dtype=torch.float32, device=device)
+    pl = torch.empty(num_splits, rows, H, dtype=torch.float32, device=device)
+    return po, pl
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace, max_len):
+    _cuda_contig(q, "q", torch.bfloat16, 4)
+    B, s_q, H, dq = q.shape
+    _check(dq == D_QK, f"q last dim must be {D_QK}")
+    _cuda_contig(kv_pool, "kv_pool", torch.uint8, 3)
+    _check(kv_pool.shape[1] == PAGE_ENTRIES and kv_pool.shape[2] == ENTRY_BYTES,
+           f"kv_pool must be [num_pages, {PAGE_ENTRIES}, {ENTRY_BYTES}]")
+    _cuda_contig(block_table, "block_table", torch.int32, 2)
+    _check(block_table.shape[0] == B, "block_table must be [B, max_pages]")
+    if attn_sink is not None:
+        _cuda_contig(attn_sink, "attn_sink", torch.float32, 1)
+        _check(attn_sink.shape[0] == H, "attn_sink must be [H]")
+    rows = B * s_q
+    if num_splits is None:
+        num_splits = plan_splits(rows, H, max_len)
+    _check(1 <= num_splits <= MAX_SPLITS, f"num_splits must be in [1, {MAX_SPLITS}]")
+    if out is None:
+        out = torch.empty(B, s_q, H, D_LATENT, dtype=torch.bfloat16, device=q.device)
+    else:
+        _cuda_contig(out, "out", torch.bfloat16, 4)
+        _check(tuple(out.shape) == (B, s_q, H, D_LATENT), "out must be [B, s_q, H, 512]")
+    if lse is None:
+        lse = torch.empty(B, s_q, H, dtype=torch.float32, device=q.device)
+    else:
+        _cuda_contig(lse, "lse", torch.float32, 3)
+        _check(tuple(lse.shape) == (B, s_q, H), "lse must be [B, s_q, H]")
+    po = pl = None
+    if num_splits > 1:
+        if workspace is None:
+            po, pl = alloc_workspace(rows, H, num_splits, q.device)
+        else:
+            po, pl = workspace
+            _cuda_contig(po, "partial_o", torch.float32)
+            _cuda_contig(pl, "partial_lse", torch.float32)
+            _check(po.numel() >= num_splits * rows * H * D_LATENT and pl.numel() >= num_splits * rows * H,
+                   "workspace too small for num_splits")
+    return B, s_q, H, num_splits, out, lse, po, pl
+
+
+def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None, attn_sink=None,
+                      num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma"):
+    """CSA sparse decode.  q bf16 [B, s_q, H, 576]; kv_pool uint8 [P, 64, 656];
+    block_table int32 [B, max_pages]; indices int32 [B, s_q, topk] (-1 = pad);
+    kv_len optional int32 [B, s_q].  Returns (out bf16 [B, s_q, H, 512],
+    lse f32 [B, s_q, H])."""
+    _cuda_contig(indices, "indices", torch.int32, 3)
+    topk = indices.shape[-1]
+    if impl == "simt":
+        num_splits = 1
+    B, s_q, H, num_splits, out, lse, po, pl = _common(q, kv_pool, block_table, attn_sink, out, lse,
+                                                      num_splits, workspace, topk)
+    _check(tuple(indices.shape[:2]) == (B, s_q), "indices must be [B, s_q, topk]")
+    if kv_len is not None:
+        _cuda_contig(kv_len, "kv_len", torch.int32, 2)
+        _check(tuple(kv_len.shape) == (B, s_q), "kv_len must be [B, s_q]")
+    p = _lib.CsaSparseDecodeParams(
+        B=B, s_q=s_q, H=H, topk=topk, max_pages=block_table.shape[1], num_splits=num_splits,
+        sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
+        q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), indices=_ptr(indices),
+        kv_len=_ptr(kv_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
+        partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
+    fn = _lib.LIB.dsv4_csa_sparse_decode_fwd if impl == "mma" else _lib.LIB.dsv4_csa_sparse_decode_simt
+    _rc(fn(C.byref(p), _stream(q.device)), "dsv4_csa_sparse_decode")
+    return out, lse
+
+
+def hca_dense_decode(q, kv_pool, block_table, kv_len, win_pool, win_len, sm_scale, *, attn_sink=None,
+                     num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma",
+                     max_len=None):
+    """HCA dense decode.  kv_len / win_len int32 [B, s_q]; win_pool uint8
+    [B, W, 656].  `max_len` (longest kv_len + win_len) only steers the split
+    planner; when omitted the block-table capacity is used so that no device
+    read-back is needed."""
+    _cuda_contig(kv_len, "kv_len", torch.int32, 2)
+    _cuda_contig(win_len, "win_len", torch.int32, 2)
+    _cuda_contig(win_pool, "win_pool", torch.uint8, 3)
+    _check(win_pool.shape[2] == ENTRY_BYTES, "win_pool must be [B, W, 656]")
+    W = win_pool.shape[1]
+    if max_len is None:
+        max_len = block_table.shape[1] * PAGE_ENTRIES + W
+    if impl == "simt":
+        num_splits = 1
+    B, s_q, H, num_splits, out, lse, po, pl = _common(q, kv_pool, block_table, attn_sink, out, lse,
+                                                      num_splits, workspace, max_len)
+    _check(tuple(kv_len.shape) == (B, s_q) and tuple(win_len.shape) == (B, s_q), "kv_len/win_len must be [B, s_q]")
+    _check(win_pool.shape[0] == B, "win_pool must be [B, W, 656]")
+    p = _lib.HcaDenseDecodeParams(
+        B=B, s_q=s_q, H=H, max_pages=block_table.shape[1], win_cap=W, num_splits=num_splits,
+        sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
+        q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), kv_len=_ptr(kv_len),
+        win_pool=_ptr(win_pool), win_len=_ptr(win_len), attn_sink=_ptr(attn_sink),
+        out=_ptr(out), lse=_ptr(lse), partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
+    fn = _lib.LIB.dsv4_hca_dense_decode_fwd if impl == "mma" else _lib.LIB.dsv4_hca_dense_decode_simt
+    _rc(fn(C.byref(p), _stream(q.device)), "dsv4_hca_dense_decode")
+    return out, lse
+
+
+def combine(partial_o, partial_lse, *, attn_sink=None, out=None, lse=None):
+    """Merge split partials: partial_o f32 [S, N, H, 512], partial_lse f32
+    [S, N, H] (log2).  Returns (out bf16 [N, H, 512], lse f32 [N, H])."""
+    _cuda_contig(partial_o, "partial_o", torch.float32, 4)
+    _cuda_contig(partial_lse, "partial_lse", torch.float32, 3)
+    S, N, H, D = partial_o.shape
+    _check(D == D_LATENT, "partial_o last dim must be 512")
+    _check(tuple(partial_lse.shape) == (S, N, H), "partial_lse must be [S, N, H]")
+    if attn_sink is not None:
+        _cuda_contig(attn_sink, "attn_sink", torch.float32, 1)
+    if out is None:
+        out = torch.empty(N, H, D, dtype=torch.bfloat16, device=partial_o.device)
+    if lse is None:
+        lse = torch.empty(N, H, dtype=torch.float32, device=partial_o.device)
+    p = _lib.CombineParams(
+        N=N, H=H, D=D, num_splits=S, partial_o=_ptr(partial_o), partial_lse=_ptr(partial_lse),
+        out=_ptr(out), lse=_ptr(lse), attn_sink=_ptr(attn_sink),
+        stride_po_split=N * H * D, stride_po_n=H * D, stride_po_h=D,
+        stride_pl_split=N * H, stride_pl_n=H, stride_out_n=H * D, stride_out_h=D, stride_lse_n=H)
+    _rc(_lib.LIB.dsv4_attn_combine(C.byref(p), _stream(partial_o.device)), "dsv4_attn_combine")
+    return out, lse
+
+
+def hca_decode_fwd(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink_logits, sm_scale, *, M_cur, swa_len,
+                   O=None, partial_O=None, partial_lse=None):
+    """The reference's entry point on its own cache layout (448 e4m3 + 7 UE8M0
+    + 64 bf16 per entry), same arguments as the reference's ctypes launcher
+    (bench/bench/candidates/hca_custom_decode.py:124-158)."""
+    _cuda_contig(Q, "Q", torch.bfloat16, 3)
+    B, n_h, dq = Q.shape
+    c = Kc.shape[-1]
+    n_rope = dq - c
+    if O is None:
+        O = torch.empty(B, n_h, dq, dtype=torch.bfloat16, device=Q.device)
+    S = (M_cur + swa_len) // 128
+    if partial_O is None and S > 1:
+        partial_O = torch.empty(S, B, n_h, dq, dtype=torch.float32, device=Q.device)
+        partial_lse = torch.empty(S, B, n_h, dtype=torch.float32, device=Q.device)
+    u8 = lambda t: t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+    rc = _lib.LIB.hca_decode_fwd(
+        _ptr(Q), _ptr(u8(Kc)), _ptr(Kc_s), _ptr(Kc_rope), _ptr(u8(Kswa)), _ptr(Kswa_s), _ptr(Kswa_rope),
+        _ptr(sink_logits), _ptr(O), _ptr(partial_O), _ptr(partial_lse),
+        C.c_float(float(sm_scale)), B, n_h, c, n_rope, int(M_cur), int(swa_len), _stream(Q.device))
+    _rc(rc, "hca_decode_fwd")
+    return O

@@ -1,0 +1,286 @@
+// C ABI of the library: argument validation, parameter filling, launches.
+// No allocation, no synchronisation, no global mutable state apart from
+// per-device kernel attributes that are set once.
+#include "../../include/dsv4_attn.h"
+
+#include <cuda_runtime.h>
+#include <cmath>
+#include <mutex>
+
+#include "combine.cuh"
+#include "decode_kernel.cuh"
+#include "decode_simt.cuh"
+
+namespace dsv4 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Opt in to the large dynamic shared memory once per (kernel, device).
+template <typename Kernel>
+cudaError_t ensure_smem(Kernel kernel, int bytes, bool* done_per_device) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!done_per_device[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        done_per_device[dev] = true;
+    }
+    return cudaSuccess;
+}
+
+template <int NCHUNK, int SRC>
+cudaError_t launch_mma(const DecodeArgs& a, int rows, cudaStream_t stream) {
+    static bool done[kMaxDevices] = {};
+    constexpr int smem = SmemLayout<NCHUNK>::kTotal;
+    cudaError_t e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
+    if (e != cudaSuccess) return e;
+    const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
+    dim3 grid(2 * head_groups, rows, a.num_splits);
+    decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <int SRC>
+cudaError_t launch_simt(const DecodeArgs& a, int rows, int max_tok, cudaStream_t stream) {
+    static bool done[kMaxDevices] = {};
+    const int smem = (576 + kSimtThreads + max_tok) * int(sizeof(float));
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_smem(decode_simt_kernel<SRC>, 200 * 1024, done);
+    if (e != cudaSuccess) return e;
+    dim3 grid(rows, a.H);
+    decode_simt_kernel<SRC><<<grid, kSimtThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const CombineArgs& c, cudaStream_t stream) {
+    const int64_t units = int64_t(c.N) * c.H;
+    const int blocks = int((units + kCombineWarps - 1) / kCombineWarps);
+    combine_kernel<<<blocks, kCombineWarps * 32, 0, stream>>>(c);
+    return cudaGetLastError();
+}
+
+CombineArgs contiguous_combine(int rows, int H, int S, const float* po, const float* pl, void* out, float* lse,
+                               const float* sink) {
+    CombineArgs c{};
+    c.N = rows;  c.H = H;  c.num_splits = S;
+    c.partial_o = po;  c.partial_lse = pl;
+    c.out = static_cast<__nv_bfloat16*>(out);  c.lse = lse;  c.attn_sink = sink;
+    c.stride_po_split = int64_t(rows) * H * 512;  c.stride_po_n = int64_t(H) * 512;  c.stride_po_h = 512;
+    c.stride_pl_split = int64_t(rows) * H;  c.stride_pl_n = H;
+    c.stride_out_n = int64_t(H) * 512;  c.stride_out_h = 512;
+    c.stride_lse_n = H;
+    return c;
+}
+
+bool common_ok(int B, int s_q, int H, int num_splits, float sm_scale, const void* q, const void* out,
+               const float* po, const float* pl) {
+    if (B <= 0 || s_q <= 0 || H <= 0) return false;
+    if (int64_t(B) * s_q > 65535) return false;                 // grid.y
+    if (num_splits < 1 || num_splits > DSV4_MAX_SPLITS) return false;
+    if (!(sm_scale > 0.f) || !std::isfinite(sm_scale)) return false;
+    if (q == nullptr || out == nullptr || !aligned(q, 16) || !aligned(out, 16)) return false;
+    if (num_splits > 1 && (po == nullptr || pl == nullptr || !aligned(po, 16))) return false;
+    return true;
+}
+
+bool fill_csa(const Dsv4CsaSparseDecodeParams* p, DecodeArgs& a) {
+    if (p == nullptr) return false;
+    if (!common_ok(p->B, p->s_q, p->H, p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
+        return false;
+    if (p->topk <= 0 || p->max_pages <= 0) return false;
+    if (p->kv_pool == nullptr || p->block_table == nullptr || p->indices == nullptr) return false;
+    if (!aligned(p->kv_pool, 16)) return false;
+    a = DecodeArgs{};
+    a.B = p->B;  a.s_q = p->s_q;  a.H = p->H;  a.topk = p->topk;  a.max_pages = p->max_pages;
+    a.num_splits = p->num_splits;
+    a.scale_log2 = p->sm_scale * 1.4426950408889634f;
+    a.q = static_cast<const __nv_bfloat16*>(p->q);
+    a.kv_pool = static_cast<const uint8_t*>(p->kv_pool);
+    a.block_table = p->block_table;  a.indices = p->indices;  a.kv_len = p->kv_len;
+    a.attn_sink = p->attn_sink;
+    a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
+    a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
+    return true;
+}
+
+bool fill_hca(const Dsv4HcaDenseDecodeParams* p, DecodeArgs& a) {
+    if (p == nullptr) return false;
+    if (!common_ok(p->B, p->s_q, p->H, p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
+        return false;
+    if (p->max_pages <= 0 || p->win_cap < 0) return false;
+    if (p->kv_pool == nullptr || p->block_table == nullptr || p->kv_len == nullptr || p->win_len == nullptr)
+        return false;
+    if (p->win_cap > 0 && p->win_pool == nullptr) return false;
+    if (!aligned(p->kv_pool, 16) || !aligned(p->win_pool, 16)) return false;
+    a = DecodeArgs{};
+    a.B = p->B;  a.s_q = p->s_q;  a.H = p->H;  a.max_pages = p->max_pages;  a.win_cap = p->win_cap;
+    a.num_splits = p->num_splits;
+    a.scale_log2 = p->sm_scale * 1.4426950408889634f;
+    a.q = static_cast<const __nv_bfloat16*>(p->q);
+    a.kv_pool = static_cast<const uint8_t*>(p->kv_pool);
+    a.block_table = p->block_table;  a.kv_len = p->kv_len;
+    a.win_pool = static_cast<const uint8_t*>(p->win_pool);  a.win_len = p->win_len;
+    a.attn_sink = p->attn_sink;
+    a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
+    a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
+    return true;
+}
+
+// Decode (+ merge when split) for the packed-entry sources.
+template <int SRC>
+int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
+    const int rows = a.B * a.s_q;
+    cudaError_t e = launch_mma<9, SRC>(a, rows, stream);
+    if (e != cudaSuccess) return int(e);
+    if (a.num_splits > 1) {
+        CombineArgs c = contiguous_combine(rows, a.H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink);
+        e = launch_combine(c, stream);
+    }
+    return int(e);
+}
+
+}  // namespace
+}  // namespace dsv4
+
+using namespace dsv4;
+
+extern "C" int dsv4_attn_version(void) { return (0 << 16) | 1; }
+
+extern "C" int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream) {
+    DecodeArgs a;
+    if (!fill_csa(p, a)) return int(cudaErrorInvalidValue);
+    return decode_fwd<kSrcCsa>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dsv4_hca_dense_decode_fwd(const Dsv4HcaDenseDecodeParams* p, void* stream) {
+    DecodeArgs a;
+    if (!fill_hca(p, a)) return int(cudaErrorInvalidValue);
+    return decode_fwd<kSrcHca>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dsv4_csa_sparse_decode_simt(const Dsv4CsaSparseDecodeParams* p, void* stream) {
+    DecodeArgs a;
+    if (!fill_csa(p, a) || p->num_splits != 1) return int(cudaErrorInvalidValue);
+    return int(launch_simt<kSrcCsa>(a, a.B * a.s_q, a.topk, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream) {
+    DecodeArgs a;
+    if (!fill_hca(p, a) || p->num_splits != 1) return int(cudaErrorInvalidValue);
+    // the longest row bounds the logit scratch; the caller's block table bounds kv_len
+    const int max_tok = p->max_pages * DSV4_PAGE_ENTRIES + p->win_cap;
+    return int(launch_simt<kSrcHca>(a, a.B * a.s_q, max_tok, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int dsv4_attn_combine(const Dsv4CombineParams* p, void* stream) {
+    if (p == nullptr || p->N <= 0 || p->H <= 0 || p->D != 512) return int(cudaErrorInvalidValue);
+    if (p->num_splits < 1 || p->num_splits > kCombineMaxSplits) return int(cudaErrorInvalidValue);
+    if (p->partial_o == nullptr || p->partial_lse == nullptr || p->out == nullptr) return int(cudaErrorInvalidValue);
+    if (!aligned(p->partial_o, 16) || !aligned(p->out, 16)) return int(cudaErrorInvalidValue);
+    if ((p->stride_po_split | p->stride_po_n | p->stride_po_h) % 4 != 0) return int(cudaErrorInvalidValue);
+    if ((p->stride_out_n | p->stride_out_h) % 8 != 0) return int(cudaErrorInvalidValue);
+    CombineArgs c{};
+    c.N = p->N;  c.H = p->H;  c.num_splits = p->num_splits;
+    c.partial_o = p->partial_o;  c.partial_lse = p->partial_lse;
+    c.out = static_cast<__nv_bfloat16*>(p->out);  c.lse = p->lse;  c.attn_sink = p->attn_sink;
+    c.stride_po_split = p->stride_po_split;  c.stride_po_n = p->stride_po_n;  c.stride_po_h = p->stride_po_h;
+    c.stride_pl_split = p->stride_pl_split;  c.stride_pl_n = p->stride_pl_n;
+    c.stride_out_n = p->stride_out_n;  c.stride_out_h = p->stride_out_h;
+    c.stride_lse_n = p->stride_lse_n;
+    return int(launch_combine(c, static_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms) {
+    if (rows <= 0 || H <= 0 || max_len < 0) return -int(cudaErrorInvalidValue);
+    if (num_sms <= 0) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return -int(e);
+    }
+    const int tiles = (max_len + kTileN - 1) / kTileN;
+    if (tiles <= 1) return 1;
+    const int64_t units = int64_t(rows) * 2 * ((H + kHeadsPerCta - 1) / kHeadsPerCta);
+    // Cost model in units of one tile's time: a block costs a fixed set-up (Q
+    // load, tensor-memory allocation, epilogue) plus its tiles; blocks run in
+    // waves of `num_sms`; splitting adds the partial write + merge read.
+    const double fixed = 3.0, merge_per_split = 0.6;
+    double best = 1e300;
+    int best_s = 1;
+    const int max_s = tiles < DSV4_MAX_SPLITS ? tiles : DSV4_MAX_SPLITS;
+    for (int s = 1; s <= max_s; ++s) {
+        const int tps = (tiles + s - 1) / s;
+        if (s > 1 && (tiles + tps - 1) / tps != s) continue;   // would leave an empty split
+        const int64_t blocks = units * s;
+        const double waves = std::ceil(double(blocks) / num_sms);
+        double cost = waves * (fixed + tps);
+        if (s > 1) cost += merge_per_split * s * std::ceil(double(units) / num_sms);
+        if (cost < best - 1e-9) { best = cost;  best_s = s; }
+    }
+    return best_s;
+}
+
+extern "C" int64_t dsv4_attn_workspace_bytes(int rows, int H, int num_splits, int64_t* lse_offset) {
+    if (rows <= 0 || H <= 0 || num_splits <= 1) {
+        if (lse_offset) *lse_offset = 0;
+        return 0;
+    }
+    const int64_t po = int64_t(num_splits) * rows * H * 512 * 4;
+    const int64_t pl = int64_t(num_splits) * rows * H * 4;
+    if (lse_offset) *lse_offset = po;
+    return po + ((pl + 255) / 256) * 256;
+}
+
+extern "C" int hca_decode_fwd(const void* Q,
+                              const void* Kc, const void* Kc_s, const void* Kc_rope,
+                              const void* Kswa, const void* Kswa_s, const void* Kswa_rope,
+                              const void* sink_logits,
+                              void* O, void* partial_O, void* partial_lse,
+                              float sm_scale,
+                              int B, int n_h, int c, int n_rope,
+                              int M_cur, int swa_len,
+                              void* stream) {
+    if (B <= 0 || B > 65535 || n_h <= 0 || c != 448 || n_rope != 64) return int(cudaErrorInvalidValue);
+    if (M_cur < 0 || swa_len < 0 || M_cur + swa_len < 1) return int(cudaErrorInvalidValue);
+    if (Q == nullptr || O == nullptr || !aligned(Q, 16) || !aligned(O, 16)) return int(cudaErrorInvalidValue);
+    if (!(sm_scale > 0.f) || !std::isfinite(sm_scale)) return int(cudaErrorInvalidValue);
+    if (M_cur > 0 && (Kc == nullptr || Kc_s == nullptr || Kc_rope == nullptr || !aligned(Kc, 16) || !aligned(Kc_rope, 16)))
+        return int(cudaErrorInvalidValue);
+    if (swa_len > 0 && (Kswa == nullptr || Kswa_s == nullptr || Kswa_rope == nullptr || !aligned(Kswa, 16) ||
+                        !aligned(Kswa_rope, 16)))
+        return int(cudaErrorInvalidValue);
+
+    DecodeArgs a{};
+    a.B = B;  a.s_q = 1;  a.H = n_h;
+    a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.q = static_cast<const __nv_bfloat16*>(Q);
+    a.out = static_cast<__nv_bfloat16*>(O);
+    a.attn_sink = static_cast<const float*>(sink_logits);
+    a.ref_kc = static_cast<const uint8_t*>(Kc);  a.ref_kc_s = static_cast<const uint8_t*>(Kc_s);
+    a.ref_kc_rope = static_cast<const __nv_bfloat16*>(Kc_rope);
+    a.ref_ks = static_cast<const uint8_t*>(Kswa);  a.ref_ks_s = static_cast<const uint8_t*>(Kswa_s);
+    a.ref_ks_rope = static_cast<const __nv_bfloat16*>(Kswa_rope);
+    a.ref_m_cur = M_cur;  a.ref_swa_len = swa_len;
+    // The caller sizes the workspaces for (M_cur + swa_len) / 128 splits; never use more.
+    const int caller_splits = (M_cur + swa_len) / 128;
+    int splits = dsv4_attn_plan_splits(B, n_h, M_cur + swa_len, 0);
+    if (splits < 1) return -splits;
+    if (splits > caller_splits) splits = caller_splits;
+    if (splits < 1 || partial_O == nullptr || partial_lse == nullptr || !aligned(partial_O, 16)) splits = 1;
+    a.num_splits = splits;
+    a.partial_o = static_cast<float*>(partial_O);
+    a.partial_lse = static_cast<float*>(partial_lse);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = launch_mma<8, kSrcRef>(a, B, s);
+    if (e != cudaSuccess) return int(e);
+    if (splits > 1) {
+        CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink);
+        e = launch_combine(cb, s);
+    }
+    return int(e);
+}

@@ -1,0 +1,111 @@
+// LSE-weighted merge of split-KV partial outputs.  One warp per (row, head):
+// the per-split log2 LSEs are reduced with warp shuffles, each lane then owns
+// 2 x 8 consecutive value columns, reads partials with 128-bit loads and
+// writes BF16 with 128-bit stores.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace dsv4 {
+
+struct CombineArgs {
+    int N, H, num_splits;
+    const float* partial_o;
+    const float* partial_lse;
+    __nv_bfloat16* out;
+    float* lse;
+    const float* attn_sink;
+    int64_t stride_po_split, stride_po_n, stride_po_h;
+    int64_t stride_pl_split, stride_pl_n;
+    int64_t stride_out_n, stride_out_h;
+    int64_t stride_lse_n;
+};
+
+constexpr int kCombineWarps = 8;
+constexpr int kCombineMaxSplits = 1024;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t unit = int64_t(blockIdx.x) * kCombineWarps + warp;   // (row, head) flattened
+    if (unit >= int64_t(a.N) * a.H) return;
+    const int n = int(unit / a.H), h = int(unit % a.H);
+    const int S = a.num_splits;
+
+    const float* pl = a.partial_lse + int64_t(n) * a.stride_pl_n + h;
+    // pass 1: maximum and sum over splits, 32 splits per step
+    float mx = -CUDART_INF_F;
+    for (int s = lane; s < S; s += 32) mx = fmaxf(mx, __ldg(pl + int64_t(s) * a.stride_pl_split));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    if (mx != -CUDART_INF_F)
+        for (int s = lane; s < S; s += 32) sum += exp2f(__ldg(pl + int64_t(s) * a.stride_pl_split) - mx);
+    sum = warp_sum(sum);
+    const bool has = sum != 0.f;
+    const float glse = has ? log2f(sum) + mx : -CUDART_INF_F;
+    if (lane == 0 && a.lse != nullptr)
+        a.lse[int64_t(n) * a.stride_lse_n + h] = has ? glse * 0.6931471805599453f : -CUDART_INF_F;
+    float denom = glse;
+    if (a.attn_sink != nullptr) {
+        const float s2 = __ldg(a.attn_sink + h) * 1.4426950408889634f;
+        denom = has ? glse + log2f(1.f + exp2f(s2 - glse)) : s2;
+    }
+
+    float acc[2][8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+
+    const float* po = a.partial_o + int64_t(n) * a.stride_po_n + int64_t(h) * a.stride_po_h + lane * 8;
+    for (int s0 = 0; s0 < S; s0 += 32) {
+        // each lane computes the weight of one split of this group; broadcast by shuffle
+        float w_mine = 0.f;
+        if (s0 + lane < S) {
+            const float l = __ldg(pl + int64_t(s0 + lane) * a.stride_pl_split);
+            w_mine = (l == -CUDART_INF_F || denom == -CUDART_INF_F) ? 0.f : exp2f(l - denom);
+        }
+        const int cnt = min(32, S - s0);
+        for (int k = 0; k < cnt; ++k) {
+            const float w = __shfl_sync(0xFFFFFFFFu, w_mine, k);
+            if (w == 0.f) continue;     // empty split: its partial may hold anything
+            const float* src = po + int64_t(s0 + k) * a.stride_po_split;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float4 v0 = __ldg(reinterpret_cast<const float4*>(src + i * 256));
+                const float4 v1 = __ldg(reinterpret_cast<const float4*>(src + i * 256 + 4));
+                acc[i][0] = fmaf(w, v0.x, acc[i][0]);  acc[i][1] = fmaf(w, v0.y, acc[i][1]);
+                acc[i][2] = fmaf(w, v0.z, acc[i][2]);  acc[i][3] = fmaf(w, v0.w, acc[i][3]);
+                acc[i][4] = fmaf(w, v1.x, acc[i][4]);  acc[i][5] = fmaf(w, v1.y, acc[i][5]);
+                acc[i][6] = fmaf(w, v1.z, acc[i][6]);  acc[i][7] = fmaf(w, v1.w, acc[i][7]);
+            }
+        }
+    }
+    __nv_bfloat16* dst = a.out + int64_t(n) * a.stride_out_n + int64_t(h) * a.stride_out_h + lane * 8;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 w;
+        w.x = ptx::pack_bf16x2(acc[i][0], acc[i][1]);
+        w.y = ptx::pack_bf16x2(acc[i][2], acc[i][3]);
+        w.z = ptx::pack_bf16x2(acc[i][4], acc[i][5]);
+        w.w = ptx::pack_bf16x2(acc[i][6], acc[i][7]);
+        *reinterpret_cast<uint4*>(dst + i * 256) = w;
+    }
+}
+
+}  // namespace dsv4

@@ -1,0 +1,572 @@
+// Decode attention over an FP8 latent KV cache on sm_100a tensor cores.
+//
+// One thread block handles (request-token row n, group of 128 heads, one half
+// of the 512 value columns, one KV split).  Per 64-entry tile:
+//   loader warps   gather the entries (index list -> block table -> 656-byte
+//                  rows, or the dense / reference-layout equivalents) into
+//                  registers, dequantise FP8 * scale -> BF16 and write the tile
+//                  into shared memory in the 128-byte-swizzled operand layout;
+//   MMA thread     S[128 heads x 64] = Q . K^T   (tcgen05.mma, BF16, K = 576
+//                  or 512) into tensor memory, later O[128 x 256] += P . V with
+//                  V read from the same tile as an MN-major operand;
+//   softmax warps  read S from tensor memory (one head per thread), run the
+//                  online softmax with a lazily updated reference maximum,
+//                  write P (BF16) to shared memory, rescale O in tensor memory
+//                  when the maximum moved, and finally normalise and store.
+// All waits are bounded; a wait that gives up records where in `status` and the
+// block leaves through the common exit, freeing its tensor memory.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace dsv4 {
+
+constexpr int kTileN = 64;             // cache entries per tile (MMA N of S, K of PV)
+constexpr int kHeadsPerCta = 128;      // MMA M
+constexpr int kDvHalf = 256;           // value columns per block (MMA N of PV)
+constexpr int kQChunkBytes = 128 * 128;   // 128 heads x 64 bf16
+constexpr int kKvChunkBytes = kTileN * 128;  // 64 entries x 64 bf16
+constexpr int kNumSoftmaxWarps = 4;
+constexpr int kMmaWarp = 4;
+constexpr int kNumLoaderWarps = 8;
+constexpr int kFirstLoaderWarp = 5;
+constexpr int kNumThreads = (kNumSoftmaxWarps + 1 + kNumLoaderWarps) * 32;  // 416
+constexpr int kTmemCols = 512;
+constexpr int kTmemS = 0;              // S accumulator: 64 columns
+constexpr int kTmemO = 256;            // O accumulator: 256 columns
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr float kRescaleThreshold = 8.0f;  // log2 units; O is rescaled only when the max grows by more
+
+enum SourceKind : int {
+    kSrcCsa = 0,   // index list + block table, packed 656-byte entries
+    kSrcHca = 1,   // dense [0, kv_len) through the block table, then the window buffer
+    kSrcRef = 2,   // reference layout: separate planes, 448 e4m3 + 7 UE8M0 + 64 bf16
+};
+
+enum StatusCode : int {
+    kStatusOk = 0,
+    kStatusWaitKvFull = 1,
+    kStatusWaitKvFree = 2,
+    kStatusWaitSFull = 3,
+    kStatusWaitPFull = 4,
+    kStatusWaitOFull = 5,
+};
+
+struct DecodeArgs {
+    int B, s_q, H;
+    int topk;            // CSA
+    int max_pages;
+    int win_cap;         // HCA
+    int num_splits;
+    float scale_log2;    // sm_scale * log2(e)
+    const __nv_bfloat16* q;
+    const uint8_t* kv_pool;
+    const int32_t* block_table;
+    const int32_t* indices;
+    const int32_t* kv_len;
+    const uint8_t* win_pool;
+    const int32_t* win_len;
+    const float* attn_sink;
+    __nv_bfloat16* out;
+    float* lse;
+    float* partial_o;
+    float* partial_lse;
+    int32_t* status;
+    // reference layout planes (kSrcRef)
+    const uint8_t* ref_kc;  const uint8_t* ref_kc_s;  const __nv_bfloat16* ref_kc_rope;
+    const uint8_t* ref_ks;  const uint8_t* ref_ks_s;  const __nv_bfloat16* ref_ks_rope;
+    int ref_m_cur, ref_swa_len;
+};
+
+template <int NCHUNK>
+struct SmemLayout {
+    static constexpr int kQBytes = NCHUNK * kQChunkBytes;
+    static constexpr int kKvBytes = NCHUNK * kKvChunkBytes;
+    static constexpr int kQOff = 0;
+    static constexpr int kKvOff = kQBytes;
+    static constexpr int kMiscOff = kQBytes + kKvBytes;
+    static constexpr int kMiscBytes = 256;
+    static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;  // + slack to align the base to 1024
+};
+
+struct SmemMisc {
+    uint64_t bar_kv_full;
+    uint64_t bar_kv_free;
+    uint64_t bar_s_full;
+    uint64_t bar_p_full;
+    uint64_t bar_o_full;
+    uint64_t valid_mask;      // bit t = entry t of the current tile takes part in the softmax
+    uint32_t tmem_base;
+    uint32_t pad;
+};
+
+__device__ __forceinline__ void report_timeout(int32_t* status, int code, int role, int tile) {
+    if (status != nullptr) {
+        if (atomicCAS(status, 0, code) == 0) {
+            status[1] = int(blockIdx.x) | (int(blockIdx.y) << 8) | (int(blockIdx.z) << 20);
+            status[2] = role;
+            status[3] = tile;
+        }
+    }
+}
+
+// FP8 e4m3 x4 (one 32-bit word) times `scale` -> 4 BF16 (two packed words).
+__device__ __forceinline__ void dequant4(uint32_t w, float scale, uint32_t& lo, uint32_t& hi) {
+    __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xFFFFu), __NV_E4M3);
+    __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
+    float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&h01));
+    float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&h23));
+    lo = ptx::pack_bf16x2(f01.x * scale, f01.y * scale);
+    hi = ptx::pack_bf16x2(f23.x * scale, f23.y * scale);
+}
+
+// Registers one loader thread holds for one tile: a quarter of one entry.
+template <int SRC>
+struct LoaderRegs {
+    static constexpr int kLatVecs = (SRC == kSrcRef) ? 7 : 8;   // 16-byte vectors of FP8 latent
+    uint4 lat[kLatVecs];
+    uint4 rope[2];
+    float scale;            // packed layout: the FP32 scale of this thread's 128-element block
+    uint32_t sbytes[2];     // reference layout: the 7 UE8M0 bytes of the entry
+    bool valid;
+};
+
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_issue(const DecodeArgs& a, int b, int n, int tile, int t, int j,
+                                             int n_tok, int kv_len_n, LoaderRegs<SRC>& r) {
+    const int v = tile * kTileN + t;      // position in this row's entry sequence
+    const uint8_t* row = nullptr;
+    bool valid = v < n_tok;
+    if constexpr (SRC == kSrcCsa) {
+        int e = -1;
+        if (valid) e = __ldg(a.indices + int64_t(n) * a.topk + v);
+        valid = (e >= 0) && (e < kv_len_n);
+        if (valid) {
+            const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (e >> 6));
+            row = a.kv_pool + (int64_t(page) * 64 + (e & 63)) * 656;
+        }
+    } else if constexpr (SRC == kSrcHca) {
+        if (valid) {
+            if (v < kv_len_n) {
+                const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (v >> 6));
+                row = a.kv_pool + (int64_t(page) * 64 + (v & 63)) * 656;
+            } else {
+                row = a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656;
+            }
+        }
+    }
+    r.valid = valid;
+    if constexpr (SRC != kSrcRef) {
+        if (valid) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r.lat[i] = ptx::ldg_nc_v4(row + j * 128 + i * 16);
+            r.scale = __ldg(reinterpret_cast<const float*>(row + 512) + j);
+            r.rope[0] = ptx::ldg_nc_v4(row + 528 + (2 * j) * 16);
+            r.rope[1] = ptx::ldg_nc_v4(row + 528 + (2 * j + 1) * 16);
+        }
+    } else {
+        if (valid) {
+            const uint8_t* lat;  const uint8_t* sc;  const __nv_bfloat16* rp;
+            if (v < a.ref_m_cur) {
+                const int64_t e = int64_t(b) * a.ref_m_cur + v;
+                lat = a.ref_kc + e * 448;  sc = a.ref_kc_s + e * 7;  rp = a.ref_kc_rope + e * 64;
+            } else {
+                const int64_t e = int64_t(b) * a.ref_swa_len + (v - a.ref_m_cur);
+                lat = a.ref_ks + e * 448;  sc = a.ref_ks_s + e * 7;  rp = a.ref_ks_rope + e * 64;
+            }
+#pragma unroll
+            for (int i = 0; i < 7; ++i) r.lat[i] = ptx::ldg_nc_v4(lat + j * 112 + i * 16);
+            uint32_t s0 = 0, s1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s0 |= uint32_t(__ldg(sc + i)) << (8 * i);
+#pragma unroll
+            for (int i = 0; i < 3; ++i) s1 |= uint32_t(__ldg(sc + 4 + i)) << (8 * i);
+            r.sbytes[0] = s0;  r.sbytes[1] = s1;
+            r.rope[0] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(rp) + (2 * j) * 16);
+            r.rope[1] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(rp) + (2 * j + 1) * 16);
+        }
+    }
+}
+
+// Write this thread's quarter entry into the KV tile: row t of each 64-column
+// chunk is 128 bytes; 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_store(uint32_t kv_base, int t, int j, const LoaderRegs<SRC>& r) {
+    const uint32_t row_off = uint32_t(t) * 128u;
+    const uint32_t sw = uint32_t(t & 7);
+    constexpr int kLatVecs = LoaderRegs<SRC>::kLatVecs;
+    const int d0 = j * kLatVecs * 16;     // first latent dim of this thread
+#pragma unroll
+    for (int i = 0; i < kLatVecs; ++i) {
+        const int d = d0 + i * 16;
+        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
+        if (r.valid) {
+            float scale;
+            if constexpr (SRC == kSrcRef) {
+                const int blk = d >> 6;
+                const uint32_t byte = (blk < 4) ? ((r.sbytes[0] >> (8 * blk)) & 0xFFu)
+                                                : ((r.sbytes[1] >> (8 * (blk - 4))) & 0xFFu);
+                scale = __uint_as_float(byte << 23);
+            } else {
+                scale = r.scale;
+            }
+            dequant4(r.lat[i].x, scale, w0.x, w0.y);
+            dequant4(r.lat[i].y, scale, w0.z, w0.w);
+            dequant4(r.lat[i].z, scale, w1.x, w1.y);
+            dequant4(r.lat[i].w, scale, w1.z, w1.w);
+        }
+        const uint32_t chunk = uint32_t(d >> 6);
+        const uint32_t c16 = uint32_t((d & 63) >> 3);
+        const uint32_t base = kv_base + chunk * kKvChunkBytes + row_off;
+        ptx::sts_v4(base + (((c16) ^ sw) << 4), w0);
+        ptx::sts_v4(base + (((c16 + 1) ^ sw) << 4), w1);
+    }
+    {
+        const uint32_t base = kv_base + uint32_t(NCHUNK - 1) * kKvChunkBytes + row_off;
+        uint4 z = make_uint4(0, 0, 0, 0);
+        ptx::sts_v4(base + ((uint32_t(2 * j) ^ sw) << 4), r.valid ? r.rope[0] : z);
+        ptx::sts_v4(base + ((uint32_t(2 * j + 1) ^ sw) << 4), r.valid ? r.rope[1] : z);
+    }
+}
+
+template <int NCHUNK, int SRC>
+__global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid_constant__ DecodeArgs a) {
+    using L = SmemLayout<NCHUNK>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t q_base = smem_base + L::kQOff;
+    const uint32_t kv_base = smem_base + L::kKvOff;
+    SmemMisc* misc = reinterpret_cast<SmemMisc*>(smem_gen + L::kMiscOff);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int half = blockIdx.x & 1;
+    const int hg = blockIdx.x >> 1;
+    const int n = blockIdx.y;                // row = b * s_q + query token
+    const int split = blockIdx.z;
+    const int b = n / a.s_q;
+
+    // ── this block's tile range ──
+    int n_tok, kv_len_n;
+    if constexpr (SRC == kSrcCsa) {
+        n_tok = a.topk;
+        kv_len_n = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
+    } else if constexpr (SRC == kSrcHca) {
+        kv_len_n = max(__ldg(a.kv_len + n), 0);
+        n_tok = kv_len_n + max(__ldg(a.win_len + n), 0);
+    } else {
+        kv_len_n = a.ref_m_cur;
+        n_tok = a.ref_m_cur + a.ref_swa_len;
+    }
+    const int tiles_total = (n_tok + kTileN - 1) / kTileN;
+    const int tiles_per_split = (tiles_total + a.num_splits - 1) / a.num_splits;
+    const int tile0 = min(split * tiles_per_split, tiles_total);
+    const int tile1 = min(tile0 + tiles_per_split, tiles_total);
+    const int ntiles = tile1 - tile0;
+
+    // P (128 x 64 bf16, K-major) overlays two KV chunks that are dead once S is
+    // complete: chunks outside this block's value half.
+    const uint32_t p_base = kv_base + uint32_t(half ? 0 : 4) * kKvChunkBytes;
+    const uint32_t v_base = kv_base + uint32_t(half ? 4 : 0) * kKvChunkBytes;
+
+    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full);
+    const uint32_t bar_kv_free = ptx::smem_u32(&misc->bar_kv_free);
+    const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full);
+    const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full);
+    const uint32_t bar_o_full = ptx::smem_u32(&misc->bar_o_full);
+
+    // ── set-up ──
+    if (tid == 0) {
+        ptx::mbar_init(bar_kv_full, kNumLoaderWarps);
+        ptx::mbar_init(bar_kv_free, 1);
+        ptx::mbar_init(bar_s_full, 1);
+        ptx::mbar_init(bar_p_full, kNumSoftmaxWarps);
+        ptx::mbar_init(bar_o_full, 1);
+        ptx::fence_mbar_init();
+    }
+    if (warp == kMmaWarp) {
+        ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    // Q tile: [128 heads x NCHUNK*64] bf16 -> NCHUNK swizzled chunks; rows >= H are zero.
+    if (ntiles > 0) {
+        constexpr int kVecsPerRow = NCHUNK * 8;
+        const __nv_bfloat16* qrow0 = a.q + int64_t(n) * a.H * (NCHUNK * 64);
+        for (int v = tid; v < kHeadsPerCta * kVecsPerRow; v += kNumThreads) {
+            const int r = v / kVecsPerRow;
+            const int cv = v - r * kVecsPerRow;
+            const int h = hg * kHeadsPerCta + r;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (h < a.H) w = ptx::ldg_nc_v4(qrow0 + int64_t(h) * (NCHUNK * 64) + cv * 8);
+            const uint32_t c = uint32_t(cv >> 3), c16 = uint32_t(cv & 7);
+            ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ uint32_t(r & 7)) << 4), w);
+        }
+        ptx::fence_proxy_async_smem();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = misc->tmem_base;
+
+    if (ntiles > 0) {
+        if (warp >= kFirstLoaderWarp) {
+            // ───────────── loader warps ─────────────
+            const int ltid = tid - kFirstLoaderWarp * 32;
+            const int t = ltid >> 2;       // entry of the tile
+            const int j = ltid & 3;        // quarter of the entry
+            const int lw = warp - kFirstLoaderWarp;
+            LoaderRegs<SRC> regs;
+            loader_issue<NCHUNK, SRC>(a, b, n, tile0, t, j, n_tok, kv_len_n, regs);
+            for (int it = 0; it < ntiles; ++it) {
+                if (it > 0) {
+                    // warp-uniform outcome: the warp-collective operations below need all lanes
+                    const bool w = ptx::mbar_wait(bar_kv_free, uint32_t(it - 1) & 1u, kWaitTimeoutNs);
+                    if (!__all_sync(0xFFFFFFFFu, w)) {
+                        report_timeout(a.status, kStatusWaitKvFree, 2, tile0 + it);
+                        break;
+                    }
+                }
+                loader_store<NCHUNK, SRC>(kv_base, t, j, regs);
+                const uint32_t bal = __ballot_sync(0xFFFFFFFFu, regs.valid);
+                if (lane == 0) {
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) m |= ((bal >> (4 * i)) & 1u) << i;
+                    reinterpret_cast<volatile uint8_t*>(&misc->valid_mask)[lw] = uint8_t(m);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_kv_full);
+                if (it + 1 < ntiles)
+                    loader_issue<NCHUNK, SRC>(a, b, n, tile0 + it + 1, t, j, n_tok, kv_len_n, regs);
+            }
+        } else if (warp == kMmaWarp) {
+            // ───────────── MMA issue (one thread) ─────────────
+            if (lane == 0) {
+                constexpr uint32_t idesc_qk = ptx::make_idesc_bf16(128, kTileN, false, false);
+                constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(128, kDvHalf, false, true);
+                bool ok = true;
+                for (int it = 0; it < ntiles && ok; ++it) {
+                    if (!ptx::mbar_wait(bar_kv_full, uint32_t(it) & 1u, kWaitTimeoutNs)) {
+                        report_timeout(a.status, kStatusWaitKvFull, 1, tile0 + it);
+                        ok = false;  break;
+                    }
+                    ptx::tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < NCHUNK; ++c) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t da = ptx::make_smem_desc(q_base + c * kQChunkBytes + k * 32, 16, 1024);
+                            const uint64_t db = ptx::make_smem_desc(kv_base + c * kKvChunkBytes + k * 32, 16, 1024);
+                            ptx::mma_bf16_ss(tmem + kTmemS, da, db, idesc_qk, (c | k) ? 1u : 0u);
+                        }
+                    }
+                    ptx::mma_commit(bar_s_full);
+                    if (!ptx::mbar_wait(bar_p_full, uint32_t(it) & 1u, kWaitTimeoutNs)) {
+                        report_timeout(a.status, kStatusWaitPFull, 1, tile0 + it);
+                        ok = false;  break;
+                    }
+                    ptx::tc_fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // A = P rows (K-major, 16 entries = 32 bytes per step);
+                        // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart,
+                        // 8-entry groups 1 KB apart.
+                        const uint64_t da = ptx::make_smem_desc(p_base + k * 32, 16, 1024);
+                        const uint64_t db = ptx::make_smem_desc(v_base + k * 2048, kKvChunkBytes, 1024);
+                        ptx::mma_bf16_ss(tmem + kTmemO, da, db, idesc_pv, (it | k) ? 1u : 0u);
+                    }
+                    ptx::mma_commit(bar_kv_free);
+                }
+                if (ok) ptx::mma_commit(bar_o_full);
+            }
+            __syncwarp();
+        } else {
+            // ───────────── softmax + epilogue warps ─────────────
+            const int r = warp * 32 + lane;                // head row inside the group
+            const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+            float m_ref = -CUDART_INF_F;                   // reference maximum used in exp2 (log2 units)
+            float l_sum = 0.f;
+            bool ok = true;
+            for (int it = 0; it < ntiles; ++it) {
+                {
+                    const bool w = ptx::mbar_wait(bar_s_full, uint32_t(it) & 1u, kWaitTimeoutNs);
+                    if (!__all_sync(0xFFFFFFFFu, w)) {
+                        report_timeout(a.status, kStatusWaitSFull, 0, tile0 + it);
+                        ok = false;  break;
+                    }
+                }
+                ptx::tc_fence_after_sync();
+                uint32_t s0[32], s1[32];
+                ptx::tmem_ld32(tmem + lane_addr + kTmemS, s0);
+                ptx::tmem_ld32(tmem + lane_addr + kTmemS + 32, s1);
+                ptx::tmem_wait_ld();
+                const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask);
+                const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
+                float x0[32], x1[32];
+                float tmax = -CUDART_INF_F;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    x0[i] = ((vm0 >> i) & 1u) ? __uint_as_float(s0[i]) * a.scale_log2 : -CUDART_INF_F;
+                    x1[i] = ((vm1 >> i) & 1u) ? __uint_as_float(s1[i]) * a.scale_log2 : -CUDART_INF_F;
+                    tmax = fmaxf(tmax, fmaxf(x0[i], x1[i]));
+                }
+                // Lazy reference maximum: move it only when the true maximum exceeds it by
+                // more than the threshold (exp2 of the excess stays <= 2^threshold).
+                float alpha = 1.f;
+                bool moved = false;
+                if (tmax > m_ref + kRescaleThreshold) {   // also true for the first finite max
+                    alpha = (m_ref == -CUDART_INF_F) ? 0.f : ptx::ex2(m_ref - tmax);
+                    m_ref = tmax;
+                    moved = true;
+                }
+                const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+                float psum = 0.f;
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = ptx::ex2(x0[2 * i] - m_use), p1 = ptx::ex2(x0[2 * i + 1] - m_use);
+                    psum += p0 + p1;
+                    pk[i] = ptx::pack_bf16x2(p0, p1);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = ptx::ex2(x1[2 * i] - m_use), p1 = ptx::ex2(x1[2 * i + 1] - m_use);
+                    psum += p0 + p1;
+                    pk[16 + i] = ptx::pack_bf16x2(p0, p1);
+                }
+                l_sum = l_sum * alpha + psum;
+                // P row r: 8 vectors of 8 entries
+                {
+                    const uint32_t prow = p_base + uint32_t(r) * 128u;
+                    const uint32_t sw = uint32_t(r & 7);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v)
+                        ptx::sts_v4(prow + ((uint32_t(v) ^ sw) << 4),
+                                    make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]));
+                }
+                // Rescale O where the reference maximum moved.  All earlier MMAs have
+                // completed (the commit that released S follows them in issue order).
+                if (it > 0 && __any_sync(0xFFFFFFFFu, moved)) {
+#pragma unroll 1
+                    for (int c = 0; c < kDvHalf / 32; ++c) {
+                        uint32_t o[32];
+                        ptx::tmem_ld32(tmem + lane_addr + kTmemO + c * 32, o);
+                        ptx::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st32(tmem + lane_addr + kTmemO + c * 32, o);
+                    }
+                    ptx::tmem_wait_st();
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_p_full);
+            }
+            // ── epilogue ──
+            if (ok) {
+                const bool w = ptx::mbar_wait(bar_o_full, 0u, kWaitTimeoutNs);
+                if (!__all_sync(0xFFFFFFFFu, w)) {
+                    report_timeout(a.status, kStatusWaitOFull, 0, tile1);
+                    ok = false;
+                }
+            }
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                const int h = hg * kHeadsPerCta + r;
+                const bool write = h < a.H;
+                const bool final_out = a.num_splits == 1;
+                float denom = l_sum;
+                if (final_out && a.attn_sink != nullptr && write) {
+                    const float s2 = __ldg(a.attn_sink + h) * 1.4426950408889634f;
+                    denom = (l_sum > 0.f) ? l_sum + ptx::ex2(s2 - m_ref) : 1.f;   // empty row: O is 0 anyway
+                }
+                const float inv = (l_sum > 0.f) ? 1.f / denom : 0.f;
+                const float lse2 = (l_sum > 0.f) ? m_ref + log2f(l_sum) : -CUDART_INF_F;
+                const int64_t row = int64_t(n) * a.H + h;
+#pragma unroll 1
+                for (int c = 0; c < kDvHalf / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld32(tmem + lane_addr + kTmemO + c * 32, o);
+                    ptx::tmem_wait_ld();
+                    if (write) {
+                        const int col = half * kDvHalf + c * 32;
+                        if (final_out) {
+                            uint4* dst = reinterpret_cast<uint4*>(a.out + row * 512 + col);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 w;
+                                w.x = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                                w.y = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                                w.z = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                                w.w = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                                dst[v] = w;
+                            }
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(
+                                a.partial_o + (int64_t(split) * gridDim.y * a.H + row) * 512 + col);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                dst[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                                     __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                        }
+                    }
+                }
+                if (write && half == 0) {
+                    if (final_out) {
+                        if (a.lse != nullptr) a.lse[row] = (l_sum > 0.f) ? lse2 * 0.6931471805599453f : -CUDART_INF_F;
+                    } else {
+                        a.partial_lse[int64_t(split) * gridDim.y * a.H + row] = lse2;
+                    }
+                }
+            }
+        }
+    } else {
+        // Nothing to attend to in this split: zero output, LSE = -inf.
+        const bool final_out = a.num_splits == 1;
+        for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumThreads) {
+            const int r = i / (kDvHalf / 8), v = i % (kDvHalf / 8);
+            const int h = hg * kHeadsPerCta + r;
+            if (h >= a.H) continue;
+            const int64_t row = int64_t(n) * a.H + h;
+            const int col = half * kDvHalf + v * 8;
+            if (final_out) {
+                *reinterpret_cast<uint4*>(a.out + row * 512 + col) = make_uint4(0, 0, 0, 0);
+            } else {
+                float4* dst = reinterpret_cast<float4*>(a.partial_o + (int64_t(split) * gridDim.y * a.H + row) * 512 + col);
+                dst[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                dst[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (half == 0 && tid < kHeadsPerCta) {
+            const int h = hg * kHeadsPerCta + tid;
+            if (h < a.H) {
+                const int64_t row = int64_t(n) * a.H + h;
+                if (final_out) {
+                    if (a.lse != nullptr) a.lse[row] = -CUDART_INF_F;
+                } else {
+                    a.partial_lse[int64_t(split) * gridDim.y * a.H + row] = -CUDART_INF_F;
+                }
+            }
+        }
+    }
+
+    // ── common exit: every thread gets here, with or without an error ──
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace dsv4

@@ -1,0 +1,195 @@
+/*
+ * dsv4_attn.h - C ABI of the B200 (sm_100a) decode-attention library for
+ * DeepSeek-V4-style attention: CSA sparse decode, HCA dense decode, and the
+ * split-KV merge.
+ *
+ * Conventions (the same ones the reference project's C entry point follows,
+ * hca/sm100/kernel.cu:269-358):
+ *   - every pointer is a raw DEVICE pointer owned by the caller; the library
+ *     allocates nothing and keeps no state between calls;
+ *   - work is enqueued on the `stream` argument (a cudaStream_t passed as
+ *     void*, NULL = default stream) and the call returns without synchronising;
+ *   - the return value is 0 on success, otherwise a cudaError_t value
+ *     (cudaErrorInvalidValue = 1 for rejected arguments).  Nothing throws and
+ *     nothing aborts.
+ *
+ * Cache entry ("BASELINE layout"), 656 bytes, 16-byte aligned:
+ *     [  0,512)  512 x FP8 e4m3 latent (also the value vector, d_v = 512)
+ *     [512,528)  4 x FP32 scale, one per 128 latent elements (value = fp8*scale)
+ *     [528,656)  64 x BF16 RoPE tail (already rotated)
+ * A page is 64 consecutive entries (41,984 bytes).  A pool is an array of
+ * pages; a request's block table maps logical page number -> pool page.
+ */
+#ifndef DSV4_ATTN_H_
+#define DSV4_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV4_D_LATENT      512
+#define DSV4_D_ROPE        64
+#define DSV4_D_QK          576
+#define DSV4_D_V           512
+#define DSV4_ENTRY_BYTES   656
+#define DSV4_PAGE_ENTRIES  64
+#define DSV4_MAX_SPLITS    64
+
+/* Words of the optional `status` array a kernel writes when one of its bounded
+ * waits gives up (it never traps and never spins without limit). */
+#define DSV4_STATUS_WORDS  4   /* [0] error code (0 = none), [1] block x|y<<8|z<<20, [2] role, [3] tile */
+
+/*
+ * CSA sparse decode.  For each request b and query token j the kernel gathers
+ * the cache entries named by indices[b][j][0..topk) through block_table[b],
+ * and computes softmax(q . k^T * sm_scale) . v over them in one pass.
+ *
+ * Takes the place of the reference's gather + attention core on pre-projected
+ * tensors (bench/bench/reference.py:576-580 followed by :516-545); the
+ * parameter-struct style follows hca/params.h:10-77 and csa/params.h:12-39.
+ */
+typedef struct Dsv4CsaSparseDecodeParams {
+    int32_t B;                  /* requests */
+    int32_t s_q;                /* query tokens per request (1, or 2 for speculative decode) */
+    int32_t H;                  /* query heads */
+    int32_t topk;               /* length of each index list */
+    int32_t max_pages;          /* row length of block_table */
+    int32_t num_splits;         /* >= 1; > 1 needs partial_o / partial_lse */
+    float   sm_scale;           /* softmax scale, usually 1/sqrt(576) */
+    int32_t reserved0;
+    int64_t num_pages;          /* pages in kv_pool (bounds checking of block_table is the caller's) */
+    const void*    q;           /* bf16  [B, s_q, H, 576] */
+    const void*    kv_pool;     /* uint8 [num_pages, 64, 656] */
+    const int32_t* block_table; /* int32 [B, max_pages] */
+    const int32_t* indices;     /* int32 [B, s_q, topk]; negative = padding */
+    const int32_t* kv_len;      /* optional int32 [B, s_q]: indices >= kv_len are masked (causality
+                                   between speculative tokens); NULL = no bound */
+    const float*   attn_sink;   /* optional float [H], natural-log units, added to the denominator */
+    void*          out;         /* bf16  [B, s_q, H, 512] */
+    float*         lse;         /* optional float [B, s_q, H], natural log, sink excluded, -inf if empty */
+    float*         partial_o;   /* float [num_splits, B*s_q, H, 512] when num_splits > 1 */
+    float*         partial_lse; /* float [num_splits, B*s_q, H], log2 units */
+    int32_t*       status;      /* optional int32 [DSV4_STATUS_WORDS], zeroed by the caller */
+} Dsv4CsaSparseDecodeParams;
+
+int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream);
+
+/*
+ * HCA dense decode.  Query token j of request b attends to every compressed
+ * entry [0, kv_len[b][j]) of the request (through the block table) followed by
+ * the first win_len[b][j] rows of the request's sliding-window buffer, in one
+ * softmax.
+ *
+ * Takes the place of the reference's hca_decode_forward
+ * (bench/bench/reference.py:471-546) and of its kernel parameter block
+ * (hca/params.h:10-77), with per-request lengths instead of one M_cur/swa_len
+ * for the whole batch.
+ */
+typedef struct Dsv4HcaDenseDecodeParams {
+    int32_t B;
+    int32_t s_q;
+    int32_t H;
+    int32_t max_pages;
+    int32_t win_cap;            /* rows per request in win_pool (W, usually 128) */
+    int32_t num_splits;
+    float   sm_scale;
+    int32_t reserved0;
+    int64_t num_pages;
+    const void*    q;           /* bf16  [B, s_q, H, 576] */
+    const void*    kv_pool;     /* uint8 [num_pages, 64, 656] */
+    const int32_t* block_table; /* int32 [B, max_pages] */
+    const int32_t* kv_len;      /* int32 [B, s_q] compressed entries visible to each query token */
+    const void*    win_pool;    /* uint8 [B, win_cap, 656] */
+    const int32_t* win_len;     /* int32 [B, s_q] window rows visible to each query token */
+    const float*   attn_sink;   /* optional float [H] */
+    void*          out;         /* bf16  [B, s_q, H, 512] */
+    float*         lse;         /* optional float [B, s_q, H] */
+    float*         partial_o;
+    float*         partial_lse;
+    int32_t*       status;
+} Dsv4HcaDenseDecodeParams;
+
+int dsv4_hca_dense_decode_fwd(const Dsv4HcaDenseDecodeParams* p, void* stream);
+
+/*
+ * LSE-weighted merge of split-KV partials.  Same algebra and the same field
+ * meaning as the reference's HcaCombineParams / launch_hca_combine
+ * (hca/sm100/combine.h:9-31, hca/sm100/combine.cu:25-145); `N` is the
+ * reference's B times the number of query tokens, and strides are in elements.
+ */
+typedef struct Dsv4CombineParams {
+    int32_t N;                  /* rows = B * s_q */
+    int32_t H;
+    int32_t D;                  /* must be 512 */
+    int32_t num_splits;         /* 1 .. 1024 */
+    const float* partial_o;     /* [split, N, H, D] */
+    const float* partial_lse;   /* [split, N, H], log2 units, -inf = empty split */
+    void*        out;           /* bf16 [N, H, D] */
+    float*       lse;           /* optional [N, H], natural log */
+    const float* attn_sink;     /* optional [H], natural-log units */
+    int64_t stride_po_split, stride_po_n, stride_po_h;
+    int64_t stride_pl_split, stride_pl_n;
+    int64_t stride_out_n, stride_out_h;
+    int64_t stride_lse_n;
+} Dsv4CombineParams;
+
+int dsv4_attn_combine(const Dsv4CombineParams* p, void* stream);
+
+/*
+ * Split-KV planning (host arithmetic only, safe during stream capture).
+ * Chooses how many splits each (request, query token) should use so that the
+ * grid fills `num_sms` SMs without excess partial traffic.  The reference's
+ * counterpart is the static one-tile-per-split rule of
+ * hca/sm100/helpers.h:831-869 and hca/sm100/kernel.cu:248-257.
+ *   rows      = B * s_q
+ *   H         = query heads
+ *   max_len   = longest per-row entry count (topk for CSA, kv_len+win_len for HCA)
+ *   num_sms   = 0 -> query the current device
+ * Returns the split count (>= 1, <= DSV4_MAX_SPLITS), or a negative cudaError_t.
+ */
+int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms);
+
+/* Bytes of partial_o + partial_lse a call with these sizes needs (0 when
+ * num_splits == 1).  partial_lse starts at the returned `*lse_offset`. */
+int64_t dsv4_attn_workspace_bytes(int rows, int H, int num_splits, int64_t* lse_offset);
+
+/*
+ * The reference's entry point, kept symbol- and argument-compatible
+ * (hca/sm100/kernel.cu:269-280; ctypes binding in
+ * bench/bench/candidates/hca_custom_decode.py:60-73).  Reference cache layout:
+ * Kc/Kswa uint8(e4m3) [B, M, 448], Kc_s/Kswa_s uint8(UE8M0) [B, M, 7],
+ * Kc_rope/Kswa_rope bf16 [B, M, 64]; Q and O bf16 [B, n_h, 512]; the value
+ * vector is the whole 512-wide row.  partial_O / partial_lse are workspaces
+ * the caller sizes for (M_cur+swa_len)/128 splits; this library uses at most
+ * that many.  Accepts any M_cur+swa_len >= 1 and any n_h >= 1 (a superset of
+ * the reference's shape guard); still requires c == 448 and n_rope == 64.
+ */
+int hca_decode_fwd(const void* Q,
+                   const void* Kc, const void* Kc_s, const void* Kc_rope,
+                   const void* Kswa, const void* Kswa_s, const void* Kswa_rope,
+                   const void* sink_logits,
+                   void* O, void* partial_O, void* partial_lse,
+                   float sm_scale,
+                   int B, int n_h, int c, int n_rope,
+                   int M_cur, int swa_len,
+                   void* stream);
+
+/*
+ * Plain-SIMT validation kernels: the same three operations computed without
+ * tensor cores, one head per thread block.  They exist so that large cases can
+ * be cross-checked on the device; they are slow and are not the product path.
+ * No counterpart in the reference.
+ */
+int dsv4_csa_sparse_decode_simt(const Dsv4CsaSparseDecodeParams* p, void* stream);
+int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream);
+
+/* Library identification: (major << 16) | minor. */
+int dsv4_attn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DSV4_ATTN_H_ */

@@ -1,0 +1,242 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU
+oracle and the committed reference outputs.  Run with `-m gpu` on a B200."""
+import ast
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from oracle import dsv4_oracle as orc  # noqa: E402
+from tests import gpu_util as gu  # noqa: E402
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import dsv4_attn_b200 as d
+    return d
+
+
+def golden(name):
+    z = np.load(GOLD / f"{name}.npz")
+    return z, ast.literal_eval(str(z["kwargs"]))
+
+
+def run_csa(lib, case, **kw):
+    st = lib.new_status("cuda")
+    args = gu.csa_to_dev(case)
+    out, lse = lib.csa_sparse_decode(status=st, **args, **kw)
+    torch.cuda.synchronize()
+    assert st.cpu().tolist() == [0, 0, 0, 0], f"kernel reported a bounded-wait timeout: {st.cpu().tolist()}"
+    return gu.out_to_f32(out), lse.cpu().numpy()
+
+
+def run_hca(lib, case, **kw):
+    st = lib.new_status("cuda")
+    args = gu.hca_to_dev(case)
+    out, lse = lib.hca_dense_decode(status=st, **args, **kw)
+    torch.cuda.synchronize()
+    assert st.cpu().tolist() == [0, 0, 0, 0], f"kernel reported a bounded-wait timeout: {st.cpu().tolist()}"
+    return gu.out_to_f32(out), lse.cpu().numpy()
+
+
+@pytest.mark.parametrize("impl", ["simt", "mma"])
+@pytest.mark.parametrize("name", ["csa_cfg0", "csa_ragged"])
+def test_csa_vs_reference_outputs(lib, name, impl):
+    z, kw = golden(name)
+    case = orc.make_csa_case(**kw)
+    out, lse = run_csa(lib, case, impl=impl, num_splits=1)
+    gu.check_out(out, z["out"], f"{name}/{impl} vs reference")
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices,
+                                               case.sm_scale, kv_len=case.kv_len)
+    gu.check_out(out, want_out, f"{name}/{impl} vs oracle")
+    gu.check_lse(lse, want_lse, f"{name}/{impl}")
+
+
+@pytest.mark.parametrize("impl", ["simt", "mma"])
+@pytest.mark.parametrize("name", ["hca_small", "hca_nosink"])
+def test_hca_vs_reference_outputs(lib, name, impl):
+    z, kw = golden(name)
+    case = orc.make_hca_case(**kw)
+    out, lse = run_hca(lib, case, impl=impl, num_splits=1)
+    gu.check_out(out, z["out"], f"{name}/{impl} vs reference")
+    want_out, want_lse = orc.hca_dense_decode(case.q, case.pool, case.block_table, case.kv_len, case.win,
+                                              case.win_len, case.sm_scale, sink=case.sink)
+    gu.check_out(out, want_out, f"{name}/{impl} vs oracle")
+    gu.check_lse(lse, want_lse, f"{name}/{impl}")
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_csa_split_kv(lib, splits):
+    case = orc.make_csa_case(seed=11, B=3, s_q=2, H=32, n_entries=[700, 1500, 90], topk=512, ragged=True)
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices,
+                                               case.sm_scale, kv_len=case.kv_len)
+    out, lse = run_csa(lib, case, num_splits=splits)
+    gu.check_out(out, want_out, f"csa splits={splits}")
+    gu.check_lse(lse, want_lse, f"csa splits={splits}")
+
+
+@pytest.mark.parametrize("splits", [2, 5])
+def test_hca_split_kv_with_sink(lib, splits):
+    case = orc.make_hca_case(seed=12, B=2, s_q=2, H=128, kv_len=[782, 333], win_len=[128, 40], with_sink=True)
+    want_out, want_lse = orc.hca_dense_decode(case.q, case.pool, case.block_table, case.kv_len, case.win,
+                                              case.win_len, case.sm_scale, sink=case.sink)
+    out, lse = run_hca(lib, case, num_splits=splits)
+    gu.check_out(out, want_out, f"hca splits={splits}")
+    gu.check_lse(lse, want_lse, f"hca splits={splits}")
+
+
+def test_csa_h128_paged_like_config1(lib):
+    """Config-1 shape at a reduced batch: H=128, 768 entries in 64-entry pages
+    behind a random block table, top-k 512, no split."""
+    case = orc.make_csa_case(seed=13, B=4, s_q=1, H=128, n_entries=768, topk=512)
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale)
+    out, lse = run_csa(lib, case, num_splits=1)
+    e = gu.check_out(out, want_out, "csa H=128")
+    gu.check_lse(lse, want_lse, "csa H=128")
+    print("csa H=128 max/mean abs err", e)
+
+
+def test_hca_h128_like_config2(lib):
+    case = orc.make_hca_case(seed=14, B=3, s_q=1, H=128, kv_len=782, win_len=128)
+    want_out, want_lse = orc.hca_dense_decode(case.q, case.pool, case.block_table, case.kv_len, case.win,
+                                              case.win_len, case.sm_scale)
+    out, lse = run_hca(lib, case, num_splits=1)
+    e = gu.check_out(out, want_out, "hca H=128")
+    gu.check_lse(lse, want_lse, "hca H=128")
+    print("hca H=128 max/mean abs err", e)
+
+
+def test_padding_anywhere_and_empty_rows(lib):
+    case = orc.make_csa_case(seed=15, B=3, s_q=1, H=16, n_entries=[5, 130, 400], topk=192, ragged=True)
+    case.indices[0, 0, :] = -1                       # nothing visible at all
+    rng = np.random.default_rng(0)
+    case.indices[2, 0] = rng.permutation(case.indices[2, 0])     # padding scattered, not at the tail
+    case.indices[2, 0, ::3] = -1
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices,
+                                               case.sm_scale, kv_len=case.kv_len)
+    for splits in (1, 2):
+        out, lse = run_csa(lib, case, num_splits=splits)
+        gu.check_out(out, want_out, f"padding splits={splits}")
+        gu.check_lse(lse, want_lse, f"padding splits={splits}")
+        assert (out[0] == 0).all() and np.isneginf(lse[0]).all()
+
+
+def test_growing_maximum_rescales_accumulator(lib):
+    """Later tiles carry much larger logits than earlier ones, so the running
+    reference maximum must move and the accumulator in tensor memory must be
+    rescaled several times."""
+    B, H, n = 1, 128, 512
+    rng = np.random.default_rng(21)
+    q = orc.bf16_round(rng.standard_normal((B, 1, H, 576)).astype(np.float32))
+    lat = rng.standard_normal((n, 512)).astype(np.float32)
+    rope = rng.standard_normal((n, 64)).astype(np.float32)
+    grow = (1.0 + 6.0 * (np.arange(n) // 64)).astype(np.float32)[:, None]   # x1 ... x43 per tile
+    lat *= grow
+    rope *= grow
+    pool = orc.pack_entries(lat.reshape(n // 64, 64, 512), rope.reshape(n // 64, 64, 64))
+    bt = np.arange(n // 64, dtype=np.int32)[None]
+    idx = np.arange(n, dtype=np.int32)[None, None]
+    sc = 1 / math.sqrt(576)
+    want_out, want_lse = orc.csa_sparse_decode(q, pool, bt, idx, sc)
+    case = orc.CsaCase(q, pool, bt, idx, np.full((1, 1), n, np.int32), sc)
+    for impl in ("simt", "mma"):
+        out, lse = run_csa(lib, case, impl=impl, num_splits=1)
+        # outputs are O(40) here: compare relative to the value scale
+        scale = np.abs(gu.bits_to_f32(want_out)).max()
+        err = np.abs(out - gu.bits_to_f32(want_out)) / scale
+        assert err.max() < 2e-2, (impl, err.max())
+        gu.check_lse(lse, want_lse, f"growing max {impl}")
+
+
+def test_combine_kernel_vs_oracle(lib):
+    rng = np.random.default_rng(31)
+    S, N, H = 5, 3, 20
+    po = rng.standard_normal((S, N, H, 512)).astype(np.float32)
+    pl = (rng.standard_normal((S, N, H)) * 3).astype(np.float32)
+    pl[1] = -np.inf                      # an empty split
+    pl[:, 2, 7] = -np.inf                # a fully empty (row, head)
+    po[1] = np.nan                       # empty splits may hold anything
+    sink = rng.standard_normal(H).astype(np.float32)
+    for snk in (None, sink):
+        want_out, want_lse = orc.combine(np.nan_to_num(po), pl, snk)
+        out, lse = lib.combine(gu.dev(po), gu.dev(pl), attn_sink=None if snk is None else gu.dev(snk))
+        torch.cuda.synchronize()
+        got = gu.out_to_f32(out)
+        assert np.abs(got - gu.bits_to_f32(want_out)).max() <= 2e-2 * max(1.0, np.abs(gu.bits_to_f32(want_out)).max())
+        gu.check_lse(lse.cpu().numpy(), want_lse, "combine")
+        assert (got[2, 7] == 0).all()
+
+
+@pytest.mark.parametrize("name", ["ref_layout", "ref_layout_ragged"])
+def test_reference_entry_point_on_reference_layout(lib, name):
+    """hca_decode_fwd, the reference's own symbol and cache layout, against the
+    reference's fp8_dequant output with the reference harness's tolerance
+    (bench/bench/decode.py:48-53,328-330) and this library's tighter one."""
+    z, kw = golden(name)
+    c = orc.make_ref_layout_case(**kw)
+    d = gu.dev
+    O = lib.hca_decode_fwd(d(c.Q, torch.bfloat16), d(c.Kc), d(c.Kc_s), d(c.Kc_rope, torch.bfloat16),
+                           d(c.Kswa), d(c.Kswa_s), d(c.Kswa_rope, torch.bfloat16), d(c.sink), c.sm_scale,
+                           M_cur=kw["M_cur"], swa_len=kw["swa_len"])
+    torch.cuda.synchronize()
+    got = gu.out_to_f32(O)
+    want = gu.bits_to_f32(z["out_fp8_dequant"])
+    err = np.abs(got - want)
+    assert err.max() <= 1.5e-2 or (err / np.maximum(np.abs(want), 1e-8)).max() <= 5e-2
+    gu.check_out(got, z["out_fp8_dequant"], name)
+
+
+def test_invalid_arguments_are_rejected(lib):
+    case = orc.make_csa_case(seed=1, B=1, s_q=1, H=4, n_entries=64, topk=64)
+    args = gu.csa_to_dev(case)
+    with pytest.raises(lib.Dsv4Error):
+        lib.csa_sparse_decode(**{**args, "sm_scale": float("nan")})
+    with pytest.raises(ValueError):
+        lib.csa_sparse_decode(**{**args, "q": args["q"].float()})
+    with pytest.raises(ValueError):
+        lib.csa_sparse_decode(**args, num_splits=65)
+    import ctypes as C
+    assert lib.LIB.dsv4_csa_sparse_decode_fwd(None, None) == 1
+    assert lib.LIB.hca_decode_fwd(*([None] * 11), C.c_float(1.0), 1, 128, 512, 64, 128, 0, None) == 1
+    torch.cuda.synchronize()
+
+
+def test_combine_kernel_vs_reference_kernel(lib):
+    """This library's merge against the reference project's own merge kernel
+    (hca/sm100/combine.cu, compiled from the reference sources into
+    oracle/_ref by oracle/build_ref.py) on the same partials: bit-exact LSE
+    pattern and BF16 outputs within one rounding step."""
+    import ctypes as C
+    so = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "libref_combine.so"
+    if not so.exists():
+        pytest.skip("oracle/_ref not built (needs the reference sources)")
+    ref = C.CDLL(str(so))
+    ref.ref_hca_combine.restype = C.c_int
+    ref.ref_hca_combine.argtypes = [C.c_int] * 3 + [C.c_void_p] * 6
+    rng = np.random.default_rng(41)
+    for S, B, H in ((8, 4, 128), (33, 2, 24), (1, 3, 8)):
+        po = gu.dev(rng.standard_normal((S, B, H, 512)).astype(np.float32))
+        pl_np = (rng.standard_normal((S, B, H)) * 4).astype(np.float32)
+        if S > 2:
+            pl_np[2] = -np.inf
+        pl = gu.dev(pl_np)
+        sink = gu.dev(rng.standard_normal(H).astype(np.float32))
+        for snk in (None, sink):
+            out_ref = torch.empty(B, H, 512, dtype=torch.bfloat16, device="cuda")
+            lse_ref = torch.empty(B, H, dtype=torch.float32, device="cuda")
+            rc = ref.ref_hca_combine(B, H, S, po.data_ptr(), pl.data_ptr(), out_ref.data_ptr(), lse_ref.data_ptr(),
+                                     None if snk is None else snk.data_ptr(), None)
+            assert rc == 0
+            out, lse = lib.combine(po, pl, attn_sink=snk)
+            torch.cuda.synchronize()
+            a, b = out.float(), out_ref.float()
+            assert torch.allclose(a, b, rtol=2 ** -7, atol=1e-6), (S, B, H, (a - b).abs().max().item())
+            assert torch.allclose(lse, lse_ref, rtol=1e-5, atol=1e-5)
