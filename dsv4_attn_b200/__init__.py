@@ -1,12 +1,24 @@
 """dsv4_attn_b200: decode attention for DeepSeek-V4-style compressed KV caches
 on NVIDIA B200 (sm_100a).  CSA sparse decode, HCA dense decode, split-KV merge.
 
-Importing the package loads libdsv4_attn.so and fails if it has not been
-built (`python -m dsv4_attn_b200.build`)."""
-from . import layout
-from ._lib import LIB, library_path
-from .api import (Dsv4Error, alloc_workspace, combine, csa_sparse_decode, hca_decode_fwd, hca_dense_decode,
-                  new_status, plan_splits)
+The operators live in libdsv4_attn.so (built by `python -m dsv4_attn_b200.build`).
+The shared object is loaded on first use of any operator or of `LIB`; if it is
+missing or stale that access raises - there is no CPU or PyTorch fallback.
+Importing the bare package stays possible so that the build module can run."""
+from __future__ import annotations
 
-__all__ = ["LIB", "library_path", "layout", "Dsv4Error", "alloc_workspace", "combine", "csa_sparse_decode",
-           "hca_decode_fwd", "hca_dense_decode", "new_status", "plan_splits"]
+import importlib
+
+_API = ("Dsv4Error", "alloc_workspace", "combine", "csa_sparse_decode", "hca_decode_fwd", "hca_dense_decode",
+        "new_status", "plan_splits")
+__all__ = ["LIB", "library_path", "layout", "synth", *_API]
+
+
+def __getattr__(name):
+    if name in _API:
+        return getattr(importlib.import_module(".api", __name__), name)
+    if name in ("LIB", "library_path"):
+        return getattr(importlib.import_module("._lib", __name__), name)
+    if name in ("layout", "synth", "api", "build"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

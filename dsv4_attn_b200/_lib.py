@@ -55,6 +55,11 @@ class CombineParams(C.Structure):
     ]
 
 
+EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt",
+           "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
+           "dsv4_attn_workspace_bytes", "hca_decode_fwd")
+
+
 def _load() -> C.CDLL:
     path = library_path()
     if not path.exists():
@@ -62,6 +67,9 @@ def _load() -> C.CDLL:
             f"{path} not found: build it with `python -m dsv4_attn_b200.build` "
             "(needs nvcc; the library has no CPU or PyTorch fallback)")
     lib = C.CDLL(str(path))
+    missing = [n for n in EXPORTS if not hasattr(lib, n)]
+    if missing:
+        raise LibraryNotBuilt(f"{path} is stale (no symbol {missing[0]}): rebuild with `python -m dsv4_attn_b200.build`")
     P = C.POINTER
     lib.dsv4_attn_version.restype = C.c_int
     lib.dsv4_attn_version.argtypes = []
@@ -73,6 +81,8 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [P(st), C.c_void_p]
+    lib.dsv4_debug_set_trace.restype = None
+    lib.dsv4_debug_set_trace.argtypes = [C.c_void_p]
     lib.dsv4_attn_plan_splits.restype = C.c_int
     lib.dsv4_attn_plan_splits.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
     lib.dsv4_attn_workspace_bytes.restype = C.c_int64

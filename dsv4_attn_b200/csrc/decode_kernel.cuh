@@ -78,6 +78,7 @@ struct DecodeArgs {
     float* partial_o;
     float* partial_lse;
     int32_t* status;
+    unsigned long long* trace;   // optional profiling aid: block (0,0,0) records phase times here
     // reference layout planes (kSrcRef)
     const uint8_t* ref_kc;  const uint8_t* ref_kc_s;  const __nv_bfloat16* ref_kc_rope;
     const uint8_t* ref_ks;  const uint8_t* ref_ks_s;  const __nv_bfloat16* ref_ks_rope;
@@ -116,122 +117,177 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int code, int ro
     }
 }
 
-// FP8 e4m3 x4 (one 32-bit word) times `scale` -> 4 BF16 (two packed words).
-__device__ __forceinline__ void dequant4(uint32_t w, float scale, uint32_t& lo, uint32_t& hi) {
-    __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xFFFFu), __NV_E4M3);
-    __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
-    float2 f01 = __half22float2(*reinterpret_cast<__half2*>(&h01));
-    float2 f23 = __half22float2(*reinterpret_cast<__half2*>(&h23));
-    lo = ptx::pack_bf16x2(f01.x * scale, f01.y * scale);
-    hi = ptx::pack_bf16x2(f23.x * scale, f23.y * scale);
+// Profiling aid: block (0,0,0) stores %globaltimer values, 1024 slots per role
+// (0 softmax, 1 MMA, 2 loader, 3 block phases).
+__device__ __forceinline__ void trace_mark(const DecodeArgs& a, int role, int slot) {
+    if (a.trace != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && slot < 1024)
+        a.trace[role * 1024 + slot] = ptx::globaltimer_ns();
 }
 
-// Registers one loader thread holds for one tile: a quarter of one entry.
+// Two FP8 e4m3 bytes sitting in bits [15:8] and [31:24] of `r` -> two BF16 bit
+// patterns whose values are the FP8 values times 2^-120 (the e4m3 exponent and
+// mantissa bits dropped into the BF16 exponent/mantissa fields; e4m3
+// subnormals become BF16 subnormals, so one multiply fixes both).
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2_bits(uint32_t r) {
+    return (r & 0x80008000u) | ((r >> 4) & 0x07F007F0u);
+}
+
+// Four FP8 e4m3 (one 32-bit word) times the block scale -> 4 BF16 (two packed
+// words).  `scale2` holds scale * 2^120 in both halves; integer ALU plus one
+// packed BF16 multiply per pair (no slow-rate conversion instructions).
+__device__ __forceinline__ void dequant4(uint32_t w, __nv_bfloat162 scale2, uint32_t& lo, uint32_t& hi) {
+    uint32_t r01 = e4m3x2_to_bf16x2_bits(__byte_perm(w, 0u, 0x1404u));
+    uint32_t r23 = e4m3x2_to_bf16x2_bits(__byte_perm(w, 0u, 0x3424u));
+    __nv_bfloat162 a = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&r01), scale2);
+    __nv_bfloat162 b = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&r23), scale2);
+    lo = *reinterpret_cast<uint32_t*>(&a);
+    hi = *reinterpret_cast<uint32_t*>(&b);
+}
+
+// Registers one loader thread holds for one tile.  A loader warp owns 8
+// consecutive entries of the tile; for entry i the 32 lanes read the 512 latent
+// bytes as 32 consecutive 16-byte vectors (one coalesced request per entry).
 template <int SRC>
 struct LoaderRegs {
-    static constexpr int kLatVecs = (SRC == kSrcRef) ? 7 : 8;   // 16-byte vectors of FP8 latent
-    uint4 lat[kLatVecs];
-    uint4 rope[2];
-    float scale;            // packed layout: the FP32 scale of this thread's 128-element block
-    uint32_t sbytes[2];     // reference layout: the 7 UE8M0 bytes of the entry
-    bool valid;
+    uint4 lat[8];        // entry i, latent dims [16*lane, 16*lane + 16)
+    uint32_t sc[8];      // entry i: FP32 scale bits of block lane/8, or the UE8M0 byte of block lane/4
+    uint4 rope[2];       // entry r*4 + lane/8, RoPE 16-byte column lane%8
+    uint32_t vmask;      // bit i = entry i of this warp takes part (same in all lanes)
 };
 
-template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_issue(const DecodeArgs& a, int b, int n, int tile, int t, int j,
-                                             int n_tok, int kv_len_n, LoaderRegs<SRC>& r) {
-    const int v = tile * kTileN + t;      // position in this row's entry sequence
-    const uint8_t* row = nullptr;
-    bool valid = v < n_tok;
+// Where an entry lives: for the packed layouts the address of its 656-byte
+// record; for the reference layout its row number in the plane, with bit 62 set
+// for the sliding-window planes.  Lanes 0..7 of a loader warp resolve the warp's
+// 8 entries one tile ahead of the data loads, so that the index -> block table
+// -> row dependency chain is off the critical path.
+template <int SRC>
+__device__ __forceinline__ unsigned long long loader_resolve(const DecodeArgs& a, int b, int n, int v, int n_tok,
+                                                             int kv_len_n, bool& valid) {
+    valid = v < n_tok;
+    unsigned long long key = 0;
     if constexpr (SRC == kSrcCsa) {
         int e = -1;
         if (valid) e = __ldg(a.indices + int64_t(n) * a.topk + v);
         valid = (e >= 0) && (e < kv_len_n);
         if (valid) {
             const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (e >> 6));
-            row = a.kv_pool + (int64_t(page) * 64 + (e & 63)) * 656;
+            key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (e & 63)) * 656);
         }
     } else if constexpr (SRC == kSrcHca) {
         if (valid) {
             if (v < kv_len_n) {
                 const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (v >> 6));
-                row = a.kv_pool + (int64_t(page) * 64 + (v & 63)) * 656;
+                key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (v & 63)) * 656);
             } else {
-                row = a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656;
+                key = reinterpret_cast<unsigned long long>(a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656);
             }
-        }
-    }
-    r.valid = valid;
-    if constexpr (SRC != kSrcRef) {
-        if (valid) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) r.lat[i] = ptx::ldg_nc_v4(row + j * 128 + i * 16);
-            r.scale = __ldg(reinterpret_cast<const float*>(row + 512) + j);
-            r.rope[0] = ptx::ldg_nc_v4(row + 528 + (2 * j) * 16);
-            r.rope[1] = ptx::ldg_nc_v4(row + 528 + (2 * j + 1) * 16);
         }
     } else {
         if (valid) {
-            const uint8_t* lat;  const uint8_t* sc;  const __nv_bfloat16* rp;
-            if (v < a.ref_m_cur) {
-                const int64_t e = int64_t(b) * a.ref_m_cur + v;
-                lat = a.ref_kc + e * 448;  sc = a.ref_kc_s + e * 7;  rp = a.ref_kc_rope + e * 64;
+            key = (v < a.ref_m_cur) ? (unsigned long long)(int64_t(b) * a.ref_m_cur + v)
+                                    : ((unsigned long long)(int64_t(b) * a.ref_swa_len + (v - a.ref_m_cur)) | (1ull << 62));
+        }
+    }
+    return key;
+}
+
+// Warp-wide: resolve the 8 entries [v0, v0+8) (lanes 0..7), return the key in
+// those lanes and the valid mask in all lanes.
+template <int SRC>
+__device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeArgs& a, int b, int n, int v0, int lane,
+                                                                  int n_tok, int kv_len_n, uint32_t& vmask) {
+    bool valid = false;
+    unsigned long long key = 0;
+    if (lane < 8) key = loader_resolve<SRC>(a, b, n, v0 + lane, n_tok, kv_len_n, valid);
+    vmask = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
+    return key;
+}
+
+template <int SRC>
+__device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
+                                             LoaderRegs<SRC>& r) {
+    r.vmask = vmask;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+        if ((vmask >> i) & 1u) {
+            if constexpr (SRC != kSrcRef) {
+                const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
+                r.lat[i] = ptx::ldg_nc_v4(row + lane * 16);
+                r.sc[i] = __ldg(reinterpret_cast<const uint32_t*>(row + 512) + (lane >> 3));
             } else {
-                const int64_t e = int64_t(b) * a.ref_swa_len + (v - a.ref_m_cur);
-                lat = a.ref_ks + e * 448;  sc = a.ref_ks_s + e * 7;  rp = a.ref_ks_rope + e * 64;
+                const bool swa = (k >> 62) & 1ull;
+                const int64_t e = int64_t(k & ~(1ull << 62));
+                const uint8_t* lat = (swa ? a.ref_ks : a.ref_kc) + e * 448;
+                const uint8_t* sc = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
+                if (lane < 28) {
+                    r.lat[i] = ptx::ldg_nc_v4(lat + lane * 16);
+                    r.sc[i] = __ldg(sc + (lane >> 2));
+                }
             }
+        }
+    }
 #pragma unroll
-            for (int i = 0; i < 7; ++i) r.lat[i] = ptx::ldg_nc_v4(lat + j * 112 + i * 16);
-            uint32_t s0 = 0, s1 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s0 |= uint32_t(__ldg(sc + i)) << (8 * i);
-#pragma unroll
-            for (int i = 0; i < 3; ++i) s1 |= uint32_t(__ldg(sc + 4 + i)) << (8 * i);
-            r.sbytes[0] = s0;  r.sbytes[1] = s1;
-            r.rope[0] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(rp) + (2 * j) * 16);
-            r.rope[1] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(rp) + (2 * j + 1) * 16);
+    for (int rr = 0; rr < 2; ++rr) {
+        const int i = rr * 4 + (lane >> 3);
+        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+        if ((vmask >> i) & 1u) {
+            if constexpr (SRC != kSrcRef) {
+                r.rope[rr] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(k) + 528 + (lane & 7) * 16);
+            } else {
+                const bool swa = (k >> 62) & 1ull;
+                const int64_t e = int64_t(k & ~(1ull << 62));
+                const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
+                r.rope[rr] = ptx::ldg_nc_v4(rp + (lane & 7) * 16);
+            }
         }
     }
 }
 
-// Write this thread's quarter entry into the KV tile: row t of each 64-column
-// chunk is 128 bytes; 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
+// Dequantise and write this warp's 8 entries (tile rows t0..t0+7) into the KV
+// tile.  Row t of each 64-column chunk is 128 bytes; 16-byte column c16 of row
+// t lives at ((c16 ^ (t & 7)) << 4).  Lanes of odd chunks write their two
+// columns in the opposite order so that one store instruction covers all eight
+// column positions (no more shared-memory wavefronts than the data needs).
 template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store(uint32_t kv_base, int t, int j, const LoaderRegs<SRC>& r) {
-    const uint32_t row_off = uint32_t(t) * 128u;
-    const uint32_t sw = uint32_t(t & 7);
-    constexpr int kLatVecs = LoaderRegs<SRC>::kLatVecs;
-    const int d0 = j * kLatVecs * 16;     // first latent dim of this thread
+__device__ __forceinline__ void loader_store(uint32_t kv_base, int t0, int lane, const LoaderRegs<SRC>& r) {
+    constexpr int kLatLanes = (SRC == kSrcRef) ? 28 : 32;
+    const uint32_t chunk = uint32_t(lane >> 2);
+    const uint32_t c16 = uint32_t(lane & 3) * 2u;
+    const uint32_t flip = chunk & 1u;
 #pragma unroll
-    for (int i = 0; i < kLatVecs; ++i) {
-        const int d = d0 + i * 16;
+    for (int i = 0; i < 8; ++i) {
+        const int t = t0 + i;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-        if (r.valid) {
-            float scale;
+        if (((r.vmask >> i) & 1u) && lane < kLatLanes) {
+            float s120;
             if constexpr (SRC == kSrcRef) {
-                const int blk = d >> 6;
-                const uint32_t byte = (blk < 4) ? ((r.sbytes[0] >> (8 * blk)) & 0xFFu)
-                                                : ((r.sbytes[1] >> (8 * (blk - 4))) & 0xFFu);
-                scale = __uint_as_float(byte << 23);
+                // 2^(byte-127) * 2^120; a zero byte means a zero scale, as in the reference's dequantiser
+                s120 = (r.sc[i] & 0xFFu) ? __uint_as_float(((r.sc[i] & 0xFFu) + 120u) << 23) : 0.f;
             } else {
-                scale = r.scale;
+                s120 = __uint_as_float(r.sc[i]) * 1.329227995784916e36f;   // 2^120
             }
-            dequant4(r.lat[i].x, scale, w0.x, w0.y);
-            dequant4(r.lat[i].y, scale, w0.z, w0.w);
-            dequant4(r.lat[i].z, scale, w1.x, w1.y);
-            dequant4(r.lat[i].w, scale, w1.z, w1.w);
+            const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
+            dequant4(r.lat[i].x, scale2, w0.x, w0.y);
+            dequant4(r.lat[i].y, scale2, w0.z, w0.w);
+            dequant4(r.lat[i].z, scale2, w1.x, w1.y);
+            dequant4(r.lat[i].w, scale2, w1.z, w1.w);
         }
-        const uint32_t chunk = uint32_t(d >> 6);
-        const uint32_t c16 = uint32_t((d & 63) >> 3);
-        const uint32_t base = kv_base + chunk * kKvChunkBytes + row_off;
-        ptx::sts_v4(base + (((c16) ^ sw) << 4), w0);
-        ptx::sts_v4(base + (((c16 + 1) ^ sw) << 4), w1);
+        if (lane < kLatLanes) {
+            const uint32_t base = kv_base + chunk * kKvChunkBytes + uint32_t(t) * 128u;
+            const uint32_t sw = uint32_t(t & 7);
+            const uint32_t ca = (c16 + flip) ^ sw, cb = (c16 + (flip ^ 1u)) ^ sw;
+            ptx::sts_v4(base + (ca << 4), flip ? w1 : w0);
+            ptx::sts_v4(base + (cb << 4), flip ? w0 : w1);
+        }
     }
-    {
-        const uint32_t base = kv_base + uint32_t(NCHUNK - 1) * kKvChunkBytes + row_off;
-        uint4 z = make_uint4(0, 0, 0, 0);
-        ptx::sts_v4(base + ((uint32_t(2 * j) ^ sw) << 4), r.valid ? r.rope[0] : z);
-        ptx::sts_v4(base + ((uint32_t(2 * j + 1) ^ sw) << 4), r.valid ? r.rope[1] : z);
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int i = rr * 4 + (lane >> 3);
+        const int t = t0 + i;
+        const uint32_t base = kv_base + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        ptx::sts_v4(base + (((uint32_t(lane) & 7u) ^ uint32_t(t & 7)) << 4), ((r.vmask >> i) & 1u) ? r.rope[rr] : z);
     }
 }
 
@@ -285,6 +341,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
 
     // ── set-up ──
     if (tid == 0) {
+        trace_mark(a, 3, 0);
         ptx::mbar_init(bar_kv_full, kNumLoaderWarps);
         ptx::mbar_init(bar_kv_free, 1);
         ptx::mbar_init(bar_s_full, 1);
@@ -296,18 +353,45 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
         ptx::tmem_relinquish();
     }
+    // Loader warps put the first tile's loads in flight before anything else.
+    LoaderRegs<SRC> regs;
+    unsigned long long next_key = 0;
+    uint32_t next_vmask = 0;
+    if (ntiles > 0 && warp >= kFirstLoaderWarp) {
+        const int lw = warp - kFirstLoaderWarp;
+        uint32_t vm;
+        const unsigned long long key0 = loader_resolve_warp<SRC>(a, b, n, tile0 * kTileN + lw * 8, lane, n_tok, kv_len_n, vm);
+        loader_fetch<SRC>(a, key0, vm, lane, regs);
+        next_key = loader_resolve_warp<SRC>(a, b, n, (tile0 + 1) * kTileN + lw * 8, lane,
+                                            (ntiles > 1) ? n_tok : 0, kv_len_n, next_vmask);
+    }
     // Q tile: [128 heads x NCHUNK*64] bf16 -> NCHUNK swizzled chunks; rows >= H are zero.
     if (ntiles > 0) {
         constexpr int kVecsPerRow = NCHUNK * 8;
         const __nv_bfloat16* qrow0 = a.q + int64_t(n) * a.H * (NCHUNK * 64);
-        for (int v = tid; v < kHeadsPerCta * kVecsPerRow; v += kNumThreads) {
-            const int r = v / kVecsPerRow;
-            const int cv = v - r * kVecsPerRow;
-            const int h = hg * kHeadsPerCta + r;
-            uint4 w = make_uint4(0, 0, 0, 0);
-            if (h < a.H) w = ptx::ldg_nc_v4(qrow0 + int64_t(h) * (NCHUNK * 64) + cv * 8);
-            const uint32_t c = uint32_t(cv >> 3), c16 = uint32_t(cv & 7);
-            ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ uint32_t(r & 7)) << 4), w);
+        constexpr int kTotalVecs = kHeadsPerCta * kVecsPerRow;
+        constexpr int kBatch = 8;             // loads in flight per thread
+        for (int v0 = tid; v0 < kTotalVecs; v0 += kNumThreads * kBatch) {
+            uint4 w[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int v = v0 + u * kNumThreads;
+                const int r = v / kVecsPerRow;
+                const int cv = v - r * kVecsPerRow;
+                const int h = hg * kHeadsPerCta + r;
+                w[u] = make_uint4(0, 0, 0, 0);
+                if (v < kTotalVecs && h < a.H) w[u] = ptx::ldg_nc_v4(qrow0 + int64_t(h) * (NCHUNK * 64) + cv * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int v = v0 + u * kNumThreads;
+                if (v < kTotalVecs) {
+                    const int r = v / kVecsPerRow;
+                    const int cv = v - r * kVecsPerRow;
+                    const uint32_t c = uint32_t(cv >> 3), c16 = uint32_t(cv & 7);
+                    ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ uint32_t(r & 7)) << 4), w[u]);
+                }
+            }
         }
         ptx::fence_proxy_async_smem();
     }
@@ -315,16 +399,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = misc->tmem_base;
+    if (tid == 0) trace_mark(a, 3, 1);
 
     if (ntiles > 0) {
         if (warp >= kFirstLoaderWarp) {
             // ───────────── loader warps ─────────────
-            const int ltid = tid - kFirstLoaderWarp * 32;
-            const int t = ltid >> 2;       // entry of the tile
-            const int j = ltid & 3;        // quarter of the entry
-            const int lw = warp - kFirstLoaderWarp;
-            LoaderRegs<SRC> regs;
-            loader_issue<NCHUNK, SRC>(a, b, n, tile0, t, j, n_tok, kv_len_n, regs);
+            const int lw = warp - kFirstLoaderWarp;      // this warp's 8 entries: tile rows lw*8 .. lw*8+7
             for (int it = 0; it < ntiles; ++it) {
                 if (it > 0) {
                     // warp-uniform outcome: the warp-collective operations below need all lanes
@@ -334,19 +414,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         break;
                     }
                 }
-                loader_store<NCHUNK, SRC>(kv_base, t, j, regs);
-                const uint32_t bal = __ballot_sync(0xFFFFFFFFu, regs.valid);
-                if (lane == 0) {
-                    uint32_t m = 0;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) m |= ((bal >> (4 * i)) & 1u) << i;
-                    reinterpret_cast<volatile uint8_t*>(&misc->valid_mask)[lw] = uint8_t(m);
-                }
+                if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it);
+                loader_store<NCHUNK, SRC>(kv_base, lw * 8, lane, regs);
+                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask)[lw] = uint8_t(regs.vmask);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_kv_full);
-                if (it + 1 < ntiles)
-                    loader_issue<NCHUNK, SRC>(a, b, n, tile0 + it + 1, t, j, n_tok, kv_len_n, regs);
+                if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
+                if (it + 1 < ntiles) {
+                    // data of the next tile: in flight during this tile's MMAs
+                    loader_fetch<SRC>(a, next_key, next_vmask, lane, regs);
+                    next_key = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 2) * kTileN + lw * 8, lane,
+                                                        (it + 2 < ntiles) ? n_tok : 0, kv_len_n, next_vmask);
+                }
             }
         } else if (warp == kMmaWarp) {
             // ───────────── MMA issue (one thread) ─────────────
@@ -360,6 +440,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         ok = false;  break;
                     }
                     ptx::tc_fence_after_sync();
+                    trace_mark(a, 1, 2 * it);
 #pragma unroll
                     for (int c = 0; c < NCHUNK; ++c) {
 #pragma unroll
@@ -375,6 +456,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         ok = false;  break;
                     }
                     ptx::tc_fence_after_sync();
+                    trace_mark(a, 1, 2 * it + 1);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         // A = P rows (K-major, 16 entries = 32 bytes per step);
@@ -405,6 +487,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                 }
                 ptx::tc_fence_after_sync();
+                if (tid == 0) trace_mark(a, 0, 2 * it);
                 uint32_t s0[32], s1[32];
                 ptx::tmem_ld32(tmem + lane_addr + kTmemS, s0);
                 ptx::tmem_ld32(tmem + lane_addr + kTmemS + 32, s1);
@@ -471,6 +554,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_p_full);
+                if (tid == 0) trace_mark(a, 0, 2 * it + 1);
             }
             // ── epilogue ──
             if (ok) {
@@ -482,6 +566,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             }
             if (ok) {
                 ptx::tc_fence_after_sync();
+                if (tid == 0) trace_mark(a, 3, 2);
                 const int h = hg * kHeadsPerCta + r;
                 const bool write = h < a.H;
                 const bool final_out = a.num_splits == 1;
@@ -563,6 +648,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     // ── common exit: every thread gets here, with or without an error ──
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (tid == 0) trace_mark(a, 3, 3);
     if (warp == kMmaWarp) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, kTmemCols);

@@ -185,6 +185,15 @@ int hca_decode_fwd(const void* Q,
 int dsv4_csa_sparse_decode_simt(const Dsv4CsaSparseDecodeParams* p, void* stream);
 int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream);
 
+/*
+ * Profiling aid.  While a non-NULL device buffer of 4 x 1024 uint64 is set,
+ * thread block (0,0,0) of every decode launch stores %globaltimer values of
+ * its pipeline phases there (role 0 softmax, 1 MMA issue, 2 loader, 3 block
+ * phases; two slots per tile).  Process-wide, not thread-safe; pass NULL to
+ * switch it off.  No counterpart in the reference.
+ */
+void dsv4_debug_set_trace(void* device_buffer);
+
 /* Library identification: (major << 16) | minor. */
 int dsv4_attn_version(void);
 

@@ -12,7 +12,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def declared_functions():
     text = (ROOT / "include" / "dsv4_attn.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"^\s*(?:int64_t|int)\s+(\w+)\s*\(", text, flags=re.M)))
+    return sorted(set(re.findall(r"^\s*(?:int64_t|int|void)\s+(\w+)\s*\(", text, flags=re.M)))
 
 
 def test_header_declares_expected_surface():
