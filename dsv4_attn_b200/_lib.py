@@ -55,7 +55,7 @@ class CombineParams(C.Structure):
     ]
 
 
-EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt",
+EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
            "dsv4_attn_workspace_bytes", "hca_decode_fwd")
 
@@ -81,6 +81,8 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [P(st), C.c_void_p]
+    lib.dsv4_debug_set_flags.restype = None
+    lib.dsv4_debug_set_flags.argtypes = [C.c_int]
     lib.dsv4_debug_set_trace.restype = None
     lib.dsv4_debug_set_trace.argtypes = [C.c_void_p]
     lib.dsv4_attn_plan_splits.restype = C.c_int

@@ -19,6 +19,7 @@ constexpr int kMaxDevices = 64;
 // Profiling aid (see dsv4_debug_set_trace): device buffer that block (0,0,0) of
 // the next decode launches writes phase timestamps to.  Null in normal use.
 unsigned long long* g_trace = nullptr;
+int g_dbg = 0;
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -109,7 +110,7 @@ bool fill_csa(const Dsv4CsaSparseDecodeParams* p, DecodeArgs& a) {
     a.attn_sink = p->attn_sink;
     a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
-    a.trace = g_trace;
+    a.trace = g_trace;  a.dbg = g_dbg;
     return true;
 }
 
@@ -133,7 +134,7 @@ bool fill_hca(const Dsv4HcaDenseDecodeParams* p, DecodeArgs& a) {
     a.attn_sink = p->attn_sink;
     a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
-    a.trace = g_trace;
+    a.trace = g_trace;  a.dbg = g_dbg;
     return true;
 }
 
@@ -156,6 +157,8 @@ int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
 using namespace dsv4;
 
 extern "C" int dsv4_attn_version(void) { return (0 << 16) | 1; }
+
+extern "C" void dsv4_debug_set_flags(int flags) { g_dbg = flags; }
 
 extern "C" void dsv4_debug_set_trace(void* device_buffer) {
     g_trace = static_cast<unsigned long long*>(device_buffer);
@@ -276,7 +279,7 @@ extern "C" int hca_decode_fwd(const void* Q,
     a.ref_ks = static_cast<const uint8_t*>(Kswa);  a.ref_ks_s = static_cast<const uint8_t*>(Kswa_s);
     a.ref_ks_rope = static_cast<const __nv_bfloat16*>(Kswa_rope);
     a.ref_m_cur = M_cur;  a.ref_swa_len = swa_len;
-    a.trace = g_trace;
+    a.trace = g_trace;  a.dbg = g_dbg;
     // The caller sizes the workspaces for (M_cur + swa_len) / 128 splits; never use more.
     const int caller_splits = (M_cur + swa_len) / 128;
     int splits = dsv4_attn_plan_splits(B, n_h, M_cur + swa_len, 0);

@@ -22,6 +22,7 @@
 #include <cuda_fp8.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <type_traits>
 
 #include "ptx.cuh"
 
@@ -32,14 +33,27 @@ constexpr int kHeadsPerCta = 128;      // MMA M
 constexpr int kDvHalf = 256;           // value columns per block (MMA N of PV)
 constexpr int kQChunkBytes = 128 * 128;   // 128 heads x 64 bf16
 constexpr int kKvChunkBytes = kTileN * 128;  // 64 entries x 64 bf16
+// Warp roles, four warpgroups of four warps.  Warps 0-3: softmax + epilogue.
+// Warps 4-11: loaders.  Warp 12: MMA issue and tensor-memory allocation; warps
+// 13-15 only take part in the block-wide barriers.  All 16 warps start with 128
+// registers (the whole register file); the last warpgroup gives most of its
+// share back and the loaders take it, so that they can hold two tiles of cache
+// entries in flight.  setmaxnreg.inc waits for registers without a time limit,
+// so the matching .dec must be reached unconditionally, as it is here.
 constexpr int kNumSoftmaxWarps = 4;
-constexpr int kMmaWarp = 4;
 constexpr int kNumLoaderWarps = 8;
-constexpr int kFirstLoaderWarp = 5;
-constexpr int kNumThreads = (kNumSoftmaxWarps + 1 + kNumLoaderWarps) * 32;  // 416
+constexpr int kFirstLoaderWarp = 4;
+constexpr int kMmaWarp = 12;
+constexpr int kNumWarps = 16;
+constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // threads that stage Q
+constexpr int kLoaderRegs = 168;       // 8 x 32 x (168-128) = 10240 registers taken ...
+constexpr int kIdleRegs = 48;          // ... from 4 x 32 x (128-48) = 10240 released
+constexpr int kNumThreads = kNumWarps * 32;  // 512
+constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
-constexpr int kTmemS = 0;              // S accumulator: 64 columns
-constexpr int kTmemO = 256;            // O accumulator: 256 columns
+constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P (BF16) overwrites the first 32 of its S
+constexpr int kTmemO = 128;            // O accumulator: 256 columns
+constexpr int kTmemQ = 384;            // Q chunks 0..3 as packed BF16: 4 x 32 columns
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; O is rescaled only when the max grows by more
 
@@ -78,6 +92,7 @@ struct DecodeArgs {
     float* partial_o;
     float* partial_lse;
     int32_t* status;
+    int dbg;                     // profiling aid: bit1 no L2 prefetch
     unsigned long long* trace;   // optional profiling aid: block (0,0,0) records phase times here
     // reference layout planes (kSrcRef)
     const uint8_t* ref_kc;  const uint8_t* ref_kc_s;  const __nv_bfloat16* ref_kc_rope;
@@ -87,22 +102,26 @@ struct DecodeArgs {
 
 template <int NCHUNK>
 struct SmemLayout {
-    static constexpr int kQBytes = NCHUNK * kQChunkBytes;
-    static constexpr int kKvBytes = NCHUNK * kKvChunkBytes;
+    static constexpr int kQSmemChunks = NCHUNK - kQTmemChunks;      // Q chunks kept in shared memory
+    static constexpr int kQBytes = kQSmemChunks * kQChunkBytes;
+    static constexpr int kKvStageBytes = NCHUNK * kKvChunkBytes;
     static constexpr int kQOff = 0;
-    static constexpr int kKvOff = kQBytes;
-    static constexpr int kMiscOff = kQBytes + kKvBytes;
+    static constexpr int kKvOff = kQBytes;                          // two stages
+    static constexpr int kMiscOff = kKvOff + 2 * kKvStageBytes;
     static constexpr int kMiscBytes = 256;
-    static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;  // + slack to align the base to 1024
+    static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;     // + slack to align the base to 1024
+    // the Q chunks bound for tensor memory are staged in the (still unused) KV stages
+    static constexpr int kQStageRowBytes = kQTmemChunks * 128;      // 512
+    static_assert(kHeadsPerCta * kQStageRowBytes <= 2 * kKvStageBytes, "Q staging must fit in the KV stages");
 };
 
 struct SmemMisc {
-    uint64_t bar_kv_full;
-    uint64_t bar_kv_free;
-    uint64_t bar_s_full;
-    uint64_t bar_p_full;
+    uint64_t bar_kv_full[2];
+    uint64_t bar_kv_free[2];
+    uint64_t bar_s_full[2];
+    uint64_t bar_p_full[2];
     uint64_t bar_o_full;
-    uint64_t valid_mask;      // bit t = entry t of the current tile takes part in the softmax
+    uint64_t valid_mask[2];   // per stage: bit t = entry t of the tile takes part in the softmax
     uint32_t tmem_base;
     uint32_t pad;
 };
@@ -203,43 +222,68 @@ __device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeAr
     return key;
 }
 
+// Loads of entry i of the warp (key held by lane i): its latent vector and scale.
+template <int SRC>
+__device__ __forceinline__ void loader_fetch_entry(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
+                                                   int i, uint4& lat, uint32_t& sc) {
+    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+    if ((vmask >> i) & 1u) {
+        if constexpr (SRC != kSrcRef) {
+            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
+            lat = ptx::ldg_nc_v4(row + lane * 16);
+            sc = __ldg(reinterpret_cast<const uint32_t*>(row + 512) + (lane >> 3));
+        } else {
+            const bool swa = (k >> 62) & 1ull;
+            const int64_t e = int64_t(k & ~(1ull << 62));
+            const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
+            const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
+            if (lane < 28) {
+                lat = ptx::ldg_nc_v4(lp + lane * 16);
+                sc = __ldg(sp + (lane >> 2));
+            }
+        }
+    }
+}
+
+// Loads of the RoPE tails of entries rr*4 .. rr*4+3 (lane/8 picks the entry).
+template <int SRC>
+__device__ __forceinline__ void loader_fetch_rope(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
+                                                  int rr, uint4& rope) {
+    const int i = rr * 4 + (lane >> 3);
+    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+    if ((vmask >> i) & 1u) {
+        if constexpr (SRC != kSrcRef) {
+            rope = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(k) + 528 + (lane & 7) * 16);
+        } else {
+            const bool swa = (k >> 62) & 1ull;
+            const int64_t e = int64_t(k & ~(1ull << 62));
+            const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
+            rope = ptx::ldg_nc_v4(rp + (lane & 7) * 16);
+        }
+    }
+}
+
 template <int SRC>
 __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
                                              LoaderRegs<SRC>& r) {
     r.vmask = vmask;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-        if ((vmask >> i) & 1u) {
-            if constexpr (SRC != kSrcRef) {
-                const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
-                r.lat[i] = ptx::ldg_nc_v4(row + lane * 16);
-                r.sc[i] = __ldg(reinterpret_cast<const uint32_t*>(row + 512) + (lane >> 3));
-            } else {
-                const bool swa = (k >> 62) & 1ull;
-                const int64_t e = int64_t(k & ~(1ull << 62));
-                const uint8_t* lat = (swa ? a.ref_ks : a.ref_kc) + e * 448;
-                const uint8_t* sc = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
-                if (lane < 28) {
-                    r.lat[i] = ptx::ldg_nc_v4(lat + lane * 16);
-                    r.sc[i] = __ldg(sc + (lane >> 2));
-                }
-            }
-        }
-    }
+    for (int i = 0; i < 8; ++i) loader_fetch_entry<SRC>(a, key, vmask, lane, i, r.lat[i], r.sc[i]);
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const int i = rr * 4 + (lane >> 3);
+    for (int rr = 0; rr < 2; ++rr) loader_fetch_rope<SRC>(a, key, vmask, lane, rr, r.rope[rr]);
+}
+
+// Pull the 656-byte records of the warp's 8 entries (keys in lanes 0..7) into L2
+// ahead of the loads: lane/4 picks the entry, lane%4 the 128-byte piece.
+template <int SRC>
+__device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint32_t vmask, int lane) {
+    if constexpr (SRC != kSrcRef) {
+        const int i = lane >> 2;
         const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
         if ((vmask >> i) & 1u) {
-            if constexpr (SRC != kSrcRef) {
-                r.rope[rr] = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(k) + 528 + (lane & 7) * 16);
-            } else {
-                const bool swa = (k >> 62) & 1ull;
-                const int64_t e = int64_t(k & ~(1ull << 62));
-                const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
-                r.rope[rr] = ptx::ldg_nc_v4(rp + (lane & 7) * 16);
-            }
+            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
+            ptx::prefetch_l2(row + (lane & 3) * 128);
+            if ((lane & 3) < 2) ptx::prefetch_l2(row + 512 + (lane & 3) * 128);
         }
     }
 }
@@ -255,11 +299,12 @@ __device__ __forceinline__ void loader_store(uint32_t kv_base, int t0, int lane,
     const uint32_t chunk = uint32_t(lane >> 2);
     const uint32_t c16 = uint32_t(lane & 3) * 2u;
     const uint32_t flip = chunk & 1u;
+    const uint32_t vmask = r.vmask;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int t = t0 + i;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-        if (((r.vmask >> i) & 1u) && lane < kLatLanes) {
+        if (((vmask >> i) & 1u) && lane < kLatLanes) {
             float s120;
             if constexpr (SRC == kSrcRef) {
                 // 2^(byte-127) * 2^120; a zero byte means a zero scale, as in the reference's dequantiser
@@ -287,7 +332,7 @@ __device__ __forceinline__ void loader_store(uint32_t kv_base, int t0, int lane,
         const int t = t0 + i;
         const uint32_t base = kv_base + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
         const uint4 z = make_uint4(0, 0, 0, 0);
-        ptx::sts_v4(base + (((uint32_t(lane) & 7u) ^ uint32_t(t & 7)) << 4), ((r.vmask >> i) & 1u) ? r.rope[rr] : z);
+        ptx::sts_v4(base + (((uint32_t(lane) & 7u) ^ uint32_t(t & 7)) << 4), ((vmask >> i) & 1u) ? r.rope[rr] : z);
     }
 }
 
@@ -328,54 +373,42 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     const int tile1 = min(tile0 + tiles_per_split, tiles_total);
     const int ntiles = tile1 - tile0;
 
-    // P (128 x 64 bf16, K-major) overlays two KV chunks that are dead once S is
-    // complete: chunks outside this block's value half.
-    const uint32_t p_base = kv_base + uint32_t(half ? 0 : 4) * kKvChunkBytes;
-    const uint32_t v_base = kv_base + uint32_t(half ? 4 : 0) * kKvChunkBytes;
+    const uint32_t v_off = uint32_t(half ? 4 : 0) * kKvChunkBytes;   // this block's value columns inside a stage
 
-    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full);
-    const uint32_t bar_kv_free = ptx::smem_u32(&misc->bar_kv_free);
-    const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full);
-    const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full);
+    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full[0]);   // [stage] at +8*stage
+    const uint32_t bar_kv_free = ptx::smem_u32(&misc->bar_kv_free[0]);
+    const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full[0]);
+    const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full[0]);
     const uint32_t bar_o_full = ptx::smem_u32(&misc->bar_o_full);
 
     // ── set-up ──
     if (tid == 0) {
         trace_mark(a, 3, 0);
-        ptx::mbar_init(bar_kv_full, kNumLoaderWarps);
-        ptx::mbar_init(bar_kv_free, 1);
-        ptx::mbar_init(bar_s_full, 1);
-        ptx::mbar_init(bar_p_full, kNumSoftmaxWarps);
+        for (int st = 0; st < 2; ++st) {
+            ptx::mbar_init(bar_kv_full + 8 * st, kNumLoaderWarps);
+            ptx::mbar_init(bar_kv_free + 8 * st, 1);
+            ptx::mbar_init(bar_s_full + 8 * st, 1);
+            ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
+        }
         ptx::mbar_init(bar_o_full, 1);
         ptx::fence_mbar_init();
     }
-    if (warp == kMmaWarp) {
-        ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
-        ptx::tmem_relinquish();
-    }
-    // Loader warps put the first tile's loads in flight before anything else.
-    LoaderRegs<SRC> regs;
-    unsigned long long next_key = 0;
-    uint32_t next_vmask = 0;
-    if (ntiles > 0 && warp >= kFirstLoaderWarp) {
-        const int lw = warp - kFirstLoaderWarp;
-        uint32_t vm;
-        const unsigned long long key0 = loader_resolve_warp<SRC>(a, b, n, tile0 * kTileN + lw * 8, lane, n_tok, kv_len_n, vm);
-        loader_fetch<SRC>(a, key0, vm, lane, regs);
-        next_key = loader_resolve_warp<SRC>(a, b, n, (tile0 + 1) * kTileN + lw * 8, lane,
-                                            (ntiles > 1) ? n_tok : 0, kv_len_n, next_vmask);
-    }
-    // Q tile: [128 heads x NCHUNK*64] bf16 -> NCHUNK swizzled chunks; rows >= H are zero.
-    if (ntiles > 0) {
+
+    // This thread's share of staging the Q tile [128 heads x NCHUNK*64] bf16 (rows >= H
+    // zero).  Chunks >= kQTmemChunks go to shared memory in the swizzled operand layout;
+    // the others are staged row-major (512 bytes per head, 16-byte columns XOR-ed with
+    // row % 8) in the still unused KV stages for the copy to tensor memory.
+    auto stage_q = [&]() {
+        if (ntiles <= 0) return;
         constexpr int kVecsPerRow = NCHUNK * 8;
         const __nv_bfloat16* qrow0 = a.q + int64_t(n) * a.H * (NCHUNK * 64);
         constexpr int kTotalVecs = kHeadsPerCta * kVecsPerRow;
         constexpr int kBatch = 8;             // loads in flight per thread
-        for (int v0 = tid; v0 < kTotalVecs; v0 += kNumThreads * kBatch) {
+        for (int v0 = tid; v0 < kTotalVecs; v0 += kStageThreads * kBatch) {
             uint4 w[kBatch];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const int v = v0 + u * kNumThreads;
+                const int v = v0 + u * kStageThreads;
                 const int r = v / kVecsPerRow;
                 const int cv = v - r * kVecsPerRow;
                 const int h = hg * kHeadsPerCta + r;
@@ -384,103 +417,250 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const int v = v0 + u * kNumThreads;
+                const int v = v0 + u * kStageThreads;
                 if (v < kTotalVecs) {
                     const int r = v / kVecsPerRow;
                     const int cv = v - r * kVecsPerRow;
-                    const uint32_t c = uint32_t(cv >> 3), c16 = uint32_t(cv & 7);
-                    ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ uint32_t(r & 7)) << 4), w[u]);
+                    const uint32_t sw = uint32_t(r & 7);
+                    if (cv < kQTmemChunks * 8) {
+                        ptx::sts_v4(kv_base + uint32_t(r) * L::kQStageRowBytes + ((uint32_t(cv) ^ sw) << 4), w[u]);
+                    } else {
+                        const uint32_t c = uint32_t(cv >> 3) - kQTmemChunks, c16 = uint32_t(cv & 7);
+                        ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ sw) << 4), w[u]);
+                    }
                 }
             }
         }
         ptx::fence_proxy_async_smem();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem = misc->tmem_base;
-    if (tid == 0) trace_mark(a, 3, 1);
+    };
+    // Block-wide rendezvous.  Every role runs the same number of them (two before the
+    // main loops, one at the exit), each from its own branch.
+    auto block_sync = [&]() {
+        ptx::tc_fence_before_sync();
+        __syncthreads();
+        ptx::tc_fence_after_sync();
+    };
 
-    if (ntiles > 0) {
-        if (warp >= kFirstLoaderWarp) {
-            // ───────────── loader warps ─────────────
-            const int lw = warp - kFirstLoaderWarp;      // this warp's 8 entries: tile rows lw*8 .. lw*8+7
-            for (int it = 0; it < ntiles; ++it) {
-                if (it > 0) {
+    if (warp >= kFirstLoaderWarp && warp < kMmaWarp) {
+        // ───────────── loader warps ─────────────
+        // Two register sets, one per KV stage: while one tile is dequantised and stored, the
+        // loads of the next one are in flight.  Keys run two tiles ahead of the loads, and the
+        // records they name are pulled into L2 at that point.  The larger register allowance
+        // holds for this branch only.
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kLoaderRegs));
+        const int lw = warp - kFirstLoaderWarp;      // this warp's 8 entries: tile rows lw*8 .. lw*8+7
+        LoaderRegs<SRC> regs_a, regs_b;
+        // keys of the tiles two and three ahead of the one being stored (records already
+        // pulled into L2), and of the tile four ahead (resolved, not yet prefetched)
+        unsigned long long key2 = 0, key3 = 0, key4 = 0;
+        uint32_t vm2 = 0, vm3 = 0, vm4 = 0;
+        if (ntiles > 0) {
+            // one round of dependent loads for the first four tiles: lanes 0-7, 8-15, 16-23, 24-31
+            bool valid = false;
+            const int which = lane >> 3;
+            const unsigned long long key = loader_resolve<SRC>(a, b, n, (tile0 + which) * kTileN + lw * 8 + (lane & 7),
+                                                               (which < ntiles) ? n_tok : 0, kv_len_n, valid);
+            const uint32_t bal = __ballot_sync(0xFFFFFFFFu, valid);
+            vm2 = (bal >> 16) & 0xFFu;
+            vm3 = (bal >> 24) & 0xFFu;
+            const unsigned long long key1 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 8);   // -> lanes 0..7
+            key2 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 16);
+            key3 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 24);
+            loader_fetch<SRC>(a, key, bal & 0xFFu, lane, regs_a);
+            loader_fetch<SRC>(a, key1, (bal >> 8) & 0xFFu, lane, regs_b);
+            loader_prefetch_l2<SRC>(key2, vm2, lane);
+            loader_prefetch_l2<SRC>(key3, vm3, lane);
+            key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + 4) * kTileN + lw * 8, lane, (4 < ntiles) ? n_tok : 0,
+                                            kv_len_n, vm4);
+        }
+        stage_q();
+        block_sync();
+        block_sync();          // Q is in tensor memory; the staging area (KV stages) is free
+        if (ntiles > 0) {
+            bool lok = true;
+            auto tile_step = [&](LoaderRegs<SRC>& regs, int it) {
+                const int st = it & 1;
+                if (it >= 2) {
                     // warp-uniform outcome: the warp-collective operations below need all lanes
-                    const bool w = ptx::mbar_wait(bar_kv_free, uint32_t(it - 1) & 1u, kWaitTimeoutNs);
+                    const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, uint32_t((it >> 1) - 1) & 1u, kWaitTimeoutNs);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
                         report_timeout(a.status, kStatusWaitKvFree, 2, tile0 + it);
-                        break;
+                        lok = false;
+                        return;
                     }
                 }
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it);
-                loader_store<NCHUNK, SRC>(kv_base, lw * 8, lane, regs);
-                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask)[lw] = uint8_t(regs.vmask);
+                // the key resolved during the previous step has arrived by now: start pulling
+                // its records into L2 (using it earlier would stall on the block-table load)
+                if (!(a.dbg & 2)) loader_prefetch_l2<SRC>(key4, vm4, lane);
+                loader_store<NCHUNK, SRC>(kv_base + uint32_t(st) * L::kKvStageBytes, lw * 8, lane, regs);
+                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_kv_full);
+                if (lane == 0) ptx::mbar_arrive(bar_kv_full + 8 * st);
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
-                if (it + 1 < ntiles) {
-                    // data of the next tile: in flight during this tile's MMAs
-                    loader_fetch<SRC>(a, next_key, next_vmask, lane, regs);
-                    next_key = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 2) * kTileN + lw * 8, lane,
-                                                        (it + 2 < ntiles) ? n_tok : 0, kv_len_n, next_vmask);
-                }
+                // this set is free again: loads of tile it+2, keys of tile it+5
+                if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
+                key2 = key3;  vm2 = vm3;
+                key3 = key4;  vm3 = vm4;
+                key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 5) * kTileN + lw * 8, lane,
+                                                (it + 5 < ntiles) ? n_tok : 0, kv_len_n, vm4);
+            };
+            for (int it = 0; it < ntiles && lok; it += 2) {
+                tile_step(regs_a, it);
+                if (it + 1 < ntiles && lok) tile_step(regs_b, it + 1);
             }
-        } else if (warp == kMmaWarp) {
-            // ───────────── MMA issue (one thread) ─────────────
+        }
+    } else if (warp >= kMmaWarp) {
+        // ───────────── last warpgroup: MMA issue (one thread of warp 12), tensor-memory owner ─────────────
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIdleRegs));
+        if (warp == kMmaWarp) {
+            ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
+            ptx::tmem_relinquish();
+        }
+        block_sync();
+        const uint32_t tmem = misc->tmem_base;
+        block_sync();
+        if (ntiles > 0 && warp == kMmaWarp) {
             if (lane == 0) {
                 constexpr uint32_t idesc_qk = ptx::make_idesc_bf16(128, kTileN, false, false);
                 constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 bool ok = true;
-                for (int it = 0; it < ntiles && ok; ++it) {
-                    if (!ptx::mbar_wait(bar_kv_full, uint32_t(it) & 1u, kWaitTimeoutNs)) {
-                        report_timeout(a.status, kStatusWaitKvFull, 1, tile0 + it);
-                        ok = false;  break;
-                    }
-                    ptx::tc_fence_after_sync();
-                    trace_mark(a, 1, 2 * it);
+                // S(it) = Q . K(it)^T into S buffer it&1; one tile ahead of the PV MMAs so that
+                // the softmax of tile it overlaps the QK MMAs of tile it+1.
+                // Chunks [C0, C1) (4 MMAs each) of S(it) = Q . K(it)^T into S buffer it&1; the chunk
+                // range is a compile-time constant so that the descriptors fold to immediates.
+                auto issue_qk_range = [&](int it, auto c0_tag, auto c1_tag) {
+                    constexpr int C0 = decltype(c0_tag)::value, C1 = decltype(c1_tag)::value;
+                    const int st = it & 1;
+                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
+                    const uint32_t d = tmem + kTmemS + uint32_t(st) * kTileN;
 #pragma unroll
-                    for (int c = 0; c < NCHUNK; ++c) {
+                    for (int c = C0; c < C1; ++c) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t da = ptx::make_smem_desc(q_base + c * kQChunkBytes + k * 32, 16, 1024);
-                            const uint64_t db = ptx::make_smem_desc(kv_base + c * kKvChunkBytes + k * 32, 16, 1024);
-                            ptx::mma_bf16_ss(tmem + kTmemS, da, db, idesc_qk, (c | k) ? 1u : 0u);
+                            const uint64_t db = ptx::make_smem_desc(kv_st + c * kKvChunkBytes + k * 32, 16, 1024);
+                            if (c < kQTmemChunks) {
+                                // A = Q columns in tensor memory: 16 BF16 = 8 columns per K step
+                                ptx::mma_bf16_ts(d, tmem + kTmemQ + c * 32 + k * 8, db, idesc_qk, (c | k) ? 1u : 0u);
+                            } else {
+                                const uint64_t da = ptx::make_smem_desc(q_base + (c - kQTmemChunks) * kQChunkBytes + k * 32, 16, 1024);
+                                ptx::mma_bf16_ss(d, da, db, idesc_qk, 1u);
+                            }
                         }
                     }
-                    ptx::mma_commit(bar_s_full);
-                    if (!ptx::mbar_wait(bar_p_full, uint32_t(it) & 1u, kWaitTimeoutNs)) {
-                        report_timeout(a.status, kStatusWaitPFull, 1, tile0 + it);
-                        ok = false;  break;
-                    }
+                };
+                // QK is issued in three groups of chunks; between groups a ready P goes first.
+                constexpr int kG1 = 3, kG2 = 6;
+                auto issue_qk_group = [&](int it, int g) {
+                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, kG1>{});
+                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, kG1>{}, std::integral_constant<int, kG2>{});
+                    else issue_qk_range(it, std::integral_constant<int, kG2>{}, std::integral_constant<int, NCHUNK>{});
+                };
+                auto issue_pv = [&](int it) {
+                    const int st = it & 1;
+                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
                     ptx::tc_fence_after_sync();
                     trace_mark(a, 1, 2 * it + 1);
+                    const uint32_t p_tmem = tmem + kTmemS + uint32_t(st) * kTileN;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        // A = P rows (K-major, 16 entries = 32 bytes per step);
+                        // A = P in tensor memory (16 entries = 8 columns per step);
                         // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart,
                         // 8-entry groups 1 KB apart.
-                        const uint64_t da = ptx::make_smem_desc(p_base + k * 32, 16, 1024);
-                        const uint64_t db = ptx::make_smem_desc(v_base + k * 2048, kKvChunkBytes, 1024);
-                        ptx::mma_bf16_ss(tmem + kTmemO, da, db, idesc_pv, (it | k) ? 1u : 0u);
+                        const uint64_t db = ptx::make_smem_desc(kv_st + v_off + k * 2048, kKvChunkBytes, 1024);
+                        ptx::mma_bf16_ts(tmem + kTmemO, p_tmem + k * 8, db, idesc_pv, (it | k) ? 1u : 0u);
                     }
-                    ptx::mma_commit(bar_kv_free);
+                    ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
+                    trace_mark(a, 1, 512 + 4 * it + 3);
+                };
+                // S(t) runs up to one tile ahead of O += P(t) . V(t), so that the softmax of
+                // tile t overlaps the QK MMAs of tile t+1.  Between the QK groups a ready P goes
+                // first, so that its stage is handed back to the loaders early.
+                int qk_tile = 0, qk_chunk = 0, pv_next = 0;
+                uint64_t t_last = 0;
+                uint32_t polls = 0;
+                while (pv_next < ntiles) {
+                    bool progress = false;
+                    if (pv_next < qk_tile &&
+                        ptx::mbar_test_wait(bar_p_full + 8 * (pv_next & 1), uint32_t(pv_next >> 1) & 1u)) {
+                        issue_pv(pv_next);
+                        ++pv_next;
+                        progress = true;
+                    } else if (qk_tile < ntiles && qk_tile <= pv_next + 1) {
+                        if (qk_chunk == 0) {
+                            if (ptx::mbar_test_wait(bar_kv_full + 8 * (qk_tile & 1), uint32_t(qk_tile >> 1) & 1u)) {
+                                ptx::tc_fence_after_sync();
+                                trace_mark(a, 1, 2 * qk_tile);
+                                issue_qk_group(qk_tile, 0);
+                                trace_mark(a, 1, 512 + 4 * qk_tile);
+                                qk_chunk = 1;
+                                progress = true;
+                            }
+                        } else {
+                            issue_qk_group(qk_tile, qk_chunk);
+                            trace_mark(a, 1, 512 + 4 * qk_tile + qk_chunk);
+                            if (++qk_chunk == 3) {
+                                ptx::mma_commit(bar_s_full + 8 * (qk_tile & 1));
+                                qk_chunk = 0;
+                                ++qk_tile;
+                            }
+                            progress = true;
+                        }
+                    }
+                    if (progress) {
+                        polls = 0;
+                    } else {
+                        __nanosleep(40);     // leave the issue slots to the warps doing the work
+                        if (polls == 0) t_last = ptx::globaltimer_ns();
+                        if ((++polls & 255u) != 0u || ptx::globaltimer_ns() - t_last <= kWaitTimeoutNs) continue;
+                        report_timeout(a.status, (pv_next < qk_tile) ? kStatusWaitPFull : kStatusWaitKvFull, 1,
+                                       tile0 + pv_next);
+                        ok = false;
+                        break;
+                    }
                 }
                 if (ok) ptx::mma_commit(bar_o_full);
             }
             __syncwarp();
-        } else {
-            // ───────────── softmax + epilogue warps ─────────────
+        }
+    } else {
+        // ───────────── softmax + epilogue warps ─────────────
+        stage_q();
+        block_sync();
+        const uint32_t tmem = misc->tmem_base;
+        if (ntiles > 0) {
+            // head row r = this thread's tensor-memory lane: copy its staged Q columns there,
+            // two BF16 per 32-bit column, in K order (the A-operand layout of the MMA)
+            const int r = warp * 32 + lane;
+            const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+            const uint32_t srow = kv_base + uint32_t(r) * L::kQStageRowBytes;
+            const uint32_t sw = uint32_t(r & 7);
+#pragma unroll 1
+            for (int g = 0; g < kQTmemChunks; ++g) {
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint4 x = ptx::lds_v4(srow + ((uint32_t(g * 8 + j) ^ sw) << 4));
+                    w[4 * j + 0] = x.x;  w[4 * j + 1] = x.y;  w[4 * j + 2] = x.z;  w[4 * j + 3] = x.w;
+                }
+                ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w);
+            }
+            ptx::tmem_wait_st();
+        }
+        block_sync();
+        if (tid == 0) trace_mark(a, 3, 1);
+        if (ntiles > 0) {
             const int r = warp * 32 + lane;                // head row inside the group
             const uint32_t lane_addr = uint32_t(warp * 32) << 16;
             float m_ref = -CUDART_INF_F;                   // reference maximum used in exp2 (log2 units)
             float l_sum = 0.f;
             bool ok = true;
             for (int it = 0; it < ntiles; ++it) {
+                const int st = it & 1;
+                const uint32_t s_tmem = tmem + lane_addr + kTmemS + uint32_t(st) * kTileN;
                 {
-                    const bool w = ptx::mbar_wait(bar_s_full, uint32_t(it) & 1u, kWaitTimeoutNs);
+                    const bool w = ptx::mbar_wait(bar_s_full + 8 * st, uint32_t(it >> 1) & 1u, kWaitTimeoutNs);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
                         report_timeout(a.status, kStatusWaitSFull, 0, tile0 + it);
                         ok = false;  break;
@@ -489,10 +669,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tc_fence_after_sync();
                 if (tid == 0) trace_mark(a, 0, 2 * it);
                 uint32_t s0[32], s1[32];
-                ptx::tmem_ld32(tmem + lane_addr + kTmemS, s0);
-                ptx::tmem_ld32(tmem + lane_addr + kTmemS + 32, s1);
+                ptx::tmem_ld32(s_tmem, s0);
+                ptx::tmem_ld32(s_tmem + 32, s1);
                 ptx::tmem_wait_ld();
-                const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask);
+                const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
                 const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
                 float x0[32], x1[32];
                 float tmax = -CUDART_INF_F;
@@ -527,18 +707,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     pk[16 + i] = ptx::pack_bf16x2(p0, p1);
                 }
                 l_sum = l_sum * alpha + psum;
-                // P row r: 8 vectors of 8 entries
-                {
-                    const uint32_t prow = p_base + uint32_t(r) * 128u;
-                    const uint32_t sw = uint32_t(r & 7);
-#pragma unroll
-                    for (int v = 0; v < 8; ++v)
-                        ptx::sts_v4(prow + ((uint32_t(v) ^ sw) << 4),
-                                    make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]));
-                }
-                // Rescale O where the reference maximum moved.  All earlier MMAs have
-                // completed (the commit that released S follows them in issue order).
+                // Rescale O where the reference maximum moved.  The PV MMAs of the previous
+                // tile must have finished first (their commit is that stage's kv_free).
                 if (it > 0 && __any_sync(0xFFFFFFFFu, moved)) {
+                    const bool w = ptx::mbar_wait(bar_kv_free + 8 * ((it - 1) & 1), uint32_t((it - 1) >> 1) & 1u, kWaitTimeoutNs);
+                    if (!__all_sync(0xFFFFFFFFu, w)) {
+                        report_timeout(a.status, kStatusWaitKvFree, 0, tile0 + it);
+                        ok = false;  break;
+                    }
+                    ptx::tc_fence_after_sync();
 #pragma unroll 1
                     for (int c = 0; c < kDvHalf / 32; ++c) {
                         uint32_t o[32];
@@ -548,12 +725,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         ptx::tmem_st32(tmem + lane_addr + kTmemO + c * 32, o);
                     }
-                    ptx::tmem_wait_st();
                 }
-                ptx::fence_proxy_async_smem();
+                // P (BF16, two entries per column) over the first 32 columns of this S buffer:
+                // the A operand of the PV MMAs.  S has been read into registers above.
+                ptx::tmem_st32(s_tmem, pk);
+                ptx::tmem_wait_st();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_p_full);
+                if (lane == 0) ptx::mbar_arrive(bar_p_full + 8 * st);
                 if (tid == 0) trace_mark(a, 0, 2 * it + 1);
             }
             // ── epilogue ──
@@ -615,7 +794,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 }
             }
         }
-    } else {
+    }
+    if (ntiles <= 0) {
         // Nothing to attend to in this split: zero output, LSE = -inf.
         const bool final_out = a.num_splits == 1;
         for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumThreads) {
@@ -651,7 +831,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     if (tid == 0) trace_mark(a, 3, 3);
     if (warp == kMmaWarp) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem, kTmemCols);
+        ptx::tmem_dealloc(misc->tmem_base, kTmemCols);
     }
 }
 
