@@ -26,7 +26,7 @@ class CsaSparseDecodeParams(C.Structure):
         ("max_pages", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float),
         ("reserved0", C.c_int32), ("num_pages", C.c_int64),
         ("q", C.c_void_p), ("kv_pool", C.c_void_p), ("block_table", C.c_void_p),
-        ("indices", C.c_void_p), ("kv_len", C.c_void_p), ("attn_sink", C.c_void_p),
+        ("indices", C.c_void_p), ("kv_len", C.c_void_p), ("topk_len", C.c_void_p), ("attn_sink", C.c_void_p),
         ("out", C.c_void_p), ("lse", C.c_void_p), ("partial_o", C.c_void_p),
         ("partial_lse", C.c_void_p), ("status", C.c_void_p),
     ]

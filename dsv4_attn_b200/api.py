@@ -110,11 +110,12 @@ def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace,
     return B, s_q, H, num_splits, out, lse, po, pl
 
 
-def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None, attn_sink=None,
+def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None, topk_len=None, attn_sink=None,
                       num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma"):
     """CSA sparse decode.  q bf16 [B, s_q, H, 576]; kv_pool uint8 [P, 64, 656];
     block_table int32 [B, max_pages]; indices int32 [B, s_q, topk] (-1 = pad);
-    kv_len optional int32 [B, s_q].  Returns (out bf16 [B, s_q, H, 512],
+    kv_len optional int32 [B, s_q]; topk_len optional int32 [B, s_q] (only the
+    first topk_len slots of each list are read).  Returns (out bf16 [B, s_q, H, 512],
     lse f32 [B, s_q, H])."""
     _cuda_contig(indices, "indices", torch.int32, 3)
     topk = indices.shape[-1]
@@ -126,11 +127,14 @@ def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None
     if kv_len is not None:
         _cuda_contig(kv_len, "kv_len", torch.int32, 2)
         _check(tuple(kv_len.shape) == (B, s_q), "kv_len must be [B, s_q]")
+    if topk_len is not None:
+        _cuda_contig(topk_len, "topk_len", torch.int32, 2)
+        _check(tuple(topk_len.shape) == (B, s_q), "topk_len must be [B, s_q]")
     p = _lib.CsaSparseDecodeParams(
         B=B, s_q=s_q, H=H, topk=topk, max_pages=block_table.shape[1], num_splits=num_splits,
         sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
         q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), indices=_ptr(indices),
-        kv_len=_ptr(kv_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
+        kv_len=_ptr(kv_len), topk_len=_ptr(topk_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
         partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
     fn = _lib.LIB.dsv4_csa_sparse_decode_fwd if impl == "mma" else _lib.LIB.dsv4_csa_sparse_decode_simt
     _rc(fn(C.byref(p), _stream(q.device)), "dsv4_csa_sparse_decode")

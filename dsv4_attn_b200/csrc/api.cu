@@ -3,6 +3,7 @@
 // per-device kernel attributes that are set once.
 #include "../../include/dsv4_attn.h"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cmath>
 #include <mutex>
@@ -20,6 +21,38 @@ constexpr int kMaxDevices = 64;
 // the next decode launches writes phase timestamps to.  Null in normal use.
 unsigned long long* g_trace = nullptr;
 int g_dbg = 0;
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does
+// not link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Q as a 2-D BF16 tensor [rows, cols], row-major; box = 64 columns x 128 rows, 128-byte swizzle.
+cudaError_t make_q_map(CUtensorMap* map, const void* q, int64_t rows, int cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -39,10 +72,12 @@ cudaError_t ensure_smem(Kernel kernel, int bytes, bool* done_per_device) {
 }
 
 template <int NCHUNK, int SRC>
-cudaError_t launch_mma(const DecodeArgs& a, int rows, cudaStream_t stream) {
+cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
     static bool done[kMaxDevices] = {};
     constexpr int smem = SmemLayout<NCHUNK>::kTotal;
     cudaError_t e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
+    if (e != cudaSuccess) return e;
+    e = make_q_map(&a.q_map, a.q, int64_t(rows) * a.H, NCHUNK * 64);
     if (e != cudaSuccess) return e;
     const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(2 * head_groups, rows, a.num_splits);
@@ -106,7 +141,7 @@ bool fill_csa(const Dsv4CsaSparseDecodeParams* p, DecodeArgs& a) {
     a.scale_log2 = p->sm_scale * 1.4426950408889634f;
     a.q = static_cast<const __nv_bfloat16*>(p->q);
     a.kv_pool = static_cast<const uint8_t*>(p->kv_pool);
-    a.block_table = p->block_table;  a.indices = p->indices;  a.kv_len = p->kv_len;
+    a.block_table = p->block_table;  a.indices = p->indices;  a.kv_len = p->kv_len;  a.topk_len = p->topk_len;
     a.attn_sink = p->attn_sink;
     a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;

@@ -17,6 +17,7 @@
 // block leaves through the common exit, freeing its tensor memory.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -46,8 +47,8 @@ constexpr int kFirstLoaderWarp = 4;
 constexpr int kMmaWarp = 12;
 constexpr int kNumWarps = 16;
 constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // threads that stage Q
-constexpr int kLoaderRegs = 168;       // 8 x 32 x (168-128) = 10240 registers taken ...
-constexpr int kIdleRegs = 48;          // ... from 4 x 32 x (128-48) = 10240 released
+constexpr int kLoaderRegs = 160;       // 8 x 32 x (160-128) = 8192 registers taken ...
+constexpr int kIdleRegs = 64;          // ... from 4 x 32 x (128-64) = 8192 released
 constexpr int kNumThreads = kNumWarps * 32;  // 512
 constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
@@ -70,9 +71,12 @@ enum StatusCode : int {
     kStatusWaitSFull = 3,
     kStatusWaitPFull = 4,
     kStatusWaitOFull = 5,
+    kStatusWaitQ = 6,
 };
 
 struct DecodeArgs {
+    // TMA descriptor of Q viewed as [rows = B*s_q*H, cols = 64*NCHUNK] bf16, box 64 x 128, 128-byte swizzle
+    alignas(64) CUtensorMap q_map;
     int B, s_q, H;
     int topk;            // CSA
     int max_pages;
@@ -84,6 +88,7 @@ struct DecodeArgs {
     const int32_t* block_table;
     const int32_t* indices;
     const int32_t* kv_len;
+    const int32_t* topk_len;
     const uint8_t* win_pool;
     const int32_t* win_len;
     const float* attn_sink;
@@ -110,9 +115,10 @@ struct SmemLayout {
     static constexpr int kMiscOff = kKvOff + 2 * kKvStageBytes;
     static constexpr int kMiscBytes = 256;
     static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;     // + slack to align the base to 1024
-    // the Q chunks bound for tensor memory are staged in the (still unused) KV stages
-    static constexpr int kQStageRowBytes = kQTmemChunks * 128;      // 512
-    static_assert(kHeadsPerCta * kQStageRowBytes <= 2 * kKvStageBytes, "Q staging must fit in the KV stages");
+    // the Q chunks bound for tensor memory are staged (as swizzled 16 KB chunks) in KV stage 1,
+    // which the loaders do not touch before the copy to tensor memory has finished
+    static constexpr int kQStageOff = kKvOff + kKvStageBytes;
+    static_assert(kQTmemChunks * kQChunkBytes <= kKvStageBytes, "Q staging must fit in one KV stage");
 };
 
 struct SmemMisc {
@@ -121,6 +127,8 @@ struct SmemMisc {
     uint64_t bar_s_full[2];
     uint64_t bar_p_full[2];
     uint64_t bar_o_full;
+    uint64_t bar_q_full;      // Q tile landed in shared memory (TMA transaction count)
+    uint64_t bar_q_ready;     // Q chunks copied to tensor memory, staging area released
     uint64_t valid_mask[2];   // per stage: bit t = entry t of the tile takes part in the softmax
     uint32_t tmem_base;
     uint32_t pad;
@@ -358,7 +366,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     // ── this block's tile range ──
     int n_tok, kv_len_n;
     if constexpr (SRC == kSrcCsa) {
-        n_tok = a.topk;
+        n_tok = (a.topk_len != nullptr) ? min(max(__ldg(a.topk_len + n), 0), a.topk) : a.topk;
         kv_len_n = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
     } else if constexpr (SRC == kSrcHca) {
         kv_len_n = max(__ldg(a.kv_len + n), 0);
@@ -380,6 +388,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full[0]);
     const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full[0]);
     const uint32_t bar_o_full = ptx::smem_u32(&misc->bar_o_full);
+    const uint32_t bar_q_full = ptx::smem_u32(&misc->bar_q_full);
+    const uint32_t bar_q_ready = ptx::smem_u32(&misc->bar_q_ready);
 
     // ── set-up ──
     if (tid == 0) {
@@ -391,49 +401,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
         }
         ptx::mbar_init(bar_o_full, 1);
+        ptx::mbar_init(bar_q_full, 1);
+        ptx::mbar_init(bar_q_ready, kNumSoftmaxWarps);
         ptx::fence_mbar_init();
-    }
-
-    // This thread's share of staging the Q tile [128 heads x NCHUNK*64] bf16 (rows >= H
-    // zero).  Chunks >= kQTmemChunks go to shared memory in the swizzled operand layout;
-    // the others are staged row-major (512 bytes per head, 16-byte columns XOR-ed with
-    // row % 8) in the still unused KV stages for the copy to tensor memory.
-    auto stage_q = [&]() {
-        if (ntiles <= 0) return;
-        constexpr int kVecsPerRow = NCHUNK * 8;
-        const __nv_bfloat16* qrow0 = a.q + int64_t(n) * a.H * (NCHUNK * 64);
-        constexpr int kTotalVecs = kHeadsPerCta * kVecsPerRow;
-        constexpr int kBatch = 8;             // loads in flight per thread
-        for (int v0 = tid; v0 < kTotalVecs; v0 += kStageThreads * kBatch) {
-            uint4 w[kBatch];
+        if (ntiles > 0) {
+            // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
+            // the swizzled operand layout: chunks >= kQTmemChunks at their final place, the others
+            // in the staging area.  Rows past the end of Q read as zero; rows of a following
+            // request (H < 128) are computed but never written out.
+            ptx::mbar_arrive_expect_tx(bar_q_full, uint32_t(NCHUNK) * kQChunkBytes);
+            const int row0 = n * a.H + hg * kHeadsPerCta;
 #pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int v = v0 + u * kStageThreads;
-                const int r = v / kVecsPerRow;
-                const int cv = v - r * kVecsPerRow;
-                const int h = hg * kHeadsPerCta + r;
-                w[u] = make_uint4(0, 0, 0, 0);
-                if (v < kTotalVecs && h < a.H) w[u] = ptx::ldg_nc_v4(qrow0 + int64_t(h) * (NCHUNK * 64) + cv * 8);
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int v = v0 + u * kStageThreads;
-                if (v < kTotalVecs) {
-                    const int r = v / kVecsPerRow;
-                    const int cv = v - r * kVecsPerRow;
-                    const uint32_t sw = uint32_t(r & 7);
-                    if (cv < kQTmemChunks * 8) {
-                        ptx::sts_v4(kv_base + uint32_t(r) * L::kQStageRowBytes + ((uint32_t(cv) ^ sw) << 4), w[u]);
-                    } else {
-                        const uint32_t c = uint32_t(cv >> 3) - kQTmemChunks, c16 = uint32_t(cv & 7);
-                        ptx::sts_v4(q_base + c * kQChunkBytes + uint32_t(r) * 128u + ((c16 ^ sw) << 4), w[u]);
-                    }
-                }
+            for (int c = 0; c < NCHUNK; ++c) {
+                const uint32_t dst = (c < kQTmemChunks) ? smem_base + L::kQStageOff + uint32_t(c) * kQChunkBytes
+                                                        : q_base + uint32_t(c - kQTmemChunks) * kQChunkBytes;
+                ptx::tma_load_2d(dst, &a.q_map, c * 64, row0, bar_q_full);
             }
         }
-        ptx::fence_proxy_async_smem();
-    };
-    // Block-wide rendezvous.  Every role runs the same number of them (two before the
+    }
+
+    // Block-wide rendezvous.  Every role runs the same number of them (one before the
     // main loops, one at the exit), each from its own branch.
     auto block_sync = [&]() {
         ptx::tc_fence_before_sync();
@@ -473,13 +460,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + 4) * kTileN + lw * 8, lane, (4 < ntiles) ? n_tok : 0,
                                             kv_len_n, vm4);
         }
-        stage_q();
         block_sync();
-        block_sync();          // Q is in tensor memory; the staging area (KV stages) is free
         if (ntiles > 0) {
             bool lok = true;
             auto tile_step = [&](LoaderRegs<SRC>& regs, int it) {
                 const int st = it & 1;
+                if (it == 1) {
+                    // stage 1 doubles as the Q staging area until the copy to tensor memory is done
+                    const bool w = ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs);
+                    if (!__all_sync(0xFFFFFFFFu, w)) {
+                        report_timeout(a.status, kStatusWaitQ, 2, tile0 + it);
+                        lok = false;
+                        return;
+                    }
+                }
                 if (it >= 2) {
                     // warp-uniform outcome: the warp-collective operations below need all lanes
                     const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, uint32_t((it >> 1) - 1) & 1u, kWaitTimeoutNs);
@@ -520,32 +514,40 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
         block_sync();
         const uint32_t tmem = misc->tmem_base;
-        block_sync();
         if (ntiles > 0 && warp == kMmaWarp) {
             if (lane == 0) {
                 constexpr uint32_t idesc_qk = ptx::make_idesc_bf16(128, kTileN, false, false);
                 constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 bool ok = true;
+                // Q: shared-memory chunks landed (TMA) and tensor-memory chunks copied
+                if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs)) {
+                    report_timeout(a.status, kStatusWaitQ, 1, tile0);
+                    ok = false;
+                }
+                ptx::tc_fence_after_sync();
                 // S(it) = Q . K(it)^T into S buffer it&1; one tile ahead of the PV MMAs so that
                 // the softmax of tile it overlaps the QK MMAs of tile it+1.
                 // Chunks [C0, C1) (4 MMAs each) of S(it) = Q . K(it)^T into S buffer it&1; the chunk
                 // range is a compile-time constant so that the descriptors fold to immediates.
+                constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);        // 8-row groups 1 KB apart
+                const uint32_t q_lo = ptx::smem_desc_lo(q_base, 16);
                 auto issue_qk_range = [&](int it, auto c0_tag, auto c1_tag) {
                     constexpr int C0 = decltype(c0_tag)::value, C1 = decltype(c1_tag)::value;
                     const int st = it & 1;
-                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
+                    const uint32_t k_lo = ptx::smem_desc_lo(kv_base + uint32_t(st) * L::kKvStageBytes, 16);
                     const uint32_t d = tmem + kTmemS + uint32_t(st) * kTileN;
 #pragma unroll
                     for (int c = C0; c < C1; ++c) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t db = ptx::make_smem_desc(kv_st + c * kKvChunkBytes + k * 32, 16, 1024);
+                            // descriptor start addresses advance by constants (in 16-byte units)
+                            const uint32_t b_lo = k_lo + uint32_t((c * kKvChunkBytes + k * 32) >> 4);
                             if (c < kQTmemChunks) {
                                 // A = Q columns in tensor memory: 16 BF16 = 8 columns per K step
-                                ptx::mma_bf16_ts(d, tmem + kTmemQ + c * 32 + k * 8, db, idesc_qk, (c | k) ? 1u : 0u);
+                                ptx::mma_bf16_ts2(d, tmem + kTmemQ + c * 32 + k * 8, b_lo, kDescHi, idesc_qk, (c | k) ? 1u : 0u);
                             } else {
-                                const uint64_t da = ptx::make_smem_desc(q_base + (c - kQTmemChunks) * kQChunkBytes + k * 32, 16, 1024);
-                                ptx::mma_bf16_ss(d, da, db, idesc_qk, 1u);
+                                const uint32_t a_lo = q_lo + uint32_t(((c - kQTmemChunks) * kQChunkBytes + k * 32) >> 4);
+                                ptx::mma_bf16_ss2(d, a_lo, b_lo, kDescHi, idesc_qk, 1u);
                             }
                         }
                     }
@@ -563,14 +565,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     ptx::tc_fence_after_sync();
                     trace_mark(a, 1, 2 * it + 1);
                     const uint32_t p_tmem = tmem + kTmemS + uint32_t(st) * kTileN;
+                    // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart (leading
+                    // offset), 8-entry groups 1 KB apart; A = P in tensor memory, 8 columns per step
+                    const uint32_t v_lo = ptx::smem_desc_lo(kv_st + v_off, kKvChunkBytes);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // A = P in tensor memory (16 entries = 8 columns per step);
-                        // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart,
-                        // 8-entry groups 1 KB apart.
-                        const uint64_t db = ptx::make_smem_desc(kv_st + v_off + k * 2048, kKvChunkBytes, 1024);
-                        ptx::mma_bf16_ts(tmem + kTmemO, p_tmem + k * 8, db, idesc_pv, (it | k) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        ptx::mma_bf16_ts2(tmem + kTmemO, p_tmem + k * 8, v_lo + uint32_t((k * 2048) >> 4), kDescHi, idesc_pv,
+                                          (it | k) ? 1u : 0u);
                     ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
                     trace_mark(a, 1, 512 + 4 * it + 3);
                 };
@@ -580,7 +581,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 int qk_tile = 0, qk_chunk = 0, pv_next = 0;
                 uint64_t t_last = 0;
                 uint32_t polls = 0;
-                while (pv_next < ntiles) {
+                while (ok && pv_next < ntiles) {
                     bool progress = false;
                     if (pv_next < qk_tile &&
                         ptx::mbar_test_wait(bar_p_full + 8 * (pv_next & 1), uint32_t(pv_next >> 1) & 1u)) {
@@ -626,37 +627,45 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
     } else {
         // ───────────── softmax + epilogue warps ─────────────
-        stage_q();
         block_sync();
         const uint32_t tmem = misc->tmem_base;
+        bool ok = true;
         if (ntiles > 0) {
             // head row r = this thread's tensor-memory lane: copy its staged Q columns there,
             // two BF16 per 32-bit column, in K order (the A-operand layout of the MMA)
-            const int r = warp * 32 + lane;
-            const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-            const uint32_t srow = kv_base + uint32_t(r) * L::kQStageRowBytes;
-            const uint32_t sw = uint32_t(r & 7);
-#pragma unroll 1
-            for (int g = 0; g < kQTmemChunks; ++g) {
-                uint32_t w[32];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint4 x = ptx::lds_v4(srow + ((uint32_t(g * 8 + j) ^ sw) << 4));
-                    w[4 * j + 0] = x.x;  w[4 * j + 1] = x.y;  w[4 * j + 2] = x.z;  w[4 * j + 3] = x.w;
-                }
-                ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w);
+            const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
+            if (!__all_sync(0xFFFFFFFFu, w)) {
+                report_timeout(a.status, kStatusWaitQ, 0, tile0);
+                ok = false;
             }
-            ptx::tmem_wait_st();
+            if (ok) {
+                const int r = warp * 32 + lane;
+                const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+                const uint32_t srow = smem_base + L::kQStageOff + uint32_t(r) * 128u;
+                const uint32_t sw = uint32_t(r & 7);
+#pragma unroll 1
+                for (int g = 0; g < kQTmemChunks; ++g) {
+                    uint32_t w32[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 x = ptx::lds_v4(srow + uint32_t(g) * kQChunkBytes + ((uint32_t(j) ^ sw) << 4));
+                        w32[4 * j + 0] = x.x;  w32[4 * j + 1] = x.y;  w32[4 * j + 2] = x.z;  w32[4 * j + 3] = x.w;
+                    }
+                    ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w32);
+                }
+                ptx::tmem_wait_st();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_q_ready);
+            }
         }
-        block_sync();
         if (tid == 0) trace_mark(a, 3, 1);
         if (ntiles > 0) {
             const int r = warp * 32 + lane;                // head row inside the group
             const uint32_t lane_addr = uint32_t(warp * 32) << 16;
             float m_ref = -CUDART_INF_F;                   // reference maximum used in exp2 (log2 units)
             float l_sum = 0.f;
-            bool ok = true;
-            for (int it = 0; it < ntiles; ++it) {
+            for (int it = 0; it < ntiles && ok; ++it) {
                 const int st = it & 1;
                 const uint32_t s_tmem = tmem + lane_addr + kTmemS + uint32_t(st) * kTileN;
                 {

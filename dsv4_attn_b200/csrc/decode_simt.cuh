@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(kSimtThreads) decode_simt_kernel(const DecodeA
     const int b = n / a.s_q;
     int n_tok, kv_len_n;
     if constexpr (SRC == kSrcCsa) {
-        n_tok = a.topk;
+        n_tok = a.topk_len ? min(max(a.topk_len[n], 0), a.topk) : a.topk;
         kv_len_n = a.kv_len ? a.kv_len[n] : 0x7FFFFFFF;
     } else if constexpr (SRC == kSrcHca) {
         kv_len_n = max(a.kv_len[n], 0);

@@ -54,6 +54,7 @@ class CsaWorkload:
     block_table: torch.Tensor
     indices: torch.Tensor
     kv_len: torch.Tensor
+    topk_len: torch.Tensor      # [B, s_q] leading index slots in use
     sm_scale: float
     valid_entries: int          # sum over (request, token) of gathered entries
 
@@ -71,16 +72,18 @@ def make_csa(seed: int, B: int, s_q: int, H: int, n_entries: IntOrSeq, topk: int
     pool = random_pool(P, device, g)
     indices = torch.full((B, s_q, topk), -1, dtype=torch.int32, device=device)
     kv_len = torch.zeros(B, s_q, dtype=torch.int32)
+    topk_len = torch.zeros(B, s_q, dtype=torch.int32)
     valid = 0
     for b in range(B):
         for j in range(s_q):
             vis = max(int(n_ent[b]) - (s_q - 1 - j), 0)
             kv_len[b, j] = vis
             k = min(topk, vis)
+            topk_len[b, j] = k
             if k > 0:
                 indices[b, j, :k] = torch.randperm(vis, generator=g, device=device)[:k].to(torch.int32)
             valid += k
-    return CsaWorkload(q, pool, bt, indices, kv_len.to(device), 1.0 / math.sqrt(D_QK), valid)
+    return CsaWorkload(q, pool, bt, indices, kv_len.to(device), topk_len.to(device), 1.0 / math.sqrt(D_QK), valid)
 
 
 @dataclass
@@ -127,3 +130,13 @@ def lognormal_contexts(n: int, seed: int = 0, median: int = 8192, sigma: float =
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(n, generator=g) * sigma + math.log(median)
     return torch.clamp(torch.exp(x), lo, hi).round().to(torch.int64).tolist()
+
+
+def make_mixed(seed: int, contexts: Sequence[int], H: int = 128, topk: int = 2048, device="cuda"):
+    """The two layers of the mixed decode workload for one shard of requests:
+    a CSA layer (compression ratio 4: ctx // 4 entries, top-k `topk`) and an HCA
+    layer (ratio 128: ctx // 128 entries plus a 128-entry window)."""
+    csa = make_csa(seed, len(contexts), 1, H, [max(c // 4, 1) for c in contexts], topk, device=device)
+    hca = make_hca(seed + 1, len(contexts), 1, H, [c // 128 for c in contexts], [min(128, c) for c in contexts],
+                   device=device)
+    return csa, hca

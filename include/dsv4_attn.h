@@ -66,6 +66,8 @@ typedef struct Dsv4CsaSparseDecodeParams {
     const int32_t* indices;     /* int32 [B, s_q, topk]; negative = padding */
     const int32_t* kv_len;      /* optional int32 [B, s_q]: indices >= kv_len are masked (causality
                                    between speculative tokens); NULL = no bound */
+    const int32_t* topk_len;    /* optional int32 [B, s_q]: only the first topk_len slots of each index list
+                                   are read (ragged batches padded to a common topk); NULL = all topk */
     const float*   attn_sink;   /* optional float [H], natural-log units, added to the denominator */
     void*          out;         /* bf16  [B, s_q, H, 512] */
     float*         lse;         /* optional float [B, s_q, H], natural log, sink excluded, -inf if empty */
