@@ -50,6 +50,7 @@ constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // th
 constexpr int kLoaderRegs = 160;       // 8 x 32 x (160-128) = 8192 registers taken ...
 constexpr int kIdleRegs = 64;          // ... from 4 x 32 x (128-64) = 8192 released
 constexpr int kNumThreads = kNumWarps * 32;  // 512
+constexpr int kGroupChunks = 3;        // chunks per hand-over from the loaders to the MMA thread
 constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
 constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P (BF16) overwrites the first 32 of its S
@@ -113,7 +114,7 @@ struct SmemLayout {
     static constexpr int kQOff = 0;
     static constexpr int kKvOff = kQBytes;                          // two stages
     static constexpr int kMiscOff = kKvOff + 2 * kKvStageBytes;
-    static constexpr int kMiscBytes = 256;
+    static constexpr int kMiscBytes = 512;
     static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;     // + slack to align the base to 1024
     // the Q chunks bound for tensor memory are staged (as swizzled 16 KB chunks) in KV stage 1,
     // which the loaders do not touch before the copy to tensor memory has finished
@@ -122,7 +123,7 @@ struct SmemLayout {
 };
 
 struct SmemMisc {
-    uint64_t bar_kv_full[2];
+    uint64_t bar_kv_full[2][10];   // [stage][chunk]: chunk written by all loader warps
     uint64_t bar_kv_free[2];
     uint64_t bar_s_full[2];
     uint64_t bar_p_full[2];
@@ -172,14 +173,17 @@ __device__ __forceinline__ void dequant4(uint32_t w, __nv_bfloat162 scale2, uint
 }
 
 // Registers one loader thread holds for one tile.  A loader warp owns 8
-// consecutive entries of the tile; for entry i the 32 lanes read the 512 latent
-// bytes as 32 consecutive 16-byte vectors (one coalesced request per entry).
+// consecutive entries of the tile; lane/4 picks the entry and lane%4 one 16-byte
+// (16-element) piece of a 64-element latent chunk, so that one load instruction
+// per chunk covers 8 entries x 64 contiguous bytes and the tile can be written
+// to shared memory - and consumed by the MMAs - chunk by chunk.
 template <int SRC>
 struct LoaderRegs {
-    uint4 lat[8];        // entry i, latent dims [16*lane, 16*lane + 16)
-    uint32_t sc[8];      // entry i: FP32 scale bits of block lane/8, or the UE8M0 byte of block lane/4
-    uint4 rope[2];       // entry r*4 + lane/8, RoPE 16-byte column lane%8
-    uint32_t vmask;      // bit i = entry i of this warp takes part (same in all lanes)
+    static constexpr int kLatChunks = (SRC == kSrcRef) ? 7 : 8;
+    uint4 lat[kLatChunks];   // latent chunk c, elements [64c + 16*(lane%4), +16) of entry lane/4
+    uint4 rope[2];           // RoPE 16-byte columns lane%4 and lane%4 + 4 of entry lane/4
+    uint32_t sc[4];          // packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
+    uint32_t vmask;          // bit i = entry i of this warp takes part (same in all lanes)
 };
 
 // Where an entry lives: for the packed layouts the address of its 656-byte
@@ -230,55 +234,39 @@ __device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeAr
     return key;
 }
 
-// Loads of entry i of the warp (key held by lane i): its latent vector and scale.
-template <int SRC>
-__device__ __forceinline__ void loader_fetch_entry(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
-                                                   int i, uint4& lat, uint32_t& sc) {
-    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-    if ((vmask >> i) & 1u) {
-        if constexpr (SRC != kSrcRef) {
-            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
-            lat = ptx::ldg_nc_v4(row + lane * 16);
-            sc = __ldg(reinterpret_cast<const uint32_t*>(row + 512) + (lane >> 3));
-        } else {
-            const bool swa = (k >> 62) & 1ull;
-            const int64_t e = int64_t(k & ~(1ull << 62));
-            const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
-            const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
-            if (lane < 28) {
-                lat = ptx::ldg_nc_v4(lp + lane * 16);
-                sc = __ldg(sp + (lane >> 2));
-            }
-        }
-    }
-}
-
-// Loads of the RoPE tails of entries rr*4 .. rr*4+3 (lane/8 picks the entry).
-template <int SRC>
-__device__ __forceinline__ void loader_fetch_rope(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
-                                                  int rr, uint4& rope) {
-    const int i = rr * 4 + (lane >> 3);
-    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-    if ((vmask >> i) & 1u) {
-        if constexpr (SRC != kSrcRef) {
-            rope = ptx::ldg_nc_v4(reinterpret_cast<const uint8_t*>(k) + 528 + (lane & 7) * 16);
-        } else {
-            const bool swa = (k >> 62) & 1ull;
-            const int64_t e = int64_t(k & ~(1ull << 62));
-            const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
-            rope = ptx::ldg_nc_v4(rp + (lane & 7) * 16);
-        }
-    }
-}
-
+// Issue the loads of one tile for this lane's entry (key held by lane `lane/4`).
 template <int SRC>
 __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
                                              LoaderRegs<SRC>& r) {
     r.vmask = vmask;
+    const int i = lane >> 2, piece = lane & 3;
+    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+    if (!((vmask >> i) & 1u)) return;
+    if constexpr (SRC != kSrcRef) {
+        const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) loader_fetch_entry<SRC>(a, key, vmask, lane, i, r.lat[i], r.sc[i]);
+        for (int c = 0; c < 8; ++c) r.lat[c] = ptx::ldg_nc_v4(row + c * 64 + piece * 16);
+        const uint4 s4 = ptx::ldg_nc_v4(row + 512);
+        r.sc[0] = s4.x;  r.sc[1] = s4.y;  r.sc[2] = s4.z;  r.sc[3] = s4.w;
+        r.rope[0] = ptx::ldg_nc_v4(row + 528 + piece * 16);
+        r.rope[1] = ptx::ldg_nc_v4(row + 528 + (piece + 4) * 16);
+    } else {
+        const bool swa = (k >> 62) & 1ull;
+        const int64_t e = int64_t(k & ~(1ull << 62));
+        const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
+        const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
+        const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) loader_fetch_rope<SRC>(a, key, vmask, lane, rr, r.rope[rr]);
+        for (int c = 0; c < 7; ++c) r.lat[c] = ptx::ldg_nc_v4(lp + c * 64 + piece * 16);
+        uint32_t s0 = 0, s1 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s0 |= uint32_t(__ldg(sp + j)) << (8 * j);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) s1 |= uint32_t(__ldg(sp + 4 + j)) << (8 * j);
+        r.sc[0] = s0;  r.sc[1] = s1;
+        r.rope[0] = ptx::ldg_nc_v4(rp + piece * 16);
+        r.rope[1] = ptx::ldg_nc_v4(rp + (piece + 4) * 16);
+    }
 }
 
 // Pull the 656-byte records of the warp's 8 entries (keys in lanes 0..7) into L2
@@ -296,52 +284,45 @@ __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint3
     }
 }
 
-// Dequantise and write this warp's 8 entries (tile rows t0..t0+7) into the KV
-// tile.  Row t of each 64-column chunk is 128 bytes; 16-byte column c16 of row
-// t lives at ((c16 ^ (t & 7)) << 4).  Lanes of odd chunks write their two
-// columns in the opposite order so that one store instruction covers all eight
-// column positions (no more shared-memory wavefronts than the data needs).
+// Dequantise and write chunk c (64 columns) of this warp's 8 entries (tile rows
+// t0 .. t0+7) into the KV tile.  Row t of a chunk is 128 bytes; 16-byte column c16
+// of row t lives at ((c16 ^ (t & 7)) << 4).  The 8 rows x 4 pieces of one store
+// instruction cover every column position four times: as few shared-memory
+// wavefronts as 512 bytes need.  Chunk NCHUNK-1 is the RoPE tail (a plain copy).
 template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store(uint32_t kv_base, int t0, int lane, const LoaderRegs<SRC>& r) {
-    constexpr int kLatLanes = (SRC == kSrcRef) ? 28 : 32;
-    const uint32_t chunk = uint32_t(lane >> 2);
-    const uint32_t c16 = uint32_t(lane & 3) * 2u;
-    const uint32_t flip = chunk & 1u;
-    const uint32_t vmask = r.vmask;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int t = t0 + i;
-        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-        if (((vmask >> i) & 1u) && lane < kLatLanes) {
-            float s120;
-            if constexpr (SRC == kSrcRef) {
-                // 2^(byte-127) * 2^120; a zero byte means a zero scale, as in the reference's dequantiser
-                s120 = (r.sc[i] & 0xFFu) ? __uint_as_float(((r.sc[i] & 0xFFu) + 120u) << 23) : 0.f;
-            } else {
-                s120 = __uint_as_float(r.sc[i]) * 1.329227995784916e36f;   // 2^120
-            }
-            const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
-            dequant4(r.lat[i].x, scale2, w0.x, w0.y);
-            dequant4(r.lat[i].y, scale2, w0.z, w0.w);
-            dequant4(r.lat[i].z, scale2, w1.x, w1.y);
-            dequant4(r.lat[i].w, scale2, w1.z, w1.w);
-        }
-        if (lane < kLatLanes) {
-            const uint32_t base = kv_base + chunk * kKvChunkBytes + uint32_t(t) * 128u;
-            const uint32_t sw = uint32_t(t & 7);
-            const uint32_t ca = (c16 + flip) ^ sw, cb = (c16 + (flip ^ 1u)) ^ sw;
-            ptx::sts_v4(base + (ca << 4), flip ? w1 : w0);
-            ptx::sts_v4(base + (cb << 4), flip ? w0 : w1);
-        }
+__device__ __forceinline__ void loader_store_chunk(uint32_t kv_base, int t0, int lane, const LoaderRegs<SRC>& r, int c) {
+    const int i = lane >> 2;
+    const uint32_t piece = uint32_t(lane & 3);
+    const int t = t0 + i;
+    const bool valid = (r.vmask >> i) & 1u;
+    const uint32_t base = kv_base + uint32_t(c) * kKvChunkBytes + uint32_t(t) * 128u;
+    const uint32_t sw = uint32_t(t & 7);
+    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
+    if (c == NCHUNK - 1) {
+        if (valid) { w0 = r.rope[0];  w1 = r.rope[1]; }
+        ptx::sts_v4(base + ((piece ^ sw) << 4), w0);
+        ptx::sts_v4(base + (((piece + 4u) ^ sw) << 4), w1);
+        return;
     }
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const int i = rr * 4 + (lane >> 3);
-        const int t = t0 + i;
-        const uint32_t base = kv_base + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        ptx::sts_v4(base + (((uint32_t(lane) & 7u) ^ uint32_t(t & 7)) << 4), ((vmask >> i) & 1u) ? r.rope[rr] : z);
+    if (valid) {
+        float s120;
+        if constexpr (SRC == kSrcRef) {
+            // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
+            // scale, as in the reference's dequantiser
+            const uint32_t byte = ((c < 4 ? r.sc[0] >> (8 * c) : r.sc[1] >> (8 * (c - 4))) & 0xFFu);
+            s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
+        } else {
+            s120 = __uint_as_float(r.sc[c >> 1]) * 1.329227995784916e36f;   // one FP32 scale per 128 elements; x 2^120
+        }
+        const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
+        const uint4 x = r.lat[c];
+        dequant4(x.x, scale2, w0.x, w0.y);
+        dequant4(x.y, scale2, w0.z, w0.w);
+        dequant4(x.z, scale2, w1.x, w1.y);
+        dequant4(x.w, scale2, w1.z, w1.w);
     }
+    ptx::sts_v4(base + (((2u * piece) ^ sw) << 4), w0);
+    ptx::sts_v4(base + (((2u * piece + 1u) ^ sw) << 4), w1);
 }
 
 template <int NCHUNK, int SRC>
@@ -383,7 +364,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
 
     const uint32_t v_off = uint32_t(half ? 4 : 0) * kKvChunkBytes;   // this block's value columns inside a stage
 
-    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full[0]);   // [stage] at +8*stage
+    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full[0][0]);   // [stage][chunk] at +80*stage + 8*chunk
     const uint32_t bar_kv_free = ptx::smem_u32(&misc->bar_kv_free[0]);
     const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full[0]);
     const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full[0]);
@@ -395,7 +376,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     if (tid == 0) {
         trace_mark(a, 3, 0);
         for (int st = 0; st < 2; ++st) {
-            ptx::mbar_init(bar_kv_full + 8 * st, kNumLoaderWarps);
+            for (int g = 0; g < (NCHUNK + kGroupChunks - 1) / kGroupChunks; ++g)
+                ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps);
             ptx::mbar_init(bar_kv_free + 8 * st, 1);
             ptx::mbar_init(bar_s_full + 8 * st, 1);
             ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
@@ -487,11 +469,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 // the key resolved during the previous step has arrived by now: start pulling
                 // its records into L2 (using it earlier would stall on the block-table load)
                 if (!(a.dbg & 2)) loader_prefetch_l2<SRC>(key4, vm4, lane);
-                loader_store<NCHUNK, SRC>(kv_base + uint32_t(st) * L::kKvStageBytes, lw * 8, lane, regs);
                 if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_kv_full + 8 * st);
+                // chunk by chunk, so that the QK MMAs of this tile start while it is still being written
+#pragma unroll
+                for (int c = 0; c < NCHUNK; ++c) {
+                    loader_store_chunk<NCHUNK, SRC>(kv_base + uint32_t(st) * L::kKvStageBytes, lw * 8, lane, regs, c);
+                    if (c % kGroupChunks == kGroupChunks - 1 || c == NCHUNK - 1) {
+                        // one proxy fence and one arrival per group of chunks
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * (c / kGroupChunks));
+                    }
+                }
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
                 // this set is free again: loads of tile it+2, keys of tile it+5
                 if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
@@ -552,12 +541,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         }
                     }
                 };
-                // QK is issued in three groups of chunks; between groups a ready P goes first.
-                constexpr int kG1 = 3, kG2 = 6;
+                // QK is issued group by group as the loaders deliver them; between groups a ready P
+                // goes first.
+                constexpr int kNumGroups = (NCHUNK + kGroupChunks - 1) / kGroupChunks;
+                static_assert(kGroupChunks == 3 && kNumGroups == 3, "group dispatch below is written for 3 x 3 chunks");
                 auto issue_qk_group = [&](int it, int g) {
-                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, kG1>{});
-                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, kG1>{}, std::integral_constant<int, kG2>{});
-                    else issue_qk_range(it, std::integral_constant<int, kG2>{}, std::integral_constant<int, NCHUNK>{});
+                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 3>{});
+                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, 3>{}, std::integral_constant<int, 6>{});
+                    else issue_qk_range(it, std::integral_constant<int, 6>{}, std::integral_constant<int, NCHUNK>{});
                 };
                 auto issue_pv = [&](int it) {
                     const int st = it & 1;
@@ -588,31 +579,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         issue_pv(pv_next);
                         ++pv_next;
                         progress = true;
-                    } else if (qk_tile < ntiles && qk_tile <= pv_next + 1) {
-                        if (qk_chunk == 0) {
-                            if (ptx::mbar_test_wait(bar_kv_full + 8 * (qk_tile & 1), uint32_t(qk_tile >> 1) & 1u)) {
-                                ptx::tc_fence_after_sync();
-                                trace_mark(a, 1, 2 * qk_tile);
-                                issue_qk_group(qk_tile, 0);
-                                trace_mark(a, 1, 512 + 4 * qk_tile);
-                                qk_chunk = 1;
-                                progress = true;
-                            }
-                        } else {
-                            issue_qk_group(qk_tile, qk_chunk);
-                            trace_mark(a, 1, 512 + 4 * qk_tile + qk_chunk);
-                            if (++qk_chunk == 3) {
-                                ptx::mma_commit(bar_s_full + 8 * (qk_tile & 1));
-                                qk_chunk = 0;
-                                ++qk_tile;
-                            }
-                            progress = true;
+                    } else if (qk_tile < ntiles && qk_tile <= pv_next + 1 &&
+                               ptx::mbar_test_wait(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u)) {
+                        ptx::tc_fence_after_sync();
+                        if (qk_chunk == 0) trace_mark(a, 1, 2 * qk_tile);
+                        issue_qk_group(qk_tile, qk_chunk);
+                        if (++qk_chunk == kNumGroups) {
+                            ptx::mma_commit(bar_s_full + 8 * (qk_tile & 1));
+                            qk_chunk = 0;
+                            ++qk_tile;
                         }
+                        progress = true;
                     }
                     if (progress) {
                         polls = 0;
                     } else {
-                        __nanosleep(40);     // leave the issue slots to the warps doing the work
                         if (polls == 0) t_last = ptx::globaltimer_ns();
                         if ((++polls & 255u) != 0u || ptx::globaltimer_ns() - t_last <= kWaitTimeoutNs) continue;
                         report_timeout(a.status, (pv_next < qk_tile) ? kStatusWaitPFull : kStatusWaitKvFull, 1,
