@@ -55,7 +55,8 @@ class CombineParams(C.Structure):
     ]
 
 
-EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt",
+EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
+           "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
            "dsv4_attn_workspace_bytes", "hca_decode_fwd")
 
@@ -75,6 +76,7 @@ def _load() -> C.CDLL:
     lib.dsv4_attn_version.argtypes = []
     for name, st in (("dsv4_csa_sparse_decode_fwd", CsaSparseDecodeParams),
                      ("dsv4_csa_sparse_decode_simt", CsaSparseDecodeParams),
+                     ("dsv4_csa_sparse_decode_fwd_noalloc", CsaSparseDecodeParams),
                      ("dsv4_hca_dense_decode_fwd", HcaDenseDecodeParams),
                      ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
                      ("dsv4_attn_combine", CombineParams)):
@@ -85,6 +87,10 @@ def _load() -> C.CDLL:
     lib.dsv4_debug_set_flags.argtypes = [C.c_int]
     lib.dsv4_debug_set_trace.restype = None
     lib.dsv4_debug_set_trace.argtypes = [C.c_void_p]
+    lib.dsv4_noalloc_scratch_bytes.restype = C.c_int64
+    lib.dsv4_noalloc_scratch_bytes.argtypes = []
+    lib.dsv4_attn_last_error.restype = C.c_char_p
+    lib.dsv4_attn_last_error.argtypes = []
     lib.dsv4_attn_plan_splits.restype = C.c_int
     lib.dsv4_attn_plan_splits.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
     lib.dsv4_attn_workspace_bytes.restype = C.c_int64

@@ -71,7 +71,7 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros(4, dtype=torch.int32, device=device)
 
 
-def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace, max_len):
+def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace, max_len, need_workspace=True):
     _cuda_contig(q, "q", torch.bfloat16, 4)
     B, s_q, H, dq = q.shape
     _check(dq == D_QK, f"q last dim must be {D_QK}")
@@ -98,7 +98,7 @@ def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace,
         _cuda_contig(lse, "lse", torch.float32, 3)
         _check(tuple(lse.shape) == (B, s_q, H), "lse must be [B, s_q, H]")
     po = pl = None
-    if num_splits > 1:
+    if num_splits > 1 and need_workspace:
         if workspace is None:
             po, pl = alloc_workspace(rows, H, num_splits, q.device)
         else:
@@ -138,6 +138,38 @@ def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None
         partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
     fn = _lib.LIB.dsv4_csa_sparse_decode_fwd if impl == "mma" else _lib.LIB.dsv4_csa_sparse_decode_simt
     _rc(fn(C.byref(p), _stream(q.device)), "dsv4_csa_sparse_decode")
+    return out, lse
+
+
+def csa_sparse_decode_noalloc(q, kv_pool, block_table, indices, sm_scale, *, out, lse, num_splits, kv_len=None,
+                              topk_len=None, attn_sink=None, status=None):
+    """CSA sparse decode through the entry point that allocates nothing.
+
+    For hosts that cannot allocate device memory when they decode (all of HBM
+    already given to the KV-cache pool, an allocator they must not touch): the
+    split-KV partials go to a fixed 32 MiB array inside the library instead of
+    a caller workspace.  `out` and `lse` must be passed in, so that this wrapper
+    allocates nothing either.  Raises ValueError when
+    num_splits * B * s_q * H * 512 exceeds 8 Mi floats.  Calls share the array:
+    do not let two of them overlap on the GPU."""
+    _cuda_contig(indices, "indices", torch.int32, 3)
+    _check(out is not None and lse is not None, "out and lse must be provided by the caller")
+    _check(num_splits is not None, "num_splits must be given")
+    B, s_q, H, num_splits, out, lse, _, _ = _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, None,
+                                                    indices.shape[-1], need_workspace=False)
+    topk = indices.shape[-1]
+    p = _lib.CsaSparseDecodeParams(
+        B=B, s_q=s_q, H=H, topk=topk, max_pages=block_table.shape[1], num_splits=num_splits,
+        sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
+        q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), indices=_ptr(indices),
+        kv_len=_ptr(kv_len), topk_len=_ptr(topk_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
+        partial_o=None, partial_lse=None, status=_ptr(status))
+    rc = _lib.LIB.dsv4_csa_sparse_decode_fwd_noalloc(C.byref(p), _stream(q.device))
+    if rc != 0:
+        why = _lib.LIB.dsv4_attn_last_error().decode()
+        if rc == 1:
+            raise ValueError(f"dsv4_csa_sparse_decode_fwd_noalloc rejected the call: {why}")
+        raise Dsv4Error(f"dsv4_csa_sparse_decode_fwd_noalloc failed: cudaError={rc} {why}")
     return out, lse
 
 

@@ -173,6 +173,34 @@ bool fill_hca(const Dsv4HcaDenseDecodeParams* p, DecodeArgs& a) {
     return true;
 }
 
+// Split-KV scratch for the entry point that must not allocate: partial outputs
+// followed by partial LSEs, in device memory that belongs to the loaded library
+// image.  32 MiB + 64 KiB per GPU that loads the library, held until exit.
+constexpr size_t kNoAllocPartialFloats = size_t(8) << 20;                 // 8 Mi floats = 32 MiB of partial outputs
+constexpr size_t kNoAllocLseFloats = kNoAllocPartialFloats / 512;         // one LSE per 512-wide partial row
+__device__ __align__(256) float g_noalloc_scratch[kNoAllocPartialFloats + kNoAllocLseFloats];
+
+// Device address of the scratch array on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could
+// use, so the address is asked for once per device and kept.
+cudaError_t noalloc_scratch(float** ptr) {
+    static float* per_device[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (per_device[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        per_device[dev] = static_cast<float*>(p);
+    }
+    *ptr = per_device[dev];
+    return cudaSuccess;
+}
+
+thread_local const char* t_last_error = "";
+
 // Decode (+ merge when split) for the packed-entry sources.
 template <int SRC>
 int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
@@ -202,6 +230,42 @@ extern "C" void dsv4_debug_set_trace(void* device_buffer) {
 extern "C" int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream) {
     DecodeArgs a;
     if (!fill_csa(p, a)) return int(cudaErrorInvalidValue);
+    return decode_fwd<kSrcCsa>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" const char* dsv4_attn_last_error(void) { return t_last_error; }
+
+extern "C" int64_t dsv4_noalloc_scratch_bytes(void) {
+    return int64_t(sizeof(float) * (kNoAllocPartialFloats + kNoAllocLseFloats));
+}
+
+extern "C" int dsv4_csa_sparse_decode_fwd_noalloc(const Dsv4CsaSparseDecodeParams* p, void* stream) {
+    DecodeArgs a;
+    t_last_error = "";
+    if (p == nullptr) { t_last_error = "null parameter block";  return int(cudaErrorInvalidValue); }
+    // the caller's workspace pointers are not used here; validate the rest as usual
+    Dsv4CsaSparseDecodeParams q = *p;
+    static float dummy;                       // stands in for the workspace during host-side validation only
+    if (q.num_splits > 1) { q.partial_o = reinterpret_cast<float*>(uintptr_t(256));  q.partial_lse = &dummy; }
+    if (!fill_csa(&q, a)) { t_last_error = "invalid argument";  return int(cudaErrorInvalidValue); }
+    if (a.num_splits > 1) {
+        const size_t rows = size_t(a.B) * a.s_q;
+        const size_t need_o = size_t(a.num_splits) * rows * a.H * 512;
+        const size_t need_l = size_t(a.num_splits) * rows * a.H;
+        if (need_o > kNoAllocPartialFloats || need_l > kNoAllocLseFloats) {
+            t_last_error = "num_splits * B * s_q * H * 512 partial floats exceed the built-in scratch "
+                           "(8 Mi floats = 32 MiB): use fewer splits or rows, or the entry point that takes a workspace";
+            return int(cudaErrorInvalidValue);
+        }
+        float* scratch = nullptr;
+        const cudaError_t e = noalloc_scratch(&scratch);
+        if (e != cudaSuccess) { t_last_error = "cudaGetSymbolAddress failed";  return int(e); }
+        a.partial_o = scratch;
+        a.partial_lse = scratch + kNoAllocPartialFloats;
+    } else {
+        a.partial_o = nullptr;
+        a.partial_lse = nullptr;
+    }
     return decode_fwd<kSrcCsa>(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -79,6 +79,41 @@ typedef struct Dsv4CsaSparseDecodeParams {
 int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream);
 
 /*
+ * CSA sparse decode for callers that cannot allocate device memory.  No
+ * counterpart in the reference.
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they
+ * decode: a serving engine that has handed all of HBM to its KV-cache pool, a
+ * plug-in loaded into a process whose allocator it must not touch, code running
+ * inside a region where allocation is forbidden.  With num_splits > 1 the
+ * ordinary entry point needs a caller-provided workspace for the split
+ * partials; this one keeps that workspace inside the library image instead: a
+ * fixed device array of 32 MiB (+ 64 KiB for the partial LSEs) that every GPU
+ * loading the library holds until the process exits.  p->partial_o and
+ * p->partial_lse are ignored; everything else means what it means for
+ * dsv4_csa_sparse_decode_fwd, and the results are identical.
+ *
+ * Limit: num_splits * B * s_q * H * 512 <= 8 Mi floats (for example 8 splits
+ * of 16 rows of 128 heads).  Larger requests are rejected with
+ * cudaErrorInvalidValue before anything is enqueued, and
+ * dsv4_attn_last_error() says why.  The call itself allocates nothing and frees
+ * nothing.
+ *
+ * The first call on a device looks the array's device address up (once per
+ * device, with that device current); make that first call outside any stream
+ * capture.  All calls share the one array: the decode kernel overwrites every
+ * partial the merge reads, so nothing has to be cleared between calls, but two
+ * calls that overlap on the GPU (different streams) race on it - serialise them.
+ */
+int dsv4_csa_sparse_decode_fwd_noalloc(const Dsv4CsaSparseDecodeParams* p, void* stream);
+
+/* Size in bytes of the built-in scratch used by the entry point above. */
+int64_t dsv4_noalloc_scratch_bytes(void);
+
+/* Why the calling thread's last call to an entry point that sets it was rejected ("" if it was not). */
+const char* dsv4_attn_last_error(void);
+
+/*
  * HCA dense decode.  Query token j of request b attends to every compressed
  * entry [0, kv_len[b][j]) of the request (through the block table) followed by
  * the first win_len[b][j] rows of the request's sliding-window buffer, in one
