@@ -374,7 +374,7 @@ def run_ours(args):
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(kind, args.workload)
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=args.out, flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -403,7 +403,17 @@ def run_reference(args):
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement (oracle port) of the reference's PyTorch decode path on a bounded sample; the reference's own CUDA decode kernel is not run: as committed it stalls on an mbarrier and then traps",
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=args.out, flush=True)
+
+
+def _claim_stdout():
+    """Keep stdout for the one JSON line: libraries (NCCL's version banner, for
+    one) write to file descriptor 1, so send that to stderr for the duration of
+    the run and return a handle on the real stdout."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
 
 
 def main():
@@ -416,6 +426,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.out = _claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:
