@@ -56,9 +56,19 @@ class CombineParams(C.Structure):
 
 
 EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
-           "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error",
+           "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error", "dsv4_csa_compress_reduce_fwd",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
            "dsv4_attn_workspace_bytes", "hca_decode_fwd")
+
+
+class CsaCompressReduceParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("n", C.c_int32), ("c_out", C.c_int32), ("m", C.c_int32),
+        ("C_a", C.c_void_p), ("C_b", C.c_void_p), ("Z_a", C.c_void_p), ("Z_b", C.c_void_p),
+        ("B_a", C.c_void_p), ("B_b", C.c_void_p), ("out", C.c_void_p),
+        ("stride_C_b", C.c_int64), ("stride_C_n", C.c_int64), ("stride_out_b", C.c_int64),
+        ("stride_out_blk", C.c_int64),
+    ]
 
 
 def _load() -> C.CDLL:
@@ -79,6 +89,7 @@ def _load() -> C.CDLL:
                      ("dsv4_csa_sparse_decode_fwd_noalloc", CsaSparseDecodeParams),
                      ("dsv4_hca_dense_decode_fwd", HcaDenseDecodeParams),
                      ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
+                     ("dsv4_csa_compress_reduce_fwd", CsaCompressReduceParams),
                      ("dsv4_attn_combine", CombineParams)):
         fn = getattr(lib, name)
         fn.restype = C.c_int

@@ -249,3 +249,31 @@ def hca_decode_fwd(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink_logits, s
         C.c_float(float(sm_scale)), B, n_h, c, n_rope, int(M_cur), int(swa_len), _stream(Q.device))
     _rc(rc, "hca_decode_fwd")
     return O
+
+
+def csa_compress_reduce_fwd(C_a, C_b, Z_a, Z_b, B_a, B_b, m, *, out=None):
+    """CSA compressor, second pass.  Same arguments, checks and result as the
+    reference's csa_compress_reduce_fwd (csa/interface.h:21-85, bound in
+    csa/pybind.cpp:5-17): four BF16 streams [B, n, c_out], two BF16 biases
+    [m, c_out], returns BF16 [B, n/m, c_out] allocated here."""
+    for name, t in (("C_a", C_a), ("C_b", C_b), ("Z_a", Z_a), ("Z_b", Z_b)):
+        _check(t.is_cuda, "all inputs must be on cuda")
+        _check(t.dtype == torch.bfloat16, f"{name} must be bf16")
+        _check(t.is_contiguous(), "input streams must be contiguous")
+    _check(B_a.dtype == torch.bfloat16 and B_b.dtype == torch.bfloat16, "biases must be bf16")
+    _check(B_a.is_cuda and B_b.is_cuda and B_a.is_contiguous() and B_b.is_contiguous(), "biases must be contiguous cuda tensors")
+    _check(C_a.dim() == 3 and C_a.shape == C_b.shape == Z_a.shape == Z_b.shape,
+           "C_a/C_b/Z_a/Z_b must all be [B, n, c_out] and equal-shaped")
+    _check(B_a.dim() == 2 and B_a.shape[0] == m and B_b.dim() == 2 and B_b.shape[0] == m, "B_a/B_b must be [m, c_out]")
+    B, n, c_out = C_a.shape
+    _check(B_a.shape[1] == c_out and B_b.shape[1] == c_out, "B_a/B_b last dim must match c_out")
+    _check(n % m == 0, "n must be divisible by m")
+    _check(m == 4, f"[dsv4-csa] unsupported m={m} (only m=4 instantiated)")
+    if out is None:
+        out = torch.empty(B, n // m, c_out, dtype=torch.bfloat16, device=C_a.device)
+    p = _lib.CsaCompressReduceParams(
+        B=B, n=n, c_out=c_out, m=m, C_a=_ptr(C_a), C_b=_ptr(C_b), Z_a=_ptr(Z_a), Z_b=_ptr(Z_b),
+        B_a=_ptr(B_a), B_b=_ptr(B_b), out=_ptr(out), stride_C_b=n * c_out, stride_C_n=c_out,
+        stride_out_b=(n // m) * c_out, stride_out_blk=c_out)
+    _rc(_lib.LIB.dsv4_csa_compress_reduce_fwd(C.byref(p), _stream(C_a.device)), "dsv4_csa_compress_reduce_fwd")
+    return out

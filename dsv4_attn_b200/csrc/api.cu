@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "combine.cuh"
+#include "compress_reduce.cuh"
 #include "decode_kernel.cuh"
 #include "decode_simt.cuh"
 
@@ -396,4 +397,35 @@ extern "C" int hca_decode_fwd(const void* Q,
         e = launch_combine(cb, s);
     }
     return int(e);
+}
+
+
+extern "C" int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream) {
+    if (p == nullptr || p->B <= 0 || p->n <= 0 || p->c_out <= 0 || p->m <= 0) return int(cudaErrorInvalidValue);
+    if (p->n % p->m != 0) return int(cudaErrorInvalidValue);
+    if (p->C_a == nullptr || p->C_b == nullptr || p->Z_a == nullptr || p->Z_b == nullptr || p->B_a == nullptr ||
+        p->B_b == nullptr || p->out == nullptr)
+        return int(cudaErrorInvalidValue);
+    if (p->m != 4) return int(cudaErrorNotSupported);      // as in the reference, only m = 4 is instantiated
+    CompressReduceArgs a{};
+    a.B = p->B;  a.n = p->n;  a.n_blocks = p->n / p->m;  a.c_out = p->c_out;  a.m = p->m;
+    a.C_a = static_cast<const __nv_bfloat16*>(p->C_a);  a.C_b = static_cast<const __nv_bfloat16*>(p->C_b);
+    a.Z_a = static_cast<const __nv_bfloat16*>(p->Z_a);  a.Z_b = static_cast<const __nv_bfloat16*>(p->Z_b);
+    a.B_a = static_cast<const __nv_bfloat16*>(p->B_a);  a.B_b = static_cast<const __nv_bfloat16*>(p->B_b);
+    a.out = static_cast<__nv_bfloat16*>(p->out);
+    a.stride_c_b = p->stride_C_b;  a.stride_c_n = p->stride_C_n;
+    a.stride_out_b = p->stride_out_b;  a.stride_out_blk = p->stride_out_blk;
+    const bool vec = (p->c_out % 8 == 0) && (p->stride_C_b % 8 == 0) && (p->stride_C_n % 8 == 0) &&
+                     (p->stride_out_b % 8 == 0) && (p->stride_out_blk % 8 == 0) && aligned(p->C_a, 16) &&
+                     aligned(p->C_b, 16) && aligned(p->Z_a, 16) && aligned(p->Z_b, 16) && aligned(p->B_a, 16) &&
+                     aligned(p->B_b, 16) && aligned(p->out, 16);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t items = int64_t(a.B) * a.n_blocks * (vec ? a.c_out / 8 : a.c_out);
+    const int64_t want = (items + kCompressThreads - 1) / kCompressThreads;
+    const int blocks = int(want < int64_t(sms) * 8 ? (want > 0 ? want : 1) : int64_t(sms) * 8);   // a whole number of waves when large
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (vec) compress_reduce_kernel<4, 8><<<blocks, kCompressThreads, 0, s>>>(a);
+    else compress_reduce_kernel<4, 1><<<blocks, kCompressThreads, 0, s>>>(a);
+    return int(cudaGetLastError());
 }

@@ -214,6 +214,37 @@ int hca_decode_fwd(const void* Q,
                    void* stream);
 
 /*
+ * CSA compressor, second pass (the cache-write side of the sparse path): for
+ * every output block and channel a softmax over 2m gating logits - m own rows
+ * (a-side) and the m rows of the previous block (b-side), each plus a
+ * per-position bias - weights the 2m value rows; block 0 has no b-side.
+ * Field for field the reference's CsaCompressReduceParams (csa/params.h:12-39)
+ * behind the reference's csa_compress_reduce_fwd (csa/interface.h:21-85,
+ * kernel csa/sm100/kernel.cuh:25-102), with 64-bit strides and the output
+ * supplied by the caller.  All tensors BF16, strides in elements.  Returns
+ * cudaErrorNotSupported for m != 4 (the reference instantiates only m = 4).
+ */
+typedef struct Dsv4CsaCompressReduceParams {
+    int32_t B;              /* batch */
+    int32_t n;              /* sequence length, divisible by m */
+    int32_t c_out;          /* channels */
+    int32_t m;              /* compression rate */
+    const void* C_a;        /* bf16 [B, n, c_out] */
+    const void* C_b;
+    const void* Z_a;
+    const void* Z_b;
+    const void* B_a;        /* bf16 [m, c_out] */
+    const void* B_b;
+    void*       out;        /* bf16 [B, n/m, c_out] */
+    int64_t stride_C_b;     /* batch stride of the four input streams */
+    int64_t stride_C_n;     /* row stride of the four input streams */
+    int64_t stride_out_b;
+    int64_t stride_out_blk;
+} Dsv4CsaCompressReduceParams;
+
+int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream);
+
+/*
  * Plain-SIMT validation kernels: the same three operations computed without
  * tensor cores, one head per thread block.  They exist so that large cases can
  * be cross-checked on the device; they are slow and are not the product path.

@@ -1,9 +1,10 @@
 #!/usr/bin/env python3
-"""TEST INFRASTRUCTURE ONLY.  Compile the reference project's split-KV merge
-kernel (hca/sm100/combine.cu) from its own sources, where they lie, into
-oracle/_ref/libref_combine.so together with the small C shim in this folder.
+"""TEST INFRASTRUCTURE ONLY.  Compile two of the reference project's kernels from
+its own sources, where they lie, together with the small C shims in this folder:
+the split-KV merge (hca/sm100/combine.cu -> oracle/_ref/libref_combine.so) and
+the CSA compressor reduce (csa/sm100/kernel.cuh -> oracle/_ref/libref_csa.so).
 
-Only the merge kernel is built: it has no spin waits and is safe to run.  The
+Only these two are built: they have no spin waits and are safe to run.  The
 reference's decode kernel is not built or run (as committed it stalls on an
 mbarrier and then traps, hca/sm100/kernel.cu:112-123 with
 hca/sm100/helpers.h:29,183-206).
@@ -36,6 +37,14 @@ def build(reference: Path, quiet: bool = False) -> Path | None:
     if not quiet:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)
+    csa = reference / "csa" / "sm100" / "kernel.cuh"
+    if csa.exists():
+        cmd = [nvcc, "-std=c++17", "-O3", "--use_fast_math", "-gencode", "arch=compute_100a,code=sm_100a",
+               "-shared", "-Xcompiler", "-fPIC", "-I", str(reference / "csa"),
+               "-o", str(OUT_DIR / "libref_csa.so"), str(HERE / "ref_csa_shim.cu")]
+        if not quiet:
+            print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
     return OUT
 
 

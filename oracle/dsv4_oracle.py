@@ -271,6 +271,49 @@ def combine(partial_o, partial_lse2, sink=None):
     return f32_to_bf16_bits(out.astype(np.float32)), lse
 
 
+# ── CSA compressor, second pass ─────────────────────────────────────────
+
+def compress_reduce(C_a, C_b, Z_a, Z_b, B_a, B_b, m):
+    """Softmax-gated reduce of the CSA compressor (cache-write side).
+
+    C_a, C_b, Z_a, Z_b [B, n, c] float32 (BF16-representable), B_a, B_b [m, c].
+    Block i combines its own m rows (a-side) with the m rows of block i-1
+    (b-side): out[i] = sum_j softmax_j(Z)[j] * C[j] over the 2m positions, per
+    channel; block 0 has no b-side.  Restates bench/bench/reference.py:139-155
+    (the part of compressor_overlap after the projections) and the kernel
+    csa/sm100/kernel.cuh:25-102.  Returns BF16 bits [B, n/m, c]."""
+    B, n, c = C_a.shape
+    nb = n // m
+    r = lambda x: np.asarray(x, np.float32).reshape(B, nb, m, c)
+    Ca, Cb, Za, Zb = r(C_a), r(C_b), r(Z_a), r(Z_b)
+    Cb_s = np.concatenate([np.zeros((B, 1, m, c), np.float32), Cb[:, :-1]], axis=1)
+    Zb_s = np.concatenate([np.full((B, 1, m, c), -np.inf, np.float32), Zb[:, :-1]], axis=1)
+    Z = np.concatenate([Za + np.asarray(B_a, np.float32), Zb_s + np.asarray(B_b, np.float32)], axis=2)
+    Cc = np.concatenate([Ca, Cb_s], axis=2)
+    zmax = Z.max(axis=2, keepdims=True)
+    e = np.exp(Z - zmax)
+    out = (e * Cc).sum(axis=2) / e.sum(axis=2)
+    return f32_to_bf16_bits(out.astype(np.float32))
+
+
+@dataclass
+class CompressCase:
+    C_a: np.ndarray
+    C_b: np.ndarray
+    Z_a: np.ndarray
+    Z_b: np.ndarray
+    B_a: np.ndarray
+    B_b: np.ndarray
+    m: int
+
+
+def make_compress_case(seed, B, n, c_out, m=4) -> CompressCase:
+    rng = np.random.default_rng(seed)
+    rn = lambda *s: bf16_round(rng.standard_normal(s, dtype=np.float32))
+    return CompressCase(rn(B, n, c_out), rn(B, n, c_out), rn(B, n, c_out) * np.float32(2), rn(B, n, c_out) * np.float32(2),
+                        rn(m, c_out), rn(m, c_out), m)
+
+
 # ── the reference's own cache layout (448 e4m3 + 7 UE8M0 + 64 bf16) ─────
 
 def quantize_ue8m0(x: np.ndarray, tile: int = 64):

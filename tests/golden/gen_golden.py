@@ -120,6 +120,23 @@ def gen_ref_layout(ref, name, **kw):
     print(name, o_deq.shape)
 
 
+def gen_compress(ref, name, **kw):
+    """compressor_overlap (reference.py:125-155) fed with selection matrices as
+    weights, so that its projections reproduce the four given streams exactly
+    and only its gated reduce (Eqs 11-12) is exercised."""
+    import torch
+    c = orc.make_compress_case(**kw)
+    B, n, co = c.C_a.shape
+    H = torch.from_numpy(np.concatenate([c.C_a, c.C_b, c.Z_a, c.Z_b], axis=-1))       # [B, n, 4*co]
+    sel = lambda k: torch.cat([torch.eye(co) if i == k else torch.zeros(co, co) for i in range(4)], dim=0)
+    w = ref.CompressorWeightsOverlap(W_a_KV=sel(0), W_b_KV=sel(1), W_a_Z=sel(2), W_b_Z=sel(3),
+                                     B_a=torch.from_numpy(c.B_a), B_b=torch.from_numpy(c.B_b))
+    out = ref.compressor_overlap(H, w, c.m)
+    np.savez_compressed(HERE / f"{name}.npz", out=bf16_bits(out),
+                        inputs_sha=sha(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b), kwargs=repr(kw))
+    print(name, tuple(out.shape))
+
+
 # The cases; tests/test_oracle.py rebuilds the inputs from the same kwargs.
 CSA_CASES = {
     "csa_cfg0": dict(seed=0, B=2, s_q=1, H=16, n_entries=1024, topk=256),
@@ -128,6 +145,10 @@ CSA_CASES = {
 HCA_CASES = {
     "hca_small": dict(seed=2, B=2, s_q=1, H=16, kv_len=[150, 70], win_len=[128, 5], with_sink=True),
     "hca_nosink": dict(seed=3, B=2, s_q=2, H=8, kv_len=[64, 1], win_len=[2, 128]),
+}
+COMPRESS_CASES = {
+    "csa_compress": dict(seed=6, B=2, n=64, c_out=128),
+    "csa_compress_odd": dict(seed=7, B=1, n=12, c_out=20),
 }
 REF_CASES = {
     "ref_layout": dict(seed=4, B=1, H=128, M_cur=192, swa_len=64),
@@ -149,6 +170,8 @@ def main() -> int:
         gen_hca(ref, name, **kw)
     for name, kw in REF_CASES.items():
         gen_ref_layout(ref, name, **kw)
+    for name, kw in COMPRESS_CASES.items():
+        gen_compress(ref, name, **kw)
     return 0
 
 

@@ -241,3 +241,47 @@ def test_combine_kernel_vs_reference_kernel(lib):
             a, b = out.float(), out_ref.float()
             assert torch.allclose(a, b, rtol=2 ** -7, atol=1e-6), (S, B, H, (a - b).abs().max().item())
             assert torch.allclose(lse, lse_ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["csa_compress", "csa_compress_odd"])
+def test_compress_reduce_vs_reference_outputs(lib, name):
+    z, kw = golden(name)
+    c = orc.make_compress_case(**kw)
+    bf = lambda a: gu.dev(a, torch.bfloat16)
+    out = lib.csa_compress_reduce_fwd(bf(c.C_a), bf(c.C_b), bf(c.Z_a), bf(c.Z_b), bf(c.B_a), bf(c.B_b), c.m)
+    torch.cuda.synchronize()
+    got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    from tests.test_oracle import bf16_ulp_diff
+    assert bf16_ulp_diff(got, z["out"]).max() <= 1
+    assert bf16_ulp_diff(got, orc.compress_reduce(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b, c.m)).max() <= 1
+
+
+def test_compress_reduce_vs_reference_kernel_and_errors(lib):
+    """Against the reference project's own kernel (csa/sm100/kernel.cuh, built
+    from the reference sources into oracle/_ref) at a realistic size, plus the
+    argument checks of the reference's operator (csa/interface.h:30-52,79-83)."""
+    import ctypes as C
+    c = orc.make_compress_case(seed=61, B=2, n=4096, c_out=512)
+    bf = lambda a: gu.dev(a, torch.bfloat16)
+    t = [bf(x) for x in (c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b)]
+    out = lib.csa_compress_reduce_fwd(*t, 4)
+    want = orc.compress_reduce(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b, 4)
+    from tests.test_oracle import bf16_ulp_diff
+    assert bf16_ulp_diff(out.view(torch.int16).cpu().numpy().view(np.uint16), want).max() <= 1
+    so = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "libref_csa.so"
+    if so.exists():
+        ref = C.CDLL(str(so))
+        ref.ref_csa_compress_reduce.restype = C.c_int
+        ref.ref_csa_compress_reduce.argtypes = [C.c_int] * 4 + [C.c_void_p] * 8
+        out_ref = torch.empty_like(out)
+        assert ref.ref_csa_compress_reduce(2, 4096, 512, 4, *[x.data_ptr() for x in t], out_ref.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        a = out.view(torch.int16).cpu().numpy().view(np.uint16)
+        b = out_ref.view(torch.int16).cpu().numpy().view(np.uint16)
+        assert bf16_ulp_diff(a, b).max() <= 1 and (a == b).mean() > 0.99
+    with pytest.raises(ValueError, match="unsupported m"):
+        lib.csa_compress_reduce_fwd(*[x if x.dim() == 3 else x[:2].contiguous() for x in t], 2)
+    with pytest.raises(ValueError, match="bf16"):
+        lib.csa_compress_reduce_fwd(t[0].float(), *t[1:], 4)
+    with pytest.raises(ValueError, match="divisible"):
+        lib.csa_compress_reduce_fwd(*[x[:, :4095].contiguous() if x.dim() == 3 else x for x in t], 4)

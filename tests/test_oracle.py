@@ -156,3 +156,13 @@ def test_empty_and_padding_rows():
     idx2[1, 0] = np.roll(idx2[1, 0], 7)
     out2, lse2 = orc.csa_sparse_decode(case.q, case.pool, case.block_table, idx2, case.sm_scale)
     assert bf16_ulp_diff(out2[1], out[1]).max() <= 1
+
+
+@pytest.mark.parametrize("name", ["csa_compress", "csa_compress_odd"])
+def test_compress_reduce_oracle_vs_reference(name):
+    z, kw = load(name)
+    c = orc.make_compress_case(**kw)
+    assert sha(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b) == str(z["inputs_sha"])
+    out = orc.compress_reduce(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b, c.m)
+    assert out.shape == z["out"].shape
+    assert bf16_ulp_diff(out, z["out"]).max() <= 1
