@@ -1,0 +1,74 @@
+"""Timing beside the reference project's own Blackwell-built kernels (the two
+that are safe to run: the split-KV merge and the CSA compressor reduce, built
+from the reference sources into oracle/_ref).  Same buffers, same L2 discipline
+(a 512 MiB write between launches), CUDA events.  Prints the numbers that
+profiles/ quotes and checks that this library is not slower."""
+import ctypes as C
+from pathlib import Path
+
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+REF = Path(__file__).resolve().parents[1] / "oracle" / "_ref"
+
+
+def _time(fn, flush, iters=10, warmup=3):
+    for _ in range(warmup):
+        flush.zero_(); fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for s, e in ev:
+        flush.zero_(); s.record(); fn(); e.record()
+    torch.cuda.synchronize()
+    t = sorted(s.elapsed_time(e) for s, e in ev)
+    return t[len(t) // 2] * 1e3        # median, microseconds
+
+
+@pytest.fixture(scope="module")
+def env():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import dsv4_attn_b200 as lib
+    return lib, torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+
+def test_merge_kernel_speed(env):
+    lib, flush = env
+    if not (REF / "libref_combine.so").exists():
+        pytest.skip("oracle/_ref not built")
+    ref = C.CDLL(str(REF / "libref_combine.so"))
+    ref.ref_hca_combine.restype = C.c_int
+    ref.ref_hca_combine.argtypes = [C.c_int] * 3 + [C.c_void_p] * 6
+    S, N, H = 8, 256, 128                      # the 8-split, 128 x 2 query-token configuration
+    po = torch.randn(S, N, H, 512, device="cuda")
+    pl = torch.randn(S, N, H, device="cuda") * 3
+    out = torch.empty(N, H, 512, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(N, H, device="cuda")
+    ours = _time(lambda: lib.combine(po, pl, out=out, lse=lse), flush)
+    theirs = _time(lambda: ref.ref_hca_combine(N, H, S, po.data_ptr(), pl.data_ptr(), out.data_ptr(), lse.data_ptr(), None, None), flush)
+    gb = (po.numel() * 4 + pl.numel() * 4 + out.numel() * 2 + lse.numel() * 4) / 1e9
+    print(f"\nmerge S={S} N={N} H={H}: ours {ours:.1f} us ({gb / ours * 1e6:.0f} GB/s), reference kernel {theirs:.1f} us "
+          f"({gb / theirs * 1e6:.0f} GB/s)")
+    assert ours <= theirs * 1.10
+
+
+def test_compress_reduce_kernel_speed(env):
+    lib, flush = env
+    if not (REF / "libref_csa.so").exists():
+        pytest.skip("oracle/_ref not built")
+    ref = C.CDLL(str(REF / "libref_csa.so"))
+    ref.ref_csa_compress_reduce.restype = C.c_int
+    ref.ref_csa_compress_reduce.argtypes = [C.c_int] * 4 + [C.c_void_p] * 8
+    B, n, c = 1, 65536, 512
+    t = [torch.randn(B, n, c, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    b = [torch.randn(4, c, device="cuda").to(torch.bfloat16) for _ in range(2)]
+    out = torch.empty(B, n // 4, c, dtype=torch.bfloat16, device="cuda")
+    ours = _time(lambda: lib.csa_compress_reduce_fwd(*t, *b, 4, out=out), flush)
+    theirs = _time(lambda: ref.ref_csa_compress_reduce(B, n, c, 4, *[x.data_ptr() for x in t], *[x.data_ptr() for x in b],
+                                                       out.data_ptr(), None), flush)
+    gb = (4 * B * n * c * 2 + out.numel() * 2) / 1e9
+    print(f"\ncompress-reduce B={B} n={n} c={c}: ours {ours:.1f} us ({gb / ours * 1e6:.0f} GB/s), reference kernel "
+          f"{theirs:.1f} us ({gb / theirs * 1e6:.0f} GB/s)")
+    assert ours <= theirs * 1.10
