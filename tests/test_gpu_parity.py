@@ -285,3 +285,45 @@ def test_compress_reduce_vs_reference_kernel_and_errors(lib):
         lib.csa_compress_reduce_fwd(t[0].float(), *t[1:], 4)
     with pytest.raises(ValueError, match="divisible"):
         lib.csa_compress_reduce_fwd(*[x[:, :4095].contiguous() if x.dim() == 3 else x for x in t], 4)
+
+
+def test_more_than_128_heads_and_partial_head_group(lib):
+    """H = 192: two groups of 128 head rows, the second only half used."""
+    case = orc.make_csa_case(seed=71, B=2, s_q=1, H=192, n_entries=300, topk=256)
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale)
+    for splits in (1, 2):
+        out, lse = run_csa(lib, case, num_splits=splits)
+        gu.check_out(out, want_out, f"H=192 splits={splits}")
+        gu.check_lse(lse, want_lse, f"H=192 splits={splits}")
+
+
+def test_topk_len_and_more_splits_than_tiles(lib):
+    """Ragged index lists padded to a common top-k with `topk_len`: only the
+    leading slots are read, and splits beyond the last tile come out empty."""
+    case = orc.make_csa_case(seed=72, B=3, s_q=1, H=32, n_entries=[40, 700, 129], topk=512, ragged=True)
+    topk_len = np.array([[40], [512], [129]], np.int32)
+    case.indices[1, 0, 300:] = np.where(np.arange(212) % 2 == 0, -1, case.indices[1, 0, 300:])   # holes inside the prefix
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale,
+                                               kv_len=case.kv_len)
+    args = gu.csa_to_dev(case)
+    for splits in (1, 4, 8):
+        st = lib.new_status("cuda")
+        out, lse = lib.csa_sparse_decode(**args, topk_len=gu.dev(topk_len), num_splits=splits, status=st)
+        torch.cuda.synchronize()
+        assert st.cpu().tolist() == [0, 0, 0, 0]
+        gu.check_out(gu.out_to_f32(out), want_out, f"topk_len splits={splits}")
+        gu.check_lse(lse.cpu().numpy(), want_lse, f"topk_len splits={splits}")
+
+
+def test_reference_entry_point_split_path(lib):
+    """hca_decode_fwd with a context long enough that the library splits it
+    (B=1 leaves most SMs idle otherwise) and merges inside the same call."""
+    c = orc.make_ref_layout_case(seed=73, B=1, H=128, M_cur=1920, swa_len=128)
+    want, _ = orc.hca_decode_ref_layout(c.Q, c.Kc, c.Kc_s, c.Kc_rope, c.Kswa, c.Kswa_s, c.Kswa_rope, c.sink, c.sm_scale)
+    d = gu.dev
+    assert lib.plan_splits(1, 128, 2048) > 1
+    O = lib.hca_decode_fwd(d(c.Q, torch.bfloat16), d(c.Kc), d(c.Kc_s), d(c.Kc_rope, torch.bfloat16),
+                           d(c.Kswa), d(c.Kswa_s), d(c.Kswa_rope, torch.bfloat16), d(c.sink), c.sm_scale,
+                           M_cur=1920, swa_len=128)
+    torch.cuda.synchronize()
+    gu.check_out(gu.out_to_f32(O), want, "hca_decode_fwd split")
