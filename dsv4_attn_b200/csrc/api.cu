@@ -11,6 +11,7 @@
 #include "combine.cuh"
 #include "compress_reduce.cuh"
 #include "decode_kernel.cuh"
+#include "decode_pair.cuh"
 #include "decode_simt.cuh"
 
 namespace dsv4 {
@@ -74,15 +75,25 @@ cudaError_t ensure_smem(Kernel kernel, int bytes, bool* done_per_device) {
 
 template <int NCHUNK, int SRC>
 cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
-    static bool done[kMaxDevices] = {};
-    constexpr int smem = SmemLayout<NCHUNK>::kTotal;
-    cudaError_t e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
-    if (e != cudaSuccess) return e;
-    e = make_q_map(&a.q_map, a.q, int64_t(rows) * a.H, NCHUNK * 64);
+    cudaError_t e = make_q_map(&a.q_map, a.q, int64_t(rows) * a.H, NCHUNK * 64);
     if (e != cudaSuccess) return e;
     const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(2 * head_groups, rows, a.num_splits);
-    decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
+    if (!(g_dbg & 16)) {
+        // product path: each block computes the whole QK product for its half of the value columns
+        static bool done[kMaxDevices] = {};
+        constexpr int smem = SmemLayout<NCHUNK>::kTotal;
+        e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
+        if (e != cudaSuccess) return e;
+        decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
+    } else {
+        // evaluated alternative, kept selectable for measurements: cluster pairs that split the
+        // query/key columns and exchange halves of S through distributed shared memory
+        static bool done[kMaxDevices] = {};
+        e = ensure_smem(pair::decode_pair_kernel<NCHUNK, SRC>, pair::kSmemTotal, done);
+        if (e != cudaSuccess) return e;
+        pair::decode_pair_kernel<NCHUNK, SRC><<<grid, kNumThreads, pair::kSmemTotal, stream>>>(a);
+    }
     return cudaGetLastError();
 }
 

@@ -81,6 +81,54 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_
     }
 }
 
+// ── thread-block clusters / distributed shared memory ───────────────────
+// Rendezvous of every thread of every block in the cluster (no time limit: it
+// must be reached unconditionally).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this block's shared-memory location `saddr` in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void sts_cluster_v4(uint32_t caddr, uint4 v) {
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// Arrive on a barrier of another block of the cluster; this thread's earlier
+// stores to that block's shared memory are visible to whoever sees the arrival.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cbar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cbar) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait on a local barrier whose arrivals come from another block.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint64_t timeout_ns) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((++polls & 63u) == 0u) {
+            if (globaltimer_ns() - t0 > timeout_ns) return false;
+        }
+    }
+}
+
 // ── fences ──────────────────────────────────────────────────────────────
 // Make this thread's generic-proxy shared-memory writes visible to the async
 // proxy (tcgen05.mma operand reads).

@@ -263,8 +263,9 @@ int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream);
 void dsv4_debug_set_trace(void* device_buffer);
 
 /* Profiling aid: pipeline experiment switches for the next launches (0 = product
- * behaviour).  bit1: no L2 prefetch of the cache entries.  No counterpart in the
- * reference. */
+ * behaviour).  bit1: no L2 prefetch of the cache entries; bit4: use the cluster-pair
+ * kernel (two blocks split the query/key columns and exchange halves of S through
+ * distributed shared memory) instead of the default kernel.  No counterpart in the reference. */
 void dsv4_debug_set_flags(int flags);
 
 /* Library identification: (major << 16) | minor. */
