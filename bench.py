@@ -343,6 +343,20 @@ def run_ours(args):
         del csa_w, hca_w
         torch.cuda.empty_cache()
     if not args.no_extras and world == 1:
+        # the cache-write side: CSA compressor second pass (a pure streaming kernel)
+        import dsv4_attn_b200 as lib
+        Bc, nc, cc = 1, 65536, 512
+        streams = [torch.randn(Bc, nc, cc, device=dev).to(torch.bfloat16) for _ in range(4)]
+        biases = [torch.randn(4, cc, device=dev).to(torch.bfloat16) for _ in range(2)]
+        cout = torch.empty(Bc, nc // 4, cc, dtype=torch.bfloat16, device=dev)
+        ct = time_steps(lambda: lib.csa_compress_reduce_fwd(*streams, *biases, 4, out=cout), max(3, min(args.steps, 10)), 3,
+                        flush, barrier)
+        cbytes = 4 * Bc * nc * cc * 2 + cout.numel() * 2
+        cms = statistics.mean(ct)
+        others["csa_compress_reduce_b1_n65536_c512"] = {"us": cms * 1e3, "gb_per_s": cbytes / (cms * 1e-3) / 1e9,
+                                                        "hbm_frac": cbytes / (cms * 1e-3) / 1e9 / peak, "bytes": cbytes}
+        del streams, cout
+        torch.cuda.empty_cache()
         for name in WORKLOADS:
             if name == args.workload:
                 continue
