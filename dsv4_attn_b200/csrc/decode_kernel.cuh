@@ -50,7 +50,7 @@ constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // th
 constexpr int kLoaderRegs = 160;       // 8 x 32 x (160-128) = 8192 registers taken ...
 constexpr int kIdleRegs = 64;          // ... from 4 x 32 x (128-64) = 8192 released
 constexpr int kNumThreads = kNumWarps * 32;  // 512
-constexpr int kGroupChunks = 3;        // chunks per hand-over from the loaders to the MMA thread
+constexpr int kNumKvGroups = 3;        // hand-overs per tile from the loaders to the MMA thread
 constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
 constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P (BF16) overwrites the first 32 of its S
@@ -173,16 +173,17 @@ __device__ __forceinline__ void dequant4(uint32_t w, __nv_bfloat162 scale2, uint
 }
 
 // Registers one loader thread holds for one tile.  A loader warp owns 8
-// consecutive entries of the tile; lane/4 picks the entry and lane%4 one 16-byte
-// (16-element) piece of a 64-element latent chunk, so that one load instruction
-// per chunk covers 8 entries x 64 contiguous bytes and the tile can be written
-// to shared memory - and consumed by the MMAs - chunk by chunk.
+// consecutive entries of the tile, as two groups of 4: lane/8 picks the entry of
+// a group and lane%8 one 16-byte piece of a 128-byte span (two 64-element latent
+// chunks, or the RoPE tail).  One load instruction then covers 4 entries x 128
+// contiguous bytes: measured on this part, an SM pulls records about 1.6 times
+// faster in this shape than with 64 bytes per entry per instruction, and the
+// record fetch is what the loader warps spend most of their time on.
 template <int SRC>
 struct LoaderRegs {
-    static constexpr int kLatChunks = (SRC == kSrcRef) ? 7 : 8;
-    uint4 lat[kLatChunks];   // latent chunk c, elements [64c + 16*(lane%4), +16) of entry lane/4
-    uint4 rope[2];           // RoPE 16-byte columns lane%4 and lane%4 + 4 of entry lane/4
-    uint32_t sc[4];          // packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
+    uint4 lat[2][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
+    uint4 rope[2];           // [group]: RoPE 16-byte column lane%8 of that entry
+    uint32_t sc[2][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
     uint32_t vmask;          // bit i = entry i of this warp takes part (same in all lanes)
 };
 
@@ -222,6 +223,28 @@ __device__ __forceinline__ unsigned long long loader_resolve(const DecodeArgs& a
     return key;
 }
 
+// Two entries at once, with the two chains of dependent loads side by side.
+template <int SRC>
+__device__ __forceinline__ void loader_resolve2(const DecodeArgs& a, int b, int n, int va, int ntok_a, int vb, int ntok_b,
+                                                int kv_len_n, unsigned long long& key_a, bool& valid_a,
+                                                unsigned long long& key_b, bool& valid_b) {
+    if constexpr (SRC == kSrcCsa) {
+        valid_a = va < ntok_a;
+        valid_b = vb < ntok_b;
+        const int ea = valid_a ? __ldg(a.indices + int64_t(n) * a.topk + va) : -1;
+        const int eb = valid_b ? __ldg(a.indices + int64_t(n) * a.topk + vb) : -1;
+        valid_a = (ea >= 0) && (ea < kv_len_n);
+        valid_b = (eb >= 0) && (eb < kv_len_n);
+        const int pa = valid_a ? __ldg(a.block_table + int64_t(b) * a.max_pages + (ea >> 6)) : 0;
+        const int pb = valid_b ? __ldg(a.block_table + int64_t(b) * a.max_pages + (eb >> 6)) : 0;
+        key_a = valid_a ? reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(pa) * 64 + (ea & 63)) * 656) : 0ull;
+        key_b = valid_b ? reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(pb) * 64 + (eb & 63)) * 656) : 0ull;
+    } else {
+        key_a = loader_resolve<SRC>(a, b, n, va, ntok_a, kv_len_n, valid_a);
+        key_b = loader_resolve<SRC>(a, b, n, vb, ntok_b, kv_len_n, valid_b);
+    }
+}
+
 // Warp-wide: resolve the 8 entries [v0, v0+8) (lanes 0..7), return the key in
 // those lanes and the valid mask in all lanes.
 template <int SRC>
@@ -234,38 +257,42 @@ __device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeAr
     return key;
 }
 
-// Issue the loads of one tile for this lane's entry (key held by lane `lane/4`).
+// Issue the loads of one tile for this lane's two entries (keys held by lanes 0..7).
 template <int SRC>
 __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
                                              LoaderRegs<SRC>& r) {
     r.vmask = vmask;
-    const int i = lane >> 2, piece = lane & 3;
-    const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-    if (!((vmask >> i) & 1u)) return;
-    if constexpr (SRC != kSrcRef) {
-        const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
+    const int piece = lane & 7;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) r.lat[c] = ptx::ldg_nc_v4(row + c * 64 + piece * 16);
-        const uint4 s4 = ptx::ldg_nc_v4(row + 512);
-        r.sc[0] = s4.x;  r.sc[1] = s4.y;  r.sc[2] = s4.z;  r.sc[3] = s4.w;
-        r.rope[0] = ptx::ldg_nc_v4(row + 528 + piece * 16);
-        r.rope[1] = ptx::ldg_nc_v4(row + 528 + (piece + 4) * 16);
-    } else {
-        const bool swa = (k >> 62) & 1ull;
-        const int64_t e = int64_t(k & ~(1ull << 62));
-        const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
-        const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
-        const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
+    for (int g = 0; g < 2; ++g) {
+        const int i = 4 * g + (lane >> 3);
+        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+        if (!((vmask >> i) & 1u)) continue;
+        if constexpr (SRC != kSrcRef) {
+            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
 #pragma unroll
-        for (int c = 0; c < 7; ++c) r.lat[c] = ptx::ldg_nc_v4(lp + c * 64 + piece * 16);
-        uint32_t s0 = 0, s1 = 0;
+            for (int j = 0; j < 4; ++j) r.lat[g][j] = ptx::ldg_nc_v4(row + j * 128 + piece * 16);
+            const uint4 s4 = ptx::ldg_nc_v4(row + 512);
+            r.sc[g][0] = s4.x;  r.sc[g][1] = s4.y;  r.sc[g][2] = s4.z;  r.sc[g][3] = s4.w;
+            r.rope[g] = ptx::ldg_nc_v4(row + 528 + piece * 16);
+        } else {
+            const bool swa = (k >> 62) & 1ull;
+            const int64_t e = int64_t(k & ~(1ull << 62));
+            const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
+            const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
+            const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s0 |= uint32_t(__ldg(sp + j)) << (8 * j);
+            for (int j = 0; j < 3; ++j) r.lat[g][j] = ptx::ldg_nc_v4(lp + j * 128 + piece * 16);
+            // the last span holds only chunk 6 (bytes 384..447 of the 448-byte row)
+            if (piece < 4) r.lat[g][3] = ptx::ldg_nc_v4(lp + 384 + piece * 16);
+            uint32_t s0 = 0, s1 = 0;
 #pragma unroll
-        for (int j = 0; j < 3; ++j) s1 |= uint32_t(__ldg(sp + 4 + j)) << (8 * j);
-        r.sc[0] = s0;  r.sc[1] = s1;
-        r.rope[0] = ptx::ldg_nc_v4(rp + piece * 16);
-        r.rope[1] = ptx::ldg_nc_v4(rp + (piece + 4) * 16);
+            for (int j = 0; j < 4; ++j) s0 |= uint32_t(__ldg(sp + j)) << (8 * j);
+#pragma unroll
+            for (int j = 0; j < 3; ++j) s1 |= uint32_t(__ldg(sp + 4 + j)) << (8 * j);
+            r.sc[g][0] = s0;  r.sc[g][1] = s1;
+            r.rope[g] = ptx::ldg_nc_v4(rp + piece * 16);
+        }
     }
 }
 
@@ -284,45 +311,61 @@ __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint3
     }
 }
 
-// Dequantise and write chunk c (64 columns) of this warp's 8 entries (tile rows
-// t0 .. t0+7) into the KV tile.  Row t of a chunk is 128 bytes; 16-byte column c16
-// of row t lives at ((c16 ^ (t & 7)) << 4).  The 8 rows x 4 pieces of one store
-// instruction cover every column position four times: as few shared-memory
-// wavefronts as 512 bytes need.  Chunk NCHUNK-1 is the RoPE tail (a plain copy).
+// Dequantise and write span j (latent chunks 2j and 2j+1) of this warp's 8 entries
+// (tile rows t0 .. t0+7, t0 a multiple of 8) into the KV stage at kv_st.  Row t of a
+// chunk is 128 bytes; 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
+// One store instruction writes 4 rows x 2 chunks x 4 column positions: every
+// 16-byte bank group is hit by exactly 4 lanes, as few shared-memory wavefronts
+// as 512 bytes need.
 template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store_chunk(uint32_t kv_base, int t0, int lane, const LoaderRegs<SRC>& r, int c) {
-    const int i = lane >> 2;
-    const uint32_t piece = uint32_t(lane & 3);
-    const int t = t0 + i;
-    const bool valid = (r.vmask >> i) & 1u;
-    const uint32_t base = kv_base + uint32_t(c) * kKvChunkBytes + uint32_t(t) * 128u;
-    const uint32_t sw = uint32_t(t & 7);
-    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-    if (c == NCHUNK - 1) {
-        if (valid) { w0 = r.rope[0];  w1 = r.rope[1]; }
-        ptx::sts_v4(base + ((piece ^ sw) << 4), w0);
-        ptx::sts_v4(base + (((piece + 4u) ^ sw) << 4), w1);
-        return;
-    }
-    if (valid) {
-        float s120;
-        if constexpr (SRC == kSrcRef) {
-            // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
-            // scale, as in the reference's dequantiser
-            const uint32_t byte = ((c < 4 ? r.sc[0] >> (8 * c) : r.sc[1] >> (8 * (c - 4))) & 0xFFu);
-            s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
-        } else {
-            s120 = __uint_as_float(r.sc[c >> 1]) * 1.329227995784916e36f;   // one FP32 scale per 128 elements; x 2^120
+__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r, int j) {
+    const uint32_t piece = uint32_t(lane & 7);
+    const uint32_t c = 2u * uint32_t(j) + (piece >> 2);        // this lane's chunk
+    const uint32_t p = piece & 3u;                             // 16 latent bytes -> 16-byte columns 2p, 2p+1
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const int i = 4 * g + (lane >> 3);
+        const int t = t0 + i;
+        const bool valid = (r.vmask >> i) & 1u;
+        const uint32_t base = kv_st + c * kKvChunkBytes + uint32_t(t) * 128u;
+        const uint32_t sw = uint32_t(t & 7);
+        if (SRC == kSrcRef && c >= uint32_t(NCHUNK - 1)) continue;   // reference layout: span 3 ends with chunk 6
+        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
+        if (valid) {
+            float s120;
+            if constexpr (SRC == kSrcRef) {
+                // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
+                // scale, as in the reference's dequantiser
+                const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
+                s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
+            } else {
+                s120 = __uint_as_float(r.sc[g][j]) * 1.329227995784916e36f;   // one FP32 scale per 128 elements; x 2^120
+            }
+            const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
+            const uint4 x = r.lat[g][j];
+            dequant4(x.x, scale2, w0.x, w0.y);
+            dequant4(x.y, scale2, w0.z, w0.w);
+            dequant4(x.z, scale2, w1.x, w1.y);
+            dequant4(x.w, scale2, w1.z, w1.w);
         }
-        const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
-        const uint4 x = r.lat[c];
-        dequant4(x.x, scale2, w0.x, w0.y);
-        dequant4(x.y, scale2, w0.z, w0.w);
-        dequant4(x.z, scale2, w1.x, w1.y);
-        dequant4(x.w, scale2, w1.z, w1.w);
+        ptx::sts_v4(base + (((2u * p) ^ sw) << 4), w0);
+        ptx::sts_v4(base + (((2u * p + 1u) ^ sw) << 4), w1);
     }
-    ptx::sts_v4(base + (((2u * piece) ^ sw) << 4), w0);
-    ptx::sts_v4(base + (((2u * piece + 1u) ^ sw) << 4), w1);
+}
+
+// The RoPE tail (chunk NCHUNK-1, a plain copy): 4 rows x 8 columns per store instruction.
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r) {
+    const uint32_t piece = uint32_t(lane & 7);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const int i = 4 * g + (lane >> 3);
+        const int t = t0 + i;
+        const bool valid = (r.vmask >> i) & 1u;
+        const uint32_t base = kv_st + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
+        const uint4 w = valid ? r.rope[g] : make_uint4(0, 0, 0, 0);
+        ptx::sts_v4(base + ((piece ^ uint32_t(t & 7)) << 4), w);
+    }
 }
 
 template <int NCHUNK, int SRC>
@@ -376,7 +419,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     if (tid == 0) {
         trace_mark(a, 3, 0);
         for (int st = 0; st < 2; ++st) {
-            for (int g = 0; g < (NCHUNK + kGroupChunks - 1) / kGroupChunks; ++g)
+            for (int g = 0; g < kNumKvGroups; ++g)
                 ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps);
             ptx::mbar_init(bar_kv_free + 8 * st, 1);
             ptx::mbar_init(bar_s_full + 8 * st, 1);
@@ -400,6 +443,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tma_load_2d(dst, &a.q_map, c * 64, row0, bar_q_full);
             }
         }
+        trace_mark(a, 3, 10);
     }
 
     // Block-wide rendezvous.  Every role runs the same number of them (one before the
@@ -421,28 +465,36 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         LoaderRegs<SRC> regs_a, regs_b;
         // keys of the tiles two and three ahead of the one being stored (records already
         // pulled into L2), and of the tile four ahead (resolved, not yet prefetched)
-        unsigned long long key2 = 0, key3 = 0, key4 = 0;
-        uint32_t vm2 = 0, vm3 = 0, vm4 = 0;
+        unsigned long long key1 = 0, key2 = 0, key3 = 0, key4 = 0;
+        uint32_t vm1 = 0, vm2 = 0, vm3 = 0, vm4 = 0;
+        if (lw == 0 && lane == 0) trace_mark(a, 3, 4);
         if (ntiles > 0) {
             // one round of dependent loads for the first four tiles: lanes 0-7, 8-15, 16-23, 24-31
-            bool valid = false;
+            // (lanes 0-7 also resolve tile 4, as a second chain of loads in flight beside the first)
+            bool valid = false, valid4 = false;
             const int which = lane >> 3;
-            const unsigned long long key = loader_resolve<SRC>(a, b, n, (tile0 + which) * kTileN + lw * 8 + (lane & 7),
-                                                               (which < ntiles) ? n_tok : 0, kv_len_n, valid);
+            unsigned long long key, k4;
+            loader_resolve2<SRC>(a, b, n, (tile0 + which) * kTileN + lw * 8 + (lane & 7), (which < ntiles) ? n_tok : 0,
+                                 (tile0 + 4) * kTileN + lw * 8 + (lane & 7), (4 < ntiles && lane < 8) ? n_tok : 0,
+                                 kv_len_n, key, valid, k4, valid4);
             const uint32_t bal = __ballot_sync(0xFFFFFFFFu, valid);
+            vm4 = __ballot_sync(0xFFFFFFFFu, valid4) & 0xFFu;
+            key4 = k4;
+            if (lw == 0 && lane == 0) trace_mark(a, 3, 5);
             vm2 = (bal >> 16) & 0xFFu;
             vm3 = (bal >> 24) & 0xFFu;
-            const unsigned long long key1 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 8);   // -> lanes 0..7
             key2 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 16);
             key3 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 24);
+            // Only what the first tile needs goes out before the main loop: the number of loads
+            // an SM keeps in flight is limited, and everything queued here delays tile 0.
             loader_fetch<SRC>(a, key, bal & 0xFFu, lane, regs_a);
-            loader_fetch<SRC>(a, key1, (bal >> 8) & 0xFFu, lane, regs_b);
-            loader_prefetch_l2<SRC>(key2, vm2, lane);
-            loader_prefetch_l2<SRC>(key3, vm3, lane);
-            key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + 4) * kTileN + lw * 8, lane, (4 < ntiles) ? n_tok : 0,
-                                            kv_len_n, vm4);
+            if (lw == 0 && lane == 0) trace_mark(a, 3, 6);
+            key1 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 8);   // -> lanes 0..7
+            vm1 = (bal >> 8) & 0xFFu;
         }
+        if (lw == 0 && lane == 0) trace_mark(a, 3, 7);
         block_sync();
+        if (lw == 0 && lane == 0) trace_mark(a, 3, 8);
         if (ntiles > 0) {
             bool lok = true;
             auto tile_step = [&](LoaderRegs<SRC>& regs, int it) {
@@ -466,21 +518,33 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                 }
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it);
-                // the key resolved during the previous step has arrived by now: start pulling
-                // its records into L2 (using it earlier would stall on the block-table load)
-                if (!(a.dbg & 2)) loader_prefetch_l2<SRC>(key4, vm4, lane);
-                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
-                // chunk by chunk, so that the QK MMAs of this tile start while it is still being written
-#pragma unroll
-                for (int c = 0; c < NCHUNK; ++c) {
-                    loader_store_chunk<NCHUNK, SRC>(kv_base + uint32_t(st) * L::kKvStageBytes, lw * 8, lane, regs, c);
-                    if (c % kGroupChunks == kGroupChunks - 1 || c == NCHUNK - 1) {
-                        // one proxy fence and one arrival per group of chunks
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * (c / kGroupChunks));
-                    }
+                if (it == 0) {
+                    // loads of tile 1 queue up behind those of tile 0, then the records of tiles 2 and 3
+                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
+                    loader_prefetch_l2<SRC>(key2, vm2, lane);
+                    loader_prefetch_l2<SRC>(key3, vm3, lane);
+                } else if (!(a.dbg & 2)) {
+                    // the key resolved during the previous step has arrived by now: start pulling
+                    // its records into L2 (using it earlier would stall on the block-table load)
+                    loader_prefetch_l2<SRC>(key4, vm4, lane);
                 }
+                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
+                // group by group (chunks 0-3, chunks 4.., RoPE tail), so that the QK MMAs of this tile
+                // start while it is still being written; one proxy fence and one arrival per group
+                const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
+                auto group_done = [&](int g) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * g);
+                };
+                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 0);
+                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 1);
+                group_done(0);
+                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 2);
+                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 3);
+                group_done(1);
+                loader_store_rope<NCHUNK, SRC>(kv_st, lw * 8, lane, regs);
+                group_done(2);
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
                 // this set is free again: loads of tile it+2, keys of tile it+5
                 if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
@@ -500,6 +564,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         if (warp == kMmaWarp) {
             ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
             ptx::tmem_relinquish();
+            if (lane == 0) trace_mark(a, 3, 9);
         }
         block_sync();
         const uint32_t tmem = misc->tmem_base;
@@ -543,12 +608,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 };
                 // QK is issued group by group as the loaders deliver them; between groups a ready P
                 // goes first.
-                constexpr int kNumGroups = (NCHUNK + kGroupChunks - 1) / kGroupChunks;
-                static_assert(kGroupChunks == 3 && kNumGroups == 3, "group dispatch below is written for 3 x 3 chunks");
+                constexpr int kNumGroups = kNumKvGroups;
+                static_assert(kNumGroups == 3, "group dispatch below is written for 3 groups");
+                // the groups the loaders deliver: chunks 0-3, the other latent chunks, the RoPE tail
                 auto issue_qk_group = [&](int it, int g) {
-                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 3>{});
-                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, 3>{}, std::integral_constant<int, 6>{});
-                    else issue_qk_range(it, std::integral_constant<int, 6>{}, std::integral_constant<int, NCHUNK>{});
+                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 4>{});
+                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK - 1>{});
+                    else issue_qk_range(it, std::integral_constant<int, NCHUNK - 1>{}, std::integral_constant<int, NCHUNK>{});
                 };
                 auto issue_pv = [&](int it) {
                     const int st = it & 1;
@@ -619,6 +685,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 report_timeout(a.status, kStatusWaitQ, 0, tile0);
                 ok = false;
             }
+            if (tid == 0) trace_mark(a, 3, 11);
             if (ok) {
                 const int r = warp * 32 + lane;
                 const uint32_t lane_addr = uint32_t(warp * 32) << 16;
