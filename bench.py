@@ -11,10 +11,18 @@ context (782 compressed entries + a 128-entry window); the CSA configurations
 are measured in the same run and reported under "other_workloads".
 
 Metric: achieved KV bytes per second = (entries attended to x 656 bytes) / step
-time, aggregated over all GPUs, next to microseconds per layer.  L2 is flushed
-between timed steps.  `--impl reference` times the CPU restatement of the
-reference's PyTorch decode path (the oracle) on a bounded sample of the same
-workload on the host cores.
+time, aggregated over all GPUs, next to microseconds per layer.
+
+Timing: the K timed steps are captured into one CUDA graph and replayed between
+two events, the way a serving engine runs its decode layers (and the way the
+reference's own graph candidate is timed).  Step i works on instance i mod R of
+the workload - R independent copies with their own KV pools, queries and outputs,
+R chosen so that the copies together are several times larger than L2 - so every
+step finds its inputs in HBM, not in L2, without a flush inside the timed region.
+The same step timed alone (L2 flushed by a 512 MiB write before each launch, one
+event pair per launch, eager launch) is reported beside it as "isolated".
+`--impl reference` times the CPU restatement of the reference's PyTorch decode
+path (the oracle) on a bounded sample of the same workload on the host cores.
 """
 from __future__ import annotations
 
@@ -51,6 +59,11 @@ WORKLOADS = {
 MIXED = "mixed_1024req_lognormal_csa+hca"
 MIXED_REQUESTS = 1024
 DEFAULT_WORKLOAD = "hca_b64_h128_ctx100k"
+# DRAM bytes (read + write) of ONE launch of the decode kernel on the workload, from an ncu
+# capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum); the summaries
+# under profiles/ hold the figures and the command lines.
+NCU_DRAM_TRAFFIC = {"hca_b64_h128_ctx100k": 48.06e6, "csa_b64_h128_topk512_ctx3072": 32.38e6}
+NCU_TRAFFIC_SOURCE = "ncu capture of one launch (profiles/decode_mma_kernel_*.md)"
 
 
 def measured_peak_gbs():
@@ -173,7 +186,7 @@ def make_step(kind, w, splits):
 
 
 def time_steps(fn, steps, warmup, flush, barrier):
-    """Device time of `steps` calls, L2 flushed before each; returns list of ms."""
+    """Device time of `steps` calls, each timed alone with L2 flushed before it; returns list of ms."""
     import torch
     for _ in range(warmup):
         flush.zero_()
@@ -190,6 +203,44 @@ def time_steps(fn, steps, warmup, flush, barrier):
     torch.cuda.synchronize()
     barrier()
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def time_rotating(fns, steps, warmup, flush, barrier):
+    """Device time (ms) of `steps` back-to-back calls, call i on fns[i % R], replayed from
+    one CUDA graph; falls back to eager launches if capture is not possible.  Returns
+    (total_ms, "graph" | "eager")."""
+    import torch
+    R = len(fns)
+    for i in range(max(warmup, R)):
+        fns[i % R]()
+    torch.cuda.synchronize()
+    graph = None
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fns[i % R]()
+        graph = g
+    except Exception as e:  # noqa: BLE001 - report and time eagerly instead
+        print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
+        torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    if graph is not None:
+        graph.replay()          # untimed: uploads the graph
+    flush.zero_()
+    barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(steps):
+            fns[i % R]()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1), ("graph" if graph is not None else "eager")
 
 
 def e2e_steps(kind, w, fn, steps, warmup, flush, barrier):
@@ -277,18 +328,33 @@ def run_ours(args):
         barrier = lambda: None
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
+    l2_bytes = int(torch.cuda.get_device_properties(dev).L2_cache_size)
+
     def measure(name, steps, warmup, with_e2e):
+        """R instances of the workload (together > 3x L2); the K steps rotate over them."""
+        insts = []
         kind, w, splits = build_workload(name, seed=1000 + rank, device=dev)
-        fn, launches, splits, status = make_step(kind, w, splits)
-        times = time_steps(fn, steps, warmup, flush, barrier)
-        res = {"kind": kind, "kv_bytes": w.kv_bytes, "times_ms": times, "launches": launches, "splits": splits}
+        B, s_q, H, _ = w.q.shape
+        footprint = w.kv_bytes + w.q.numel() * 2 + B * s_q * H * 512 * 2
+        R = max(1, min(12, -(-3 * l2_bytes // footprint)))
+        for r in range(R):
+            if r > 0:
+                kind, w, splits = build_workload(name, seed=1000 + rank + 101 * r, device=dev)
+            fn, launches, splits_used, status = make_step(kind, w, splits)
+            insts.append((w, fn, status))
+        total_ms, mode = time_rotating([f for _, f, _ in insts], steps, warmup, flush, barrier)
+        w0, fn0, _ = insts[0]
+        iso = time_steps(fn0, max(3, min(steps, 10)), 3, flush, barrier)
+        res = {"kind": kind, "kv_bytes": w0.kv_bytes, "total_ms": total_ms, "mode": mode, "instances": R,
+               "isolated_ms": iso, "launches": launches, "splits": splits_used}
         if with_e2e:
-            et, h2d, d2h = e2e_steps(kind, w, fn, steps, warmup, flush, barrier)
+            et, h2d, d2h = e2e_steps(kind, w0, fn0, steps, warmup, flush, barrier)
             res.update(e2e_ms=et, h2d=h2d, d2h=d2h)
-        st = status.cpu().tolist()
-        if st != [0, 0, 0, 0]:
-            raise RuntimeError(f"{name}: a kernel wait timed out: status={st}")
-        del w
+        for _, _, status in insts:
+            st = status.cpu().tolist()
+            if st != [0, 0, 0, 0]:
+                raise RuntimeError(f"{name}: a kernel wait timed out: status={st}")
+        del insts, w, w0
         torch.cuda.empty_cache()
         return res
 
@@ -312,14 +378,15 @@ def run_ours(args):
     head = measure(args.workload, args.steps, args.warmup, with_e2e=True)
     clocks = sampler.stop() if rank == 0 else None
 
-    total_ms = reduce_max(sum(head["times_ms"]))
+    total_ms = reduce_max(head["total_ms"])
     total_bytes = reduce_sum(head["kv_bytes"])
     ms_per_step = total_ms / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e12
+    isolated_ms = reduce_max(statistics.mean(head["isolated_ms"]))
     e2e_ms = reduce_max(sum(head["e2e_ms"])) / args.steps
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e12
     peak, peak_src = measured_peak_gbs()
-    per_gpu_gbs = head["kv_bytes"] / (statistics.mean(head["times_ms"]) * 1e-3) / 1e9
+    per_gpu_gbs = head["kv_bytes"] / (head["total_ms"] / args.steps * 1e-3) / 1e9
 
     others = {}
     if not args.no_extras:
@@ -330,15 +397,17 @@ def run_ours(args):
         def both():
             fc()
             fh()
-        mt = time_steps(both, max(3, min(args.steps, 10)), 3, flush, barrier)
-        mixed_ms = reduce_max(sum(mt)) / len(mt)
+        # one instance: each layer streams far more than L2 holds
+        msteps = max(3, min(args.steps, 10))
+        mixed_total, mixed_mode = time_rotating([both], msteps, 3, flush, barrier)
+        mixed_ms = reduce_max(mixed_total) / msteps
         mixed_bytes = reduce_sum(csa_w.kv_bytes + hca_w.kv_bytes)
         if st_c.cpu().tolist() != [0, 0, 0, 0] or st_h.cpu().tolist() != [0, 0, 0, 0]:
             raise RuntimeError("mixed workload: a kernel wait timed out")
         others[MIXED] = {"tokens_per_s": MIXED_REQUESTS / (mixed_ms * 1e-3), "ms_per_step": mixed_ms,
                          "us_per_layer": mixed_ms * 1e3 / 2, "kv_tb_per_s": mixed_bytes / (mixed_ms * 1e-3) / 1e12,
                          "kv_bytes": mixed_bytes, "requests_per_gpu": n_mine, "layers_per_step": 2,
-                         "scaling": "strong", "num_splits": {"csa": sc, "hca": sh},
+                         "scaling": "strong", "num_splits": {"csa": sc, "hca": sh}, "timing": mixed_mode,
                          "sharding": "sorted by context, dealt round-robin"}
         del csa_w, hca_w
         torch.cuda.empty_cache()
@@ -360,11 +429,13 @@ def run_ours(args):
         for name in WORKLOADS:
             if name == args.workload:
                 continue
-            r = measure(name, max(3, min(args.steps, 10)), 3, with_e2e=False)
-            ms = statistics.mean(r["times_ms"])
+            osteps = max(3, min(args.steps, 10))
+            r = measure(name, osteps, 3, with_e2e=False)
+            ms = r["total_ms"] / osteps
             others[name] = {"us_per_layer": ms * 1e3, "kv_tb_per_s": r["kv_bytes"] / (ms * 1e-3) / 1e12,
                             "hbm_frac": r["kv_bytes"] / (ms * 1e-3) / 1e9 / peak, "kv_bytes": r["kv_bytes"],
-                            "num_splits": r["splits"]}
+                            "num_splits": r["splits"], "isolated_us": statistics.mean(r["isolated_ms"]) * 1e3,
+                            "timing": r["mode"], "instances": r["instances"]}
 
     if rank != 0:
         if world > 1:
@@ -373,16 +444,22 @@ def run_ours(args):
     kind, kw = WORKLOADS[args.workload]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "isolated_us_per_layer": isolated_ms * 1e3,
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 MMA over fp8-e4m3 KV, fp32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in kw.items()}, "requests_per_gpu": kw["B"],
-                   "num_splits": head["splits"], "entry_bytes": ENTRY_BYTES, "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)",
+                   "num_splits": head["splits"], "entry_bytes": ENTRY_BYTES,
+                   "timing": f"{head['mode']} replay of the K steps" if head["mode"] == "graph" else "eager back-to-back launches",
+                   "l2": f"inputs larger than L2: the steps rotate over {head['instances']} independent instances of the workload "
+                         f"({head['instances']} KV pools, queries and outputs; L2 = {l2_bytes >> 20} MiB); the isolated figure flushes L2 "
+                         f"with a {L2_FLUSH_BYTES >> 20} MiB write before each launch",
                    "kv_bytes_per_gpu_step": head["kv_bytes"], "parallelism": f"dp{world} over requests, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"],
                 "ms_per_step": e2e_ms, "note": "q and per-step length/index tensors copied from pinned host memory, out+lse read back; the KV cache is device-resident state"},
         "gpu_launches": head["launches"] * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "decode_mma_kernel" + ("+combine_kernel" if head["launches"] > 1 else "")},
+                     "traffic": NCU_DRAM_TRAFFIC.get(args.workload), "traffic_source": NCU_TRAFFIC_SOURCE if args.workload in NCU_DRAM_TRAFFIC else None,
+                     "algorithmic_bytes": head["kv_bytes"], "peak_source": peak_src, "kernel": "decode_mma_kernel" + ("+combine_kernel" if head["launches"] > 1 else "")},
         "clocks": clocks,
         "other_workloads": others,
     }

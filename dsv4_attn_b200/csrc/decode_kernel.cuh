@@ -152,6 +152,12 @@ __device__ __forceinline__ void trace_mark(const DecodeArgs& a, int role, int sl
         a.trace[role * 1024 + slot] = ptx::globaltimer_ns();
 }
 
+// Start (which = 0) and end (1) time of every block, in the last quarter of the trace buffer.
+__device__ __forceinline__ void trace_block(const DecodeArgs& a, int which) {
+    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (a.trace != nullptr && lin < 240) a.trace[3 * 1024 + 512 + 2 * lin + which] = ptx::globaltimer_ns();
+}
+
 // Two FP8 e4m3 bytes sitting in bits [15:8] and [31:24] of `r` -> two BF16 bit
 // patterns whose values are the FP8 values times 2^-120 (the e4m3 exponent and
 // mantissa bits dropped into the BF16 exponent/mantissa fields; e4m3
@@ -418,6 +424,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     // ── set-up ──
     if (tid == 0) {
         trace_mark(a, 3, 0);
+        trace_block(a, 0);
         for (int st = 0; st < 2; ++st) {
             for (int g = 0; g < kNumKvGroups; ++g)
                 ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps);
@@ -885,7 +892,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     // ── common exit: every thread gets here, with or without an error ──
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0) trace_mark(a, 3, 3);
+    if (tid == 0) { trace_mark(a, 3, 3);  trace_block(a, 1); }
     if (warp == kMmaWarp) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(misc->tmem_base, kTmemCols);
