@@ -425,6 +425,35 @@ def run_ours(args):
         others["csa_compress_reduce_b1_n65536_c512"] = {"us": cms * 1e3, "gb_per_s": cbytes / (cms * 1e-3) / 1e9,
                                                         "hbm_frac": cbytes / (cms * 1e-3) / 1e9 / peak, "bytes": cbytes}
         del streams, cout
+        # the HCA compressor fused with the FP8 quantiser and the paged-cache insert, and the
+        # stand-alone quantise-and-insert step
+        nh, ch, mh = 65536, 576, 128
+        Ch = torch.randn(1, nh, ch, device=dev).to(torch.bfloat16)
+        Zh = (2 * torch.randn(1, nh, ch, device=dev)).to(torch.bfloat16)
+        bh = torch.randn(mh, ch, device=dev).to(torch.bfloat16)
+        n_new = nh // mh
+        pages = (n_new + 63) // 64
+        pool_h = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
+        bt_h = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        pos_h = torch.zeros(1, dtype=torch.int32, device=dev)
+        ht = time_steps(lambda: lib.hca_compress_fwd(Ch, Zh, bh, mh, kv_pool=pool_h, block_table=bt_h, insert_pos=pos_h,
+                                                     want_out=False), max(3, min(args.steps, 10)), 3, flush, barrier)
+        hbytes = 2 * nh * ch * 2 + n_new * ENTRY_BYTES
+        hms = statistics.mean(ht)
+        others["hca_compress_insert_b1_n65536_c576_m128"] = {"us": hms * 1e3, "gb_per_s": hbytes / (hms * 1e-3) / 1e9,
+                                                            "hbm_frac": hbytes / (hms * 1e-3) / 1e9 / peak, "bytes": hbytes}
+        del Ch, Zh
+        Tq = 65536
+        rows_q = torch.randn(1, Tq, ch, device=dev).to(torch.bfloat16)
+        pages = Tq // 64
+        pool_q = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
+        bt_q = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages)
+        qt = time_steps(lambda: lib.kv_quantize_insert(rows_q, pool_q, bt_q, pos_h), max(3, min(args.steps, 10)), 3, flush, barrier)
+        qbytes = Tq * (ch * 2 + ENTRY_BYTES)
+        qms = statistics.mean(qt)
+        others["kv_quantize_insert_65536rows"] = {"us": qms * 1e3, "gb_per_s": qbytes / (qms * 1e-3) / 1e9,
+                                                  "hbm_frac": qbytes / (qms * 1e-3) / 1e9 / peak, "bytes": qbytes}
+        del rows_q, pool_q, pool_h
         torch.cuda.empty_cache()
         for name in WORKLOADS:
             if name == args.workload:

@@ -58,7 +58,7 @@ class CombineParams(C.Structure):
 EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
            "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error", "dsv4_csa_compress_reduce_fwd",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
-           "dsv4_attn_workspace_bytes", "hca_decode_fwd")
+           "dsv4_attn_workspace_bytes", "hca_decode_fwd", "dsv4_hca_compress_fwd", "dsv4_kv_quantize_insert")
 
 
 class CsaCompressReduceParams(C.Structure):
@@ -68,6 +68,28 @@ class CsaCompressReduceParams(C.Structure):
         ("B_a", C.c_void_p), ("B_b", C.c_void_p), ("out", C.c_void_p),
         ("stride_C_b", C.c_int64), ("stride_C_n", C.c_int64), ("stride_out_b", C.c_int64),
         ("stride_out_blk", C.c_int64),
+    ]
+
+
+class CacheDest(C.Structure):
+    _fields_ = [
+        ("kv_pool", C.c_void_p), ("block_table", C.c_void_p), ("insert_pos", C.c_void_p),
+        ("max_pages", C.c_int32), ("reserved0", C.c_int32), ("num_pages", C.c_int64), ("status", C.c_void_p),
+    ]
+
+
+class HcaCompressParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("n", C.c_int32), ("c", C.c_int32), ("m", C.c_int32),
+        ("C", C.c_void_p), ("Z", C.c_void_p), ("bias", C.c_void_p),
+        ("stride_b", C.c_int64), ("stride_n", C.c_int64), ("out", C.c_void_p), ("dst", C.POINTER(CacheDest)),
+    ]
+
+
+class KvQuantizeInsertParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("T", C.c_int32), ("rows", C.c_void_p),
+        ("stride_b", C.c_int64), ("stride_t", C.c_int64), ("n_rows", C.c_void_p), ("dst", C.POINTER(CacheDest)),
     ]
 
 
@@ -90,6 +112,8 @@ def _load() -> C.CDLL:
                      ("dsv4_hca_dense_decode_fwd", HcaDenseDecodeParams),
                      ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
                      ("dsv4_csa_compress_reduce_fwd", CsaCompressReduceParams),
+                     ("dsv4_hca_compress_fwd", HcaCompressParams),
+                     ("dsv4_kv_quantize_insert", KvQuantizeInsertParams),
                      ("dsv4_attn_combine", CombineParams)):
         fn = getattr(lib, name)
         fn.restype = C.c_int

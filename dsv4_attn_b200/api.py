@@ -277,3 +277,62 @@ def csa_compress_reduce_fwd(C_a, C_b, Z_a, Z_b, B_a, B_b, m, *, out=None):
         stride_out_b=(n // m) * c_out, stride_out_blk=c_out)
     _rc(_lib.LIB.dsv4_csa_compress_reduce_fwd(C.byref(p), _stream(C_a.device)), "dsv4_csa_compress_reduce_fwd")
     return out
+
+
+def _cache_dest(kv_pool, block_table, insert_pos, status, B):
+    _cuda_contig(kv_pool, "kv_pool", torch.uint8, 3)
+    _check(kv_pool.shape[1] == PAGE_ENTRIES and kv_pool.shape[2] == ENTRY_BYTES, f"kv_pool must be [pages, {PAGE_ENTRIES}, {ENTRY_BYTES}]")
+    _cuda_contig(block_table, "block_table", torch.int32, 2)
+    _cuda_contig(insert_pos, "insert_pos", torch.int32, 1)
+    _check(block_table.shape[0] == B and insert_pos.shape[0] == B, "block_table / insert_pos must have one row per request")
+    if status is not None:
+        _cuda_contig(status, "status", torch.int32, 1)
+        _check(status.numel() >= 4, "status must hold 4 int32")
+    return _lib.CacheDest(kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), insert_pos=_ptr(insert_pos),
+                          max_pages=block_table.shape[1], num_pages=kv_pool.shape[0], status=_ptr(status))
+
+
+def hca_compress_fwd(C_, Z, bias, m, *, out=None, kv_pool=None, block_table=None, insert_pos=None, status=None,
+                     want_out=True):
+    """HCA compressor: BF16 streams C, Z [B, n, c] and bias [m, c] -> BF16 [B, n/m, c]
+    (the reduce of the reference's compressor_simple, bench/bench/reference.py:117-122).
+    With kv_pool / block_table / insert_pos (c == 576) the rows are also quantised and
+    written into the paged cache as entries insert_pos[b] + i; `want_out=False` skips the
+    dense output then."""
+    for name, t in (("C", C_), ("Z", Z)):
+        _cuda_contig(t, name, torch.bfloat16, 3)
+    _check(C_.shape == Z.shape, "C and Z must be equal-shaped [B, n, c]")
+    _cuda_contig(bias, "bias", torch.bfloat16, 2)
+    B, n, c = C_.shape
+    _check(bias.shape[0] == m and bias.shape[1] == c, "bias must be [m, c]")
+    _check(m >= 1 and n % m == 0, "n must be divisible by m")
+    _check(c % 8 == 0, "c must be a multiple of 8")
+    dst = None
+    if kv_pool is not None:
+        _check(c == D_QK, f"the cache insert needs c == {D_QK}")
+        dst = _cache_dest(kv_pool, block_table, insert_pos, status, B)
+    _check(want_out or dst is not None, "nothing to produce")
+    if want_out and out is None:
+        out = torch.empty(B, n // m, c, dtype=torch.bfloat16, device=C_.device)
+    if out is not None:
+        _cuda_contig(out, "out", torch.bfloat16, 3)
+        _check(tuple(out.shape) == (B, n // m, c), "out must be [B, n/m, c]")
+    p = _lib.HcaCompressParams(B=B, n=n, c=c, m=m, C=_ptr(C_), Z=_ptr(Z), bias=_ptr(bias), stride_b=n * c, stride_n=c,
+                               out=_ptr(out), dst=C.pointer(dst) if dst is not None else None)
+    _rc(_lib.LIB.dsv4_hca_compress_fwd(C.byref(p), _stream(C_.device)), "dsv4_hca_compress_fwd")
+    return out
+
+
+def kv_quantize_insert(rows, kv_pool, block_table, insert_pos, *, n_rows=None, status=None) -> None:
+    """Quantise BF16 rows [B, T, 576] into 656-byte cache entries and write them at logical
+    positions insert_pos[b] + t of request b (in place, into kv_pool)."""
+    _cuda_contig(rows, "rows", torch.bfloat16, 3)
+    B, T, c = rows.shape
+    _check(c == D_QK, f"rows must be [B, T, {D_QK}]")
+    dst = _cache_dest(kv_pool, block_table, insert_pos, status, B)
+    if n_rows is not None:
+        _cuda_contig(n_rows, "n_rows", torch.int32, 1)
+        _check(n_rows.shape[0] == B, "n_rows must be [B]")
+    p = _lib.KvQuantizeInsertParams(B=B, T=T, rows=_ptr(rows), stride_b=T * c, stride_t=c, n_rows=_ptr(n_rows),
+                                    dst=C.pointer(dst))
+    _rc(_lib.LIB.dsv4_kv_quantize_insert(C.byref(p), _stream(rows.device)), "dsv4_kv_quantize_insert")

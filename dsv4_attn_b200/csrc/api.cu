@@ -10,6 +10,7 @@
 
 #include "combine.cuh"
 #include "compress_reduce.cuh"
+#include "cache_write.cuh"
 #include "decode_kernel.cuh"
 #include "decode_pair.cuh"
 #include "decode_simt.cuh"
@@ -440,5 +441,65 @@ extern "C" int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (vec) compress_reduce_kernel<4, 8><<<blocks, kCompressThreads, 0, s>>>(a);
     else compress_reduce_kernel<4, 1><<<blocks, kCompressThreads, 0, s>>>(a);
+    return int(cudaGetLastError());
+}
+
+
+static bool fill_cache_dest(const Dsv4CacheDest* d, int B, CacheDest& out) {
+    if (d == nullptr || d->kv_pool == nullptr || d->block_table == nullptr || d->insert_pos == nullptr) return false;
+    if (d->max_pages <= 0 || d->num_pages <= 0 || !aligned(d->kv_pool, 16)) return false;
+    (void)B;
+    out.kv_pool = static_cast<uint8_t*>(d->kv_pool);
+    out.block_table = d->block_table;
+    out.insert_pos = d->insert_pos;
+    out.max_pages = d->max_pages;
+    out.num_pages = d->num_pages;
+    out.status = d->status;
+    return true;
+}
+
+extern "C" int dsv4_hca_compress_fwd(const Dsv4HcaCompressParams* p, void* stream) {
+    if (p == nullptr || p->B <= 0 || p->n <= 0 || p->c <= 0 || p->m <= 0) return int(cudaErrorInvalidValue);
+    if (p->n % p->m != 0 || p->c % 8 != 0) return int(cudaErrorInvalidValue);
+    if (p->C == nullptr || p->Z == nullptr || p->bias == nullptr) return int(cudaErrorInvalidValue);
+    if (p->out == nullptr && p->dst == nullptr) return int(cudaErrorInvalidValue);
+    if (p->stride_b % 8 != 0 || p->stride_n % 8 != 0 || !aligned(p->C, 16) || !aligned(p->Z, 16) || !aligned(p->bias, 16) ||
+        (p->out != nullptr && !aligned(p->out, 16)))
+        return int(cudaErrorInvalidValue);
+    HcaCompressArgs a{};
+    a.B = p->B;  a.n = p->n;  a.n_blocks = p->n / p->m;  a.c = p->c;  a.m = p->m;
+    a.C = static_cast<const __nv_bfloat16*>(p->C);
+    a.Z = static_cast<const __nv_bfloat16*>(p->Z);
+    a.bias = static_cast<const __nv_bfloat16*>(p->bias);
+    a.stride_b = p->stride_b;  a.stride_n = p->stride_n;
+    a.out = static_cast<__nv_bfloat16*>(p->out);
+    a.stride_out_b = int64_t(a.n_blocks) * a.c;  a.stride_out_blk = a.c;
+    if (p->dst != nullptr) {
+        if (p->c != 576 || !fill_cache_dest(p->dst, p->B, a.dst)) return int(cudaErrorInvalidValue);
+    }
+    const int64_t rows_out = int64_t(a.B) * a.n_blocks;
+    if (rows_out > 0x7FFFFFFF) return int(cudaErrorInvalidValue);
+    const dim3 grid(unsigned(rows_out), unsigned((a.c / 8 + kHcaVecsPerBlock - 1) / kHcaVecsPerBlock), 1);
+    if (grid.y > 65535u) return int(cudaErrorInvalidValue);
+    hca_compress_kernel<<<grid, kHcaCompressThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return int(cudaGetLastError());
+}
+
+extern "C" int dsv4_kv_quantize_insert(const Dsv4KvQuantizeInsertParams* p, void* stream) {
+    if (p == nullptr || p->B <= 0 || p->T <= 0 || p->rows == nullptr) return int(cudaErrorInvalidValue);
+    if (p->stride_b % 8 != 0 || p->stride_t % 8 != 0 || !aligned(p->rows, 16)) return int(cudaErrorInvalidValue);
+    KvInsertArgs a{};
+    a.B = p->B;  a.T = p->T;
+    a.rows = static_cast<const __nv_bfloat16*>(p->rows);
+    a.stride_b = p->stride_b;  a.stride_t = p->stride_t;
+    a.n_rows = p->n_rows;
+    if (!fill_cache_dest(p->dst, p->B, a.dst)) return int(cudaErrorInvalidValue);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t rows = int64_t(a.B) * a.T;
+    const int64_t want = (rows + kInsertThreads / 32 - 1) / (kInsertThreads / 32);
+    const int64_t cap = int64_t(sms) * 8;
+    const int blocks = int(want < cap ? want : cap);
+    kv_quantize_insert_kernel<<<blocks, kInsertThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return int(cudaGetLastError());
 }

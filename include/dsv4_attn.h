@@ -245,6 +245,79 @@ typedef struct Dsv4CsaCompressReduceParams {
 int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream);
 
 /*
+ * Destination of a cache insert: the paged pool of 656-byte entries and, per
+ * request, the logical index of the first entry to write (normally the number of
+ * entries the request already has).  Entry e of request b goes to page
+ * block_table[b][e / 64], slot e % 64.  A position outside the block table, or a
+ * table value outside the pool, is skipped and reported through `status`
+ * (status[0] = 16, status[1] = request, status[2] = position) - nothing is
+ * written out of bounds.  Paging has no counterpart in the reference.
+ */
+typedef struct Dsv4CacheDest {
+    void*          kv_pool;      /* uint8 [num_pages, 64, 656] */
+    const int32_t* block_table;  /* int32 [B, max_pages] */
+    const int32_t* insert_pos;   /* int32 [B] */
+    int32_t        max_pages;
+    int32_t        reserved0;
+    int64_t        num_pages;
+    int32_t*       status;       /* optional int32[4], zeroed by the caller */
+} Dsv4CacheDest;
+
+/*
+ * HCA compressor (cache-write side of the dense path): every block of m rows
+ * becomes one row; per channel, softmax over the m gating logits Z + bias weights
+ * the m value rows C.  Follows the reduce of the reference's compressor_simple
+ * (bench/bench/reference.py:108-122) and replaces the reference's kernel stub
+ * hca_compress (hca/sm100/kernel.cu:34-78, which writes FP8 with a scale of one).
+ * Output, either or both:
+ *   out  - dense BF16 [B, n/m, c];
+ *   dst  - (c must be 576) the BF16-rounded row quantised with the cache's recipe
+ *          (FP32 absmax/448 scale per 128 latent elements, e4m3 round-to-nearest-even
+ *          saturating, RoPE tail kept in BF16: the reference quantiser
+ *          bench/bench/decode.py:92-114 with this cache's tile and scale type) and
+ *          written as entry insert_pos[b] + i of request b.  Bit-identical to calling
+ *          dsv4_kv_quantize_insert on `out`.
+ * Requires c % 8 == 0, strides % 8 == 0 and 16-byte aligned pointers
+ * (cudaErrorInvalidValue otherwise).  Any m >= 1 with n % m == 0.
+ */
+typedef struct Dsv4HcaCompressParams {
+    int32_t B;              /* batch */
+    int32_t n;              /* rows per request, divisible by m */
+    int32_t c;              /* channels */
+    int32_t m;              /* compression rate (128 in the model) */
+    const void* C;          /* bf16 [B, n, c] value stream */
+    const void* Z;          /* bf16 [B, n, c] gating logits */
+    const void* bias;       /* bf16 [m, c] */
+    int64_t stride_b;       /* element strides of C and Z */
+    int64_t stride_n;
+    void*   out;            /* bf16 [B, n/m, c] contiguous, or NULL */
+    const Dsv4CacheDest* dst;   /* or NULL */
+} Dsv4HcaCompressParams;
+
+int dsv4_hca_compress_fwd(const Dsv4HcaCompressParams* p, void* stream);
+
+/*
+ * Quantise BF16 rows [B, T, 576] (512 latent + 64 RoPE) into cache entries and
+ * write them at logical positions insert_pos[b] .. insert_pos[b] + T - 1 (or
+ * n_rows[b] rows when n_rows is given).  The step that follows the CSA compressor
+ * (dsv4_csa_compress_reduce_fwd) or any other producer of new cache rows.  The
+ * quantiser is the reference's recipe (bench/bench/decode.py:92-114) with this
+ * cache's FP32 scale per 128 elements; results are bit-identical to the CPU
+ * restatement.
+ */
+typedef struct Dsv4KvQuantizeInsertParams {
+    int32_t B;
+    int32_t T;
+    const void* rows;       /* bf16 [B, T, 576] */
+    int64_t stride_b;       /* element strides, multiples of 8 */
+    int64_t stride_t;
+    const int32_t* n_rows;  /* optional int32 [B] */
+    const Dsv4CacheDest* dst;
+} Dsv4KvQuantizeInsertParams;
+
+int dsv4_kv_quantize_insert(const Dsv4KvQuantizeInsertParams* p, void* stream);
+
+/*
  * Plain-SIMT validation kernels: the same three operations computed without
  * tensor cores, one head per thread block.  They exist so that large cases can
  * be cross-checked on the device; they are slow and are not the product path.

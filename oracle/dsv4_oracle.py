@@ -314,6 +314,56 @@ def make_compress_case(seed, B, n, c_out, m=4) -> CompressCase:
                         rn(m, c_out), rn(m, c_out), m)
 
 
+def hca_compress(C, Z, bias, m):
+    """One-branch compressor of the HCA path (cache-write side).
+
+    C, Z [B, n, c] float32 (BF16-representable), bias [m, c].  Block i of m rows
+    becomes one row: out[i] = sum_j softmax_j(Z + bias)[j] * C[j], per channel.
+    Restates the part of compressor_simple after the projections
+    (bench/bench/reference.py:117-122) and the online-softmax loop of the
+    reference's kernel stub (hca/sm100/kernel.cu:57-75).  Returns float32
+    [B, n/m, c] (not yet rounded)."""
+    B, n, c = C.shape
+    nb = n // m
+    Cc = np.asarray(C, np.float32).reshape(B, nb, m, c)
+    Zz = np.asarray(Z, np.float32).reshape(B, nb, m, c) + np.asarray(bias, np.float32)
+    zmax = Zz.max(axis=2, keepdims=True)
+    e = np.exp(Zz - zmax)
+    return ((e * Cc).sum(axis=2) / e.sum(axis=2)).astype(np.float32)
+
+
+def quantize_insert(pool, block_table, insert_pos, rows, n_rows=None):
+    """Append rows to the paged cache: rows [B, T, 576] float32 (BF16-representable)
+    are quantised with this cache's recipe (`pack_entries`: FP32 absmax/448 scale per
+    128 latent elements, e4m3 cast, RoPE tail kept as BF16) and written at logical
+    positions insert_pos[b] .. insert_pos[b]+T-1 of request b through its block
+    table.  Returns a new pool.  The quantiser follows bench/bench/decode.py:92-114;
+    paging has no counterpart in the reference."""
+    pool = np.array(pool, copy=True)
+    B, T, _ = rows.shape
+    ent = pack_entries(rows[..., :D_LATENT], rows[..., D_LATENT:])
+    for b in range(B):
+        t_b = T if n_rows is None else int(n_rows[b])
+        for t in range(t_b):
+            e = int(insert_pos[b]) + t
+            pool[int(block_table[b, e // PAGE_ENTRIES]), e % PAGE_ENTRIES] = ent[b, t]
+    return pool
+
+
+@dataclass
+class HcaCompressCase:
+    C: np.ndarray
+    Z: np.ndarray
+    bias: np.ndarray
+    m: int
+
+
+def make_hca_compress_case(seed, B, n, c, m=128) -> HcaCompressCase:
+    rng = np.random.default_rng(seed)
+    rn = lambda *s: bf16_round(rng.standard_normal(s, dtype=np.float32))
+    return HcaCompressCase(rn(B, n, c), rn(B, n, c) * np.float32(2), rn(m, c), m)
+
+
 # ── the reference's own cache layout (448 e4m3 + 7 UE8M0 + 64 bf16) ─────
 
 def quantize_ue8m0(x: np.ndarray, tile: int = 64):

@@ -137,6 +137,22 @@ def gen_compress(ref, name, **kw):
     print(name, tuple(out.shape))
 
 
+def gen_hca_compress(ref, name, **kw):
+    """compressor_simple (reference.py:108-122) fed with selection matrices as
+    weights, so that its projections reproduce the two given streams exactly and
+    only its softmax-weighted reduce is exercised.  Stored as float32."""
+    import torch
+    c = orc.make_hca_compress_case(**kw)
+    B, n, co = c.C.shape
+    H = torch.from_numpy(np.concatenate([c.C, c.Z], axis=-1))                           # [B, n, 2*co]
+    sel = lambda k: torch.cat([torch.eye(co) if i == k else torch.zeros(co, co) for i in range(2)], dim=0)
+    w = ref.CompressorWeightsSimple(W_a_KV=sel(0), W_a_Z=sel(1), B_a=torch.from_numpy(c.bias))
+    out = ref.compressor_simple(H, w, c.m)
+    np.savez_compressed(HERE / f"{name}.npz", out=out.numpy().astype(np.float32),
+                        inputs_sha=sha(c.C, c.Z, c.bias), kwargs=repr(kw))
+    print(name, tuple(out.shape))
+
+
 # The cases; tests/test_oracle.py rebuilds the inputs from the same kwargs.
 CSA_CASES = {
     "csa_cfg0": dict(seed=0, B=2, s_q=1, H=16, n_entries=1024, topk=256),
@@ -149,6 +165,10 @@ HCA_CASES = {
 COMPRESS_CASES = {
     "csa_compress": dict(seed=6, B=2, n=64, c_out=128),
     "csa_compress_odd": dict(seed=7, B=1, n=12, c_out=20),
+}
+HCA_COMPRESS_CASES = {
+    "hca_compress": dict(seed=8, B=2, n=256, c=576),
+    "hca_compress_m16": dict(seed=9, B=1, n=48, c=40, m=16),
 }
 REF_CASES = {
     "ref_layout": dict(seed=4, B=1, H=128, M_cur=192, swa_len=64),
@@ -172,6 +192,8 @@ def main() -> int:
         gen_ref_layout(ref, name, **kw)
     for name, kw in COMPRESS_CASES.items():
         gen_compress(ref, name, **kw)
+    for name, kw in HCA_COMPRESS_CASES.items():
+        gen_hca_compress(ref, name, **kw)
     return 0
 
 

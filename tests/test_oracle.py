@@ -166,3 +166,39 @@ def test_compress_reduce_oracle_vs_reference(name):
     out = orc.compress_reduce(c.C_a, c.C_b, c.Z_a, c.Z_b, c.B_a, c.B_b, c.m)
     assert out.shape == z["out"].shape
     assert bf16_ulp_diff(out, z["out"]).max() <= 1
+
+
+@pytest.mark.parametrize("name", ["hca_compress", "hca_compress_m16"])
+def test_hca_compress_oracle_vs_reference(name):
+    z, kw = load(name)
+    c = orc.make_hca_compress_case(**kw)
+    assert sha(c.C, c.Z, c.bias) == str(z["inputs_sha"])
+    out = orc.hca_compress(c.C, c.Z, c.bias, c.m)
+    assert out.shape == z["out"].shape
+    np.testing.assert_allclose(out, z["out"], rtol=2e-5, atol=2e-6)
+
+
+def test_quantize_insert_places_entries():
+    """Rows appended through the block table read back (unpack_entries) as the
+    quantiser's round trip of the rows; untouched entries keep their bytes."""
+    rng = np.random.default_rng(11)
+    B, T = 3, 70
+    pages_per = 3
+    bt = rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per)
+    pool = rng.integers(0, 255, size=(B * pages_per, orc.PAGE_ENTRIES, orc.ENTRY_BYTES), dtype=np.uint8)
+    rows = orc.bf16_round(rng.standard_normal((B, T, orc.D_QK), dtype=np.float32))
+    rows[0, 0, :128] = 0           # a block of zeros gets scale 1
+    pos = np.array([0, 60, 100], np.int32)
+    n_rows = np.array([70, 64, 5], np.int32)
+    new = orc.quantize_insert(pool, bt, pos, rows, n_rows)
+    want = orc.unpack_entries(orc.pack_entries(rows[..., :512], rows[..., 512:]))
+    changed = np.zeros(pool.shape[:2], bool)
+    for b in range(B):
+        for t in range(n_rows[b]):
+            e = pos[b] + t
+            got = orc.unpack_entries(new[bt[b, e // 64], e % 64])
+            np.testing.assert_array_equal(got, want[b, t])
+            changed[bt[b, e // 64], e % 64] = True
+    assert np.array_equal(new[~changed], pool[~changed])
+    assert np.abs(want[..., :512] - rows[..., :512]).max() <= np.abs(rows).max() / 16 + 1e-6   # e4m3: 3 mantissa bits
+    assert np.array_equal(want[..., 512:], rows[..., 512:])
