@@ -58,7 +58,8 @@ class CombineParams(C.Structure):
 EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
            "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error", "dsv4_csa_compress_reduce_fwd",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
-           "dsv4_attn_workspace_bytes", "hca_decode_fwd", "dsv4_hca_compress_fwd", "dsv4_kv_quantize_insert")
+           "dsv4_attn_workspace_bytes", "hca_decode_fwd", "dsv4_hca_compress_fwd", "dsv4_kv_quantize_insert",
+           "dsv4_hca_packed_decode_fwd")
 
 
 class CsaCompressReduceParams(C.Structure):
@@ -68,6 +69,18 @@ class CsaCompressReduceParams(C.Structure):
         ("B_a", C.c_void_p), ("B_b", C.c_void_p), ("out", C.c_void_p),
         ("stride_C_b", C.c_int64), ("stride_C_n", C.c_int64), ("stride_out_b", C.c_int64),
         ("stride_out_blk", C.c_int64),
+    ]
+
+
+class HcaPackedDecodeParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("H", C.c_int32), ("page_size", C.c_int32), ("max_pages", C.c_int32),
+        ("swa_max_pages", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float), ("reserved0", C.c_int32),
+        ("num_pages", C.c_int64), ("swa_num_pages", C.c_int64),
+        ("q", C.c_void_p), ("kv_pages", C.c_void_p), ("block_table", C.c_void_p), ("m_cur", C.c_void_p),
+        ("swa_pages", C.c_void_p), ("swa_block_table", C.c_void_p), ("swa_len", C.c_void_p),
+        ("attn_sink", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("status", C.c_void_p),
     ]
 
 
@@ -113,6 +126,7 @@ def _load() -> C.CDLL:
                      ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
                      ("dsv4_csa_compress_reduce_fwd", CsaCompressReduceParams),
                      ("dsv4_hca_compress_fwd", HcaCompressParams),
+                     ("dsv4_hca_packed_decode_fwd", HcaPackedDecodeParams),
                      ("dsv4_kv_quantize_insert", KvQuantizeInsertParams),
                      ("dsv4_attn_combine", CombineParams)):
         fn = getattr(lib, name)

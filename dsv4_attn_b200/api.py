@@ -336,3 +336,54 @@ def kv_quantize_insert(rows, kv_pool, block_table, insert_pos, *, n_rows=None, s
     p = _lib.KvQuantizeInsertParams(B=B, T=T, rows=_ptr(rows), stride_b=T * c, stride_t=c, n_rows=_ptr(n_rows),
                                     dst=C.pointer(dst))
     _rc(_lib.LIB.dsv4_kv_quantize_insert(C.byref(p), _stream(rows.device)), "dsv4_kv_quantize_insert")
+
+
+REF_TOKEN_BYTES = 576      # 448 e4m3 latent + 64 BF16 RoPE values
+REF_PAGE_TOKEN_BYTES = 584 # + 7 UE8M0 scale bytes and 1 pad byte in the page's scale area
+
+
+def hca_packed_decode(q, kv_pages, block_table, m_cur, swa_pages, swa_block_table, swa_len, sm_scale, *,
+                      page_size=64, attn_sink=None, num_splits=None, out=None, lse=None, workspace=None, status=None):
+    """HCA decode over packed cache pages in the reference's byte format (see
+    Dsv4HcaPackedDecodeParams in include/dsv4_attn.h), per-request lengths m_cur / swa_len
+    int32 [B].  q bf16 [B, H, 512]; pools uint8 [pages, page_size*584].  Returns
+    (out bf16 [B, H, 512], lse f32 [B, H])."""
+    _cuda_contig(q, "q", torch.bfloat16, 3)
+    B, H, dq = q.shape
+    _check(dq == 512, "q must be [B, H, 512]")
+    _check(page_size in (16, 32, 64), "page_size must be 16, 32 or 64")
+    for name, pool, table in (("kv_pages", kv_pages, block_table), ("swa_pages", swa_pages, swa_block_table)):
+        if pool is None:
+            continue
+        _cuda_contig(pool, name, torch.uint8, 2)
+        _check(pool.shape[1] == page_size * REF_PAGE_TOKEN_BYTES, f"{name} must be [pages, page_size*{REF_PAGE_TOKEN_BYTES}]")
+        _cuda_contig(table, name + " block table", torch.int32, 2)
+        _check(table.shape[0] == B, "block tables must have one row per request")
+    _check(kv_pages is not None or swa_pages is not None, "at least one pool is needed")
+    _cuda_contig(m_cur, "m_cur", torch.int32, 1)
+    _cuda_contig(swa_len, "swa_len", torch.int32, 1)
+    _check(m_cur.shape[0] == B and swa_len.shape[0] == B, "m_cur / swa_len must be [B]")
+    if attn_sink is not None:
+        _cuda_contig(attn_sink, "attn_sink", torch.float32, 1)
+        _check(attn_sink.shape[0] == H, "attn_sink must be [H]")
+    cap = (block_table.shape[1] if kv_pages is not None else 0) * page_size + \
+          (swa_block_table.shape[1] if swa_pages is not None else 0) * page_size
+    if num_splits is None:
+        num_splits = plan_splits(B, H, cap)
+    _check(1 <= num_splits <= MAX_SPLITS, "num_splits out of range")
+    if out is None:
+        out = torch.empty(B, H, 512, dtype=torch.bfloat16, device=q.device)
+    if lse is None:
+        lse = torch.empty(B, H, dtype=torch.float32, device=q.device)
+    po, pl = workspace if workspace is not None else alloc_workspace(B, H, num_splits, q.device)
+    p = _lib.HcaPackedDecodeParams(
+        B=B, H=H, page_size=page_size, max_pages=block_table.shape[1] if kv_pages is not None else 0,
+        swa_max_pages=swa_block_table.shape[1] if swa_pages is not None else 0, num_splits=num_splits,
+        sm_scale=float(sm_scale), num_pages=kv_pages.shape[0] if kv_pages is not None else 0,
+        swa_num_pages=swa_pages.shape[0] if swa_pages is not None else 0,
+        q=_ptr(q), kv_pages=_ptr(kv_pages), block_table=_ptr(block_table) if kv_pages is not None else None, m_cur=_ptr(m_cur),
+        swa_pages=_ptr(swa_pages), swa_block_table=_ptr(swa_block_table) if swa_pages is not None else None,
+        swa_len=_ptr(swa_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
+        partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
+    _rc(_lib.LIB.dsv4_hca_packed_decode_fwd(C.byref(p), _stream(q.device)), "dsv4_hca_packed_decode_fwd")
+    return out, lse

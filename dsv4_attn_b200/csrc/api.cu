@@ -80,14 +80,14 @@ cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(2 * head_groups, rows, a.num_splits);
-    if (!(g_dbg & 16)) {
+    if (!(g_dbg & 16) || SRC == kSrcRefPaged) {
         // product path: each block computes the whole QK product for its half of the value columns
         static bool done[kMaxDevices] = {};
         constexpr int smem = SmemLayout<NCHUNK>::kTotal;
         e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
         if (e != cudaSuccess) return e;
         decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
-    } else {
+    } else if constexpr (SRC != kSrcRefPaged) {
         // evaluated alternative, kept selectable for measurements: cluster pairs that split the
         // query/key columns and exchange halves of S through distributed shared memory
         static bool done[kMaxDevices] = {};
@@ -502,4 +502,51 @@ extern "C" int dsv4_kv_quantize_insert(const Dsv4KvQuantizeInsertParams* p, void
     const int blocks = int(want < cap ? want : cap);
     kv_quantize_insert_kernel<<<blocks, kInsertThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return int(cudaGetLastError());
+}
+
+
+extern "C" int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, void* stream) {
+    if (p == nullptr || p->B <= 0 || p->B > 65535 || p->H <= 0) return int(cudaErrorInvalidValue);
+    if (p->page_size != 16 && p->page_size != 32 && p->page_size != 64) return int(cudaErrorInvalidValue);
+    if (p->q == nullptr || p->out == nullptr || !aligned(p->q, 16) || !aligned(p->out, 16)) return int(cudaErrorInvalidValue);
+    if (p->m_cur == nullptr || p->swa_len == nullptr) return int(cudaErrorInvalidValue);
+    if (!(p->sm_scale > 0.f) || !std::isfinite(p->sm_scale)) return int(cudaErrorInvalidValue);
+    // a leg may be absent altogether (null pool): its lengths must then be zero, which only the caller can know
+    if (p->kv_pages != nullptr && (p->block_table == nullptr || p->max_pages <= 0 || p->num_pages <= 0 || !aligned(p->kv_pages, 64)))
+        return int(cudaErrorInvalidValue);
+    if (p->swa_pages != nullptr && (p->swa_block_table == nullptr || p->swa_max_pages <= 0 || p->swa_num_pages <= 0 ||
+                                    !aligned(p->swa_pages, 64)))
+        return int(cudaErrorInvalidValue);
+    if (p->kv_pages == nullptr && p->swa_pages == nullptr) return int(cudaErrorInvalidValue);
+    if (p->num_splits < 1 || p->num_splits > DSV4_MAX_SPLITS) return int(cudaErrorInvalidValue);
+    if (p->num_splits > 1 && (p->partial_o == nullptr || p->partial_lse == nullptr || !aligned(p->partial_o, 16)))
+        return int(cudaErrorInvalidValue);
+
+    DecodeArgs a{};
+    a.B = p->B;  a.s_q = 1;  a.H = p->H;
+    a.scale_log2 = p->sm_scale * 1.4426950408889634f;
+    a.q = static_cast<const __nv_bfloat16*>(p->q);
+    a.out = static_cast<__nv_bfloat16*>(p->out);
+    a.lse = p->lse;
+    a.attn_sink = p->attn_sink;
+    a.kv_len = p->m_cur;  a.win_len = p->swa_len;
+    a.block_table = p->block_table;  a.max_pages = p->max_pages;
+    a.pg_kv = static_cast<const uint8_t*>(p->kv_pages);
+    a.pg_swa = static_cast<const uint8_t*>(p->swa_pages);
+    a.pg_swa_table = p->swa_block_table;  a.pg_swa_max_pages = p->swa_max_pages;
+    a.pg_page_shift = p->page_size == 64 ? 6 : (p->page_size == 32 ? 5 : 4);
+    a.pg_page_bytes = int64_t(p->page_size) * 584;
+    a.pg_num_pages = p->num_pages;  a.pg_swa_num_pages = p->swa_num_pages;
+    a.num_splits = p->num_splits;
+    a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;
+    a.status = p->status;
+    a.trace = g_trace;  a.dbg = g_dbg;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = launch_mma<8, kSrcRefPaged>(a, p->B, s);
+    if (e != cudaSuccess) return int(e);
+    if (a.num_splits > 1) {
+        CombineArgs cb = contiguous_combine(p->B, p->H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink);
+        e = launch_combine(cb, s);
+    }
+    return int(e);
 }

@@ -63,7 +63,12 @@ enum SourceKind : int {
     kSrcCsa = 0,   // index list + block table, packed 656-byte entries
     kSrcHca = 1,   // dense [0, kv_len) through the block table, then the window buffer
     kSrcRef = 2,   // reference layout: separate planes, 448 e4m3 + 7 UE8M0 + 64 bf16
+    kSrcRefPaged = 3,   // the same bytes in packed pages: per page, page_size tokens of [448 e4m3 | 64 bf16]
+                        // followed by page_size x 8 scale bytes (7 UE8M0 + 1 pad), behind block tables
 };
+
+// both kinds with the reference's quantisation (448 latent elements, one UE8M0 byte per 64)
+__host__ __device__ constexpr bool is_ref_layout(int src) { return src == kSrcRef || src == kSrcRefPaged; }
 
 enum StatusCode : int {
     kStatusOk = 0,
@@ -104,6 +109,14 @@ struct DecodeArgs {
     const uint8_t* ref_kc;  const uint8_t* ref_kc_s;  const __nv_bfloat16* ref_kc_rope;
     const uint8_t* ref_ks;  const uint8_t* ref_ks_s;  const __nv_bfloat16* ref_ks_rope;
     int ref_m_cur, ref_swa_len;
+    // packed pages (kSrcRefPaged): two pools (compressed cache, sliding window) with their block tables;
+    // per-request lengths come through kv_len / win_len
+    const uint8_t* pg_kv;  const uint8_t* pg_swa;
+    const int32_t* pg_swa_table;
+    int pg_swa_max_pages;
+    int pg_page_shift;           // log2(page_size), page_size <= 64
+    int64_t pg_page_bytes;       // page_size * 584
+    int64_t pg_num_pages, pg_swa_num_pages;
 };
 
 template <int NCHUNK>
@@ -220,6 +233,27 @@ __device__ __forceinline__ unsigned long long loader_resolve(const DecodeArgs& a
                 key = reinterpret_cast<unsigned long long>(a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656);
             }
         }
+    } else if constexpr (SRC == kSrcRefPaged) {
+        // key = address of the token's 576 data bytes (a multiple of 64) | slot of the token in its page
+        // a token outside its block table, or a table value outside the pool, is left out of the
+        // softmax instead of being read
+        if (valid) {
+            const int slot_mask = (1 << a.pg_page_shift) - 1;
+            const bool swa = v >= kv_len_n;
+            const int w = swa ? v - kv_len_n : v;
+            const uint8_t* pool = swa ? a.pg_swa : a.pg_kv;
+            const int32_t* table = swa ? a.pg_swa_table : a.block_table;
+            const int cols = swa ? a.pg_swa_max_pages : a.max_pages;
+            const int64_t pages = swa ? a.pg_swa_num_pages : a.pg_num_pages;
+            valid = pool != nullptr && (w >> a.pg_page_shift) < cols;
+            if (valid) {
+                const int page = __ldg(table + int64_t(b) * cols + (w >> a.pg_page_shift));
+                valid = page >= 0 && page < pages;
+                if (valid)
+                    key = reinterpret_cast<unsigned long long>(pool + int64_t(page) * a.pg_page_bytes + (w & slot_mask) * 576) |
+                          (unsigned long long)(w & slot_mask);
+            }
+        }
     } else {
         if (valid) {
             key = (v < a.ref_m_cur) ? (unsigned long long)(int64_t(b) * a.ref_m_cur + v)
@@ -274,13 +308,24 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long 
         const int i = 4 * g + (lane >> 3);
         const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
         if (!((vmask >> i) & 1u)) continue;
-        if constexpr (SRC != kSrcRef) {
+        if constexpr (!is_ref_layout(SRC)) {
             const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
 #pragma unroll
             for (int j = 0; j < 4; ++j) r.lat[g][j] = ptx::ldg_nc_v4(row + j * 128 + piece * 16);
             const uint4 s4 = ptx::ldg_nc_v4(row + 512);
             r.sc[g][0] = s4.x;  r.sc[g][1] = s4.y;  r.sc[g][2] = s4.z;  r.sc[g][3] = s4.w;
             r.rope[g] = ptx::ldg_nc_v4(row + 528 + piece * 16);
+        } else if constexpr (SRC == kSrcRefPaged) {
+            const int slot = int(k & 63ull);
+            const uint8_t* lp = reinterpret_cast<const uint8_t*>(k & ~63ull);
+            // the page's scale area starts after its page_size tokens: 8 bytes per token
+            const uint8_t* sp = lp + int64_t((1 << a.pg_page_shift) - slot) * 576 + slot * 8;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) r.lat[g][j] = ptx::ldg_nc_v4(lp + j * 128 + piece * 16);
+            if (piece < 4) r.lat[g][3] = ptx::ldg_nc_v4(lp + 384 + piece * 16);
+            const uint2 s2 = __ldg(reinterpret_cast<const uint2*>(sp));
+            r.sc[g][0] = s2.x;  r.sc[g][1] = s2.y;
+            r.rope[g] = ptx::ldg_nc_v4(lp + 448 + piece * 16);
         } else {
             const bool swa = (k >> 62) & 1ull;
             const int64_t e = int64_t(k & ~(1ull << 62));
@@ -306,13 +351,21 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long 
 // ahead of the loads: lane/4 picks the entry, lane%4 the 128-byte piece.
 template <int SRC>
 __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint32_t vmask, int lane) {
-    if constexpr (SRC != kSrcRef) {
+    if constexpr (!is_ref_layout(SRC)) {
         const int i = lane >> 2;
         const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
         if ((vmask >> i) & 1u) {
             const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
             ptx::prefetch_l2(row + (lane & 3) * 128);
             if ((lane & 3) < 2) ptx::prefetch_l2(row + 512 + (lane & 3) * 128);
+        }
+    } else if constexpr (SRC == kSrcRefPaged) {
+        const int i = lane >> 2;
+        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
+        if ((vmask >> i) & 1u) {
+            const uint8_t* lp = reinterpret_cast<const uint8_t*>(k & ~63ull);
+            ptx::prefetch_l2(lp + (lane & 3) * 128);
+            if ((lane & 3) == 0) ptx::prefetch_l2(lp + 512);
         }
     }
 }
@@ -335,11 +388,11 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
         const bool valid = (r.vmask >> i) & 1u;
         const uint32_t base = kv_st + c * kKvChunkBytes + uint32_t(t) * 128u;
         const uint32_t sw = uint32_t(t & 7);
-        if (SRC == kSrcRef && c >= uint32_t(NCHUNK - 1)) continue;   // reference layout: span 3 ends with chunk 6
+        if (is_ref_layout(SRC) && c >= uint32_t(NCHUNK - 1)) continue;   // reference layout: span 3 ends with chunk 6
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
         if (valid) {
             float s120;
-            if constexpr (SRC == kSrcRef) {
+            if constexpr (is_ref_layout(SRC)) {
                 // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
                 // scale, as in the reference's dequantiser
                 const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
@@ -398,7 +451,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     if constexpr (SRC == kSrcCsa) {
         n_tok = (a.topk_len != nullptr) ? min(max(__ldg(a.topk_len + n), 0), a.topk) : a.topk;
         kv_len_n = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
-    } else if constexpr (SRC == kSrcHca) {
+    } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
         kv_len_n = max(__ldg(a.kv_len + n), 0);
         n_tok = kv_len_n + max(__ldg(a.win_len + n), 0);
     } else {

@@ -245,6 +245,49 @@ typedef struct Dsv4CsaCompressReduceParams {
 int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream);
 
 /*
+ * HCA dense decode over a serving engine's packed cache pages, read in place, with
+ * per-request lengths.  The bytes are the reference cache's (448 e4m3 latent with one
+ * UE8M0 scale byte per 64 elements, 64 BF16 RoPE values; hca/params.h:27-46), laid out
+ * as the engine stores them (hca/fixes.txt:79-101): a page of page_size tokens is
+ *     [0, page_size*576)                 per token: 448 latent bytes | 128 RoPE bytes
+ *     [page_size*576, page_size*584)     per token: 7 scale bytes | 1 pad byte
+ * Token t of request b lives in page block_table[b][t / page_size], slot t % page_size.
+ * Request b attends to its first m_cur[b] compressed tokens and the first swa_len[b]
+ * tokens of its sliding-window pages, in one softmax (the per-request lengths asked for
+ * in traces/hca_vs_sglang_sigs.txt:170-176, where the reference has one scalar for the
+ * batch).  Q/O BF16 [B, H, 512]; the value row is the whole 512-wide row, the sink
+ * enters the denominator only, as in hca_decode_fwd.  page_size 16, 32 or 64; pools
+ * 64-byte aligned.  Either pool may be NULL if its lengths are all zero.
+ */
+typedef struct Dsv4HcaPackedDecodeParams {
+    int32_t B;
+    int32_t H;
+    int32_t page_size;
+    int32_t max_pages;          /* columns of block_table */
+    int32_t swa_max_pages;      /* columns of swa_block_table */
+    int32_t num_splits;         /* >= 1 */
+    float   sm_scale;
+    int32_t reserved0;
+    int64_t num_pages;          /* pages in kv_pages (bounds are the caller's responsibility) */
+    int64_t swa_num_pages;
+    const void*    q;               /* bf16 [B, H, 512] */
+    const void*    kv_pages;        /* uint8 [num_pages, page_size * 584] */
+    const int32_t* block_table;     /* int32 [B, max_pages] */
+    const int32_t* m_cur;           /* int32 [B] */
+    const void*    swa_pages;       /* uint8 [swa_num_pages, page_size * 584] */
+    const int32_t* swa_block_table; /* int32 [B, swa_max_pages] */
+    const int32_t* swa_len;         /* int32 [B] */
+    const float*   attn_sink;       /* float [H] natural-log units, or NULL */
+    void*          out;             /* bf16 [B, H, 512] */
+    float*         lse;             /* float [B, H] natural log, or NULL */
+    float*         partial_o;       /* float [num_splits, B, H, 512] when num_splits > 1 */
+    float*         partial_lse;     /* float [num_splits, B, H] */
+    int32_t*       status;          /* optional int32[4], zeroed by the caller */
+} Dsv4HcaPackedDecodeParams;
+
+int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, void* stream);
+
+/*
  * Destination of a cache insert: the paged pool of 656-byte entries and, per
  * request, the logical index of the first entry to write (normally the number of
  * entries the request already has).  Entry e of request b goes to page

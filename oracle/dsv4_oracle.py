@@ -418,6 +418,65 @@ def hca_decode_ref_layout(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink, s
     return out, lse
 
 
+REF_TOKEN_BYTES = 576        # 448 e4m3 latent + 64 BF16 RoPE values
+REF_SCALE_BYTES = 8          # 7 UE8M0 bytes + 1 pad
+
+
+def pack_ref_pages(K, K_s, K_rope, page_size, rng=None):
+    """Reference-layout planes of ONE leg, K [B, M, 448] e4m3 bytes, K_s [B, M, 7]
+    UE8M0, K_rope [B, M, 64] float32 (BF16-representable) -> (pages uint8
+    [P, page_size*584], block_table int32 [B, ceil(M/page_size)]) in the packed page
+    format of a serving engine's cache (hca/fixes.txt:79-101): per page, page_size
+    tokens of [448 latent bytes | 128 RoPE bytes], then page_size x [7 scale bytes |
+    1 pad byte].  Pages are handed out in a shuffled order; unused bytes are noise."""
+    rng = rng or np.random.default_rng(0)
+    B, M, _ = K.shape
+    per = max(1, -(-M // page_size))
+    P = B * per + 2
+    pages = rng.integers(0, 255, size=(P, page_size * (REF_TOKEN_BYTES + REF_SCALE_BYTES)), dtype=np.uint8)
+    bt = rng.permutation(P)[:B * per].astype(np.int32).reshape(B, per)
+    rope_b = f32_to_bf16_bits(K_rope).view(np.uint8).reshape(B, M, 128)
+    for b in range(B):
+        for t in range(M):
+            pg, slot = bt[b, t // page_size], t % page_size
+            o = slot * REF_TOKEN_BYTES
+            pages[pg, o:o + 448] = K[b, t]
+            pages[pg, o + 448:o + 576] = rope_b[b, t]
+            so = page_size * REF_TOKEN_BYTES + slot * REF_SCALE_BYTES
+            pages[pg, so:so + 7] = K_s[b, t]
+    return pages, bt
+
+
+def unpack_ref_pages(pages, bt_row, n, page_size):
+    """First n tokens of one request -> (K [n,448] u8, K_s [n,7] u8, K_rope [n,64] f32)."""
+    K = np.zeros((n, 448), np.uint8)
+    K_s = np.zeros((n, 7), np.uint8)
+    rope = np.zeros((n, 64), np.float32)
+    for t in range(n):
+        pg, slot = bt_row[t // page_size], t % page_size
+        o = slot * REF_TOKEN_BYTES
+        K[t] = pages[pg, o:o + 448]
+        rope[t] = bf16_bits_to_f32(np.ascontiguousarray(pages[pg, o + 448:o + 576]).view(np.uint16))
+        so = page_size * REF_TOKEN_BYTES + slot * REF_SCALE_BYTES
+        K_s[t] = pages[pg, so:so + 7]
+    return K, K_s, rope
+
+
+def hca_decode_packed_pages(Q, kv_pages, bt, m_cur, swa_pages, swa_bt, swa_len, sink, sm_scale, page_size):
+    """hca_decode_ref_layout on packed pages with per-request lengths: request b
+    attends to its first m_cur[b] compressed and swa_len[b] window tokens.  Only the
+    addressing is new; the arithmetic is the reference decode step's."""
+    B, H, dq = Q.shape
+    out = np.zeros((B, H, dq), np.uint16)
+    lse = np.zeros((B, H), np.float32)
+    for b in range(B):
+        Kc, Kc_s, Kc_r = unpack_ref_pages(kv_pages, bt[b], int(m_cur[b]), page_size)
+        Ks, Ks_s, Ks_r = unpack_ref_pages(swa_pages, swa_bt[b], int(swa_len[b]), page_size)
+        o, l = hca_decode_ref_layout(Q[b:b + 1], Kc[None], Kc_s[None], Kc_r[None], Ks[None], Ks_s[None], Ks_r[None], sink, sm_scale)
+        out[b], lse[b] = o[0], l[0]
+    return out, lse
+
+
 # ── seeded synthetic inputs (shared by tests, smoke and the CPU baseline) ──
 
 @dataclass

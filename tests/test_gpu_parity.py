@@ -358,3 +358,56 @@ def test_cluster_pair_kernel_variant(lib):
         gu.check_out(gu.out_to_f32(O), z["out_fp8_dequant"], "pair kernel reference layout")
     finally:
         lib.LIB.dsv4_debug_set_flags(0)
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_packed_pages_decode_vs_reference_outputs(lib, page_size):
+    """Packed cache pages read in place: the reference-layout golden cases repacked into
+    pages give the reference's outputs; per-request lengths give the oracle's."""
+    for name in ("ref_layout", "ref_layout_ragged"):
+        z, kw = golden(name)
+        c = orc.make_ref_layout_case(**kw)
+        B, H = c.Q.shape[:2]
+        rng = np.random.default_rng(9)
+        kv_pages, bt = orc.pack_ref_pages(c.Kc, c.Kc_s, c.Kc_rope, page_size, rng)
+        sw_pages, sbt = orc.pack_ref_pages(c.Kswa, c.Kswa_s, c.Kswa_rope, page_size, rng)
+        d = lambda a: gu.dev(a)
+        q = gu.dev(c.Q, torch.bfloat16)
+        status = lib.new_status(q.device)
+        full = (np.full(B, c.Kc.shape[1], np.int32), np.full(B, c.Kswa.shape[1], np.int32))
+        ragged = (np.array([c.Kc.shape[1] - 7, 1][:B], np.int32), np.array([0, c.Kswa.shape[1]][:B], np.int32))
+        for m_cur, swa in (full, ragged):
+            for splits in (1, 2):
+                out, lse = lib.hca_packed_decode(q, d(kv_pages), d(bt), d(m_cur), d(sw_pages), d(sbt), d(swa), c.sm_scale,
+                                                 page_size=page_size, attn_sink=gu.dev(c.sink), num_splits=splits, status=status)
+                torch.cuda.synchronize()
+                assert status.cpu().tolist() == [0, 0, 0, 0]
+                want, want_lse = orc.hca_decode_packed_pages(c.Q, kv_pages, bt, m_cur, sw_pages, sbt, swa, c.sink, c.sm_scale, page_size)
+                gu.check_out(gu.out_to_f32(out), want, f"{name} ps={page_size} splits={splits}")
+                gu.check_lse(lse.cpu().numpy(), want_lse, f"{name} ps={page_size}")
+                if m_cur is full[0]:
+                    gu.check_out(gu.out_to_f32(out), z["out_fp8_dequant"], f"{name} vs reference output")
+
+
+def test_packed_pages_decode_bad_tables_and_arguments(lib):
+    """A block-table value outside the pool drops those tokens instead of reading them; bad
+    shapes are refused on the host."""
+    c = orc.make_ref_layout_case(seed=81, B=2, H=16, M_cur=128, swa_len=16)
+    rng = np.random.default_rng(3)
+    kv_pages, bt = orc.pack_ref_pages(c.Kc, c.Kc_s, c.Kc_rope, 64, rng)
+    sw_pages, sbt = orc.pack_ref_pages(c.Kswa, c.Kswa_s, c.Kswa_rope, 64, rng)
+    q = gu.dev(c.Q, torch.bfloat16)
+    m_cur, swa = np.array([128, 128], np.int32), np.array([16, 16], np.int32)
+    bad = bt.copy()
+    bad[1, 1] = kv_pages.shape[0] + 5          # request 1 loses tokens 64..127
+    out, lse = lib.hca_packed_decode(q, gu.dev(kv_pages), gu.dev(bad), gu.dev(m_cur), gu.dev(sw_pages), gu.dev(sbt), gu.dev(swa),
+                                     c.sm_scale, num_splits=1)
+    torch.cuda.synchronize()
+    want, _ = orc.hca_decode_packed_pages(c.Q, kv_pages, bt, np.array([128, 64], np.int32), sw_pages, sbt, swa, None, c.sm_scale, 64)
+    gu.check_out(gu.out_to_f32(out), want, "bad table entry")
+    with pytest.raises(ValueError):
+        lib.hca_packed_decode(q, gu.dev(kv_pages)[:, :100].contiguous(), gu.dev(bt), gu.dev(m_cur), gu.dev(sw_pages), gu.dev(sbt),
+                              gu.dev(swa), c.sm_scale)
+    with pytest.raises(ValueError):
+        lib.hca_packed_decode(q, gu.dev(kv_pages), gu.dev(bt), gu.dev(m_cur), gu.dev(sw_pages), gu.dev(sbt), gu.dev(swa), c.sm_scale,
+                              page_size=48)

@@ -202,3 +202,28 @@ def test_quantize_insert_places_entries():
     assert np.array_equal(new[~changed], pool[~changed])
     assert np.abs(want[..., :512] - rows[..., :512]).max() <= np.abs(rows).max() / 16 + 1e-6   # e4m3: 3 mantissa bits
     assert np.array_equal(want[..., 512:], rows[..., 512:])
+
+
+def test_packed_pages_oracle_matches_reference_output():
+    """The reference-layout golden case repacked into cache pages (page sizes 16 and 64)
+    decodes to the reference's own output: packing is addressing only."""
+    z, kw = load("ref_layout_ragged")
+    c = orc.make_ref_layout_case(**kw)
+    B = c.Q.shape[0]
+    for ps in (16, 64):
+        rng = np.random.default_rng(5)
+        kv_pages, bt = orc.pack_ref_pages(c.Kc, c.Kc_s, c.Kc_rope, ps, rng)
+        sw_pages, sbt = orc.pack_ref_pages(c.Kswa, c.Kswa_s, c.Kswa_rope, ps, rng)
+        m_cur = np.full(B, c.Kc.shape[1], np.int32)
+        swa = np.full(B, c.Kswa.shape[1], np.int32)
+        out, _ = orc.hca_decode_packed_pages(c.Q, kv_pages, bt, m_cur, sw_pages, sbt, swa, c.sink, c.sm_scale, ps)
+        assert bf16_ulp_diff(out, z["out_fp8_dequant"]).max() <= 1
+        # shorter per-request lengths = the same attention over a prefix
+        m2 = np.array([40, 3], np.int32)[:B]
+        s2 = np.array([0, 19], np.int32)[:B]
+        out2, lse2 = orc.hca_decode_packed_pages(c.Q, kv_pages, bt, m2, sw_pages, sbt, s2, c.sink, c.sm_scale, ps)
+        for b in range(B):
+            want, wl = orc.hca_decode_ref_layout(c.Q[b:b + 1], c.Kc[b:b + 1, :m2[b]], c.Kc_s[b:b + 1, :m2[b]], c.Kc_rope[b:b + 1, :m2[b]],
+                                                 c.Kswa[b:b + 1, :s2[b]], c.Kswa_s[b:b + 1, :s2[b]], c.Kswa_rope[b:b + 1, :s2[b]],
+                                                 c.sink, c.sm_scale)
+            assert np.array_equal(out2[b], want[0]) and np.array_equal(lse2[b], wl[0])
