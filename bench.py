@@ -389,7 +389,7 @@ def run_ours(args):
     per_gpu_gbs = head["kv_bytes"] / (head["total_ms"] / args.steps * 1e-3) / 1e9
 
     others = {}
-    if not args.no_extras:
+    if "mixed" in args.extras:
         (csa_w, hca_w), n_mine = build_mixed(rank, world, dev)
         fc, lc, sc, st_c = make_step("csa", csa_w, None)
         fh, lh, sh, st_h = make_step("hca", hca_w, None)
@@ -411,7 +411,7 @@ def run_ours(args):
                          "sharding": "sorted by context, dealt round-robin"}
         del csa_w, hca_w
         torch.cuda.empty_cache()
-    if not args.no_extras and world == 1:
+    if "cache_write" in args.extras and world == 1:
         # the cache-write side: CSA compressor second pass (a pure streaming kernel)
         import dsv4_attn_b200 as lib
         Bc, nc, cc = 1, 65536, 512
@@ -455,6 +455,7 @@ def run_ours(args):
                                                   "hbm_frac": qbytes / (qms * 1e-3) / 1e9 / peak, "bytes": qbytes}
         del rows_q, pool_q, pool_h
         torch.cuda.empty_cache()
+    if "decode" in args.extras and world == 1:
         for name in WORKLOADS:
             if name == args.workload:
                 continue
@@ -544,7 +545,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads")
+    ap.add_argument("--extras", default="mixed,cache_write,decode",
+                    help="which groups of other workloads to run: mixed, cache_write, decode (comma-separated)")
     args = ap.parse_args()
+    args.extras = set() if args.no_extras else {x for x in args.extras.split(",") if x}
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     args.out = _claim_stdout()
     if args.impl == "reference":

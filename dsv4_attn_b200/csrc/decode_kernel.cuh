@@ -373,9 +373,9 @@ __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint3
 // Dequantise and write span j (latent chunks 2j and 2j+1) of this warp's 8 entries
 // (tile rows t0 .. t0+7, t0 a multiple of 8) into the KV stage at kv_st.  Row t of a
 // chunk is 128 bytes; 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
-// One store instruction writes 4 rows x 2 chunks x 4 column positions: every
-// 16-byte bank group is hit by exactly 4 lanes, as few shared-memory wavefronts
-// as 512 bytes need.
+// One store instruction writes 4 rows x 2 chunks x 4 column positions, arranged
+// (see the end of the function) so that it needs as few shared-memory wavefronts
+// as 512 bytes can: four.
 template <int NCHUNK, int SRC>
 __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r, int j) {
     const uint32_t piece = uint32_t(lane & 7);
@@ -407,8 +407,13 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
             dequant4(x.z, scale2, w1.x, w1.y);
             dequant4(x.w, scale2, w1.z, w1.w);
         }
-        ptx::sts_v4(base + (((2u * p) ^ sw) << 4), w0);
-        ptx::sts_v4(base + (((2u * p + 1u) ^ sw) << 4), w1);
+        // A 16-byte store is served per quarter-warp: 8 lanes = one row, both chunks.  The two
+        // chunks are 8 KB apart (same banks), so the lanes of the second chunk write their
+        // odd column first and the even one second: every quarter-warp then covers all eight
+        // 16-byte bank groups once per instruction.
+        const uint32_t flip = piece >> 2;
+        ptx::sts_v4(base + (((2u * p + flip) ^ sw) << 4), flip ? w1 : w0);
+        ptx::sts_v4(base + (((2u * p + (flip ^ 1u)) ^ sw) << 4), flip ? w0 : w1);
     }
 }
 
