@@ -50,7 +50,7 @@ constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // th
 constexpr int kLoaderRegs = 160;       // 8 x 32 x (160-128) = 8192 registers taken ...
 constexpr int kIdleRegs = 64;          // ... from 4 x 32 x (128-64) = 8192 released
 constexpr int kNumThreads = kNumWarps * 32;  // 512
-constexpr int kNumKvGroups = 3;        // hand-overs per tile from the loaders to the MMA thread
+constexpr int kNumKvGroups = 2;        // hand-overs per tile from the loaders to the MMA thread
 constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
 constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P (BF16) overwrites the first 32 of its S
@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     loader_prefetch_l2<SRC>(key4, vm4, lane);
                 }
                 if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
-                // group by group (chunks 0-3, chunks 4.., RoPE tail), so that the QK MMAs of this tile
+                // in two groups (chunks 0-3, then the rest with the RoPE tail), so that the QK MMAs of this tile
                 // start while it is still being written; one proxy fence and one arrival per group
                 const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
                 auto group_done = [&](int g) {
@@ -607,9 +607,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 group_done(0);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 2);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 3);
-                group_done(1);
                 loader_store_rope<NCHUNK, SRC>(kv_st, lw * 8, lane, regs);
-                group_done(2);
+                group_done(1);
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
                 // this set is free again: loads of tile it+2, keys of tile it+5
                 if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
@@ -674,12 +673,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 // QK is issued group by group as the loaders deliver them; between groups a ready P
                 // goes first.
                 constexpr int kNumGroups = kNumKvGroups;
-                static_assert(kNumGroups == 3, "group dispatch below is written for 3 groups");
-                // the groups the loaders deliver: chunks 0-3, the other latent chunks, the RoPE tail
+                static_assert(kNumGroups == 2, "group dispatch below is written for 2 groups");
+                // the groups the loaders deliver: chunks 0-3, then the rest with the RoPE tail
                 auto issue_qk_group = [&](int it, int g) {
                     if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 4>{});
-                    else if (g == 1) issue_qk_range(it, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK - 1>{});
-                    else issue_qk_range(it, std::integral_constant<int, NCHUNK - 1>{}, std::integral_constant<int, NCHUNK>{});
+                    else issue_qk_range(it, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK>{});
                 };
                 auto issue_pv = [&](int it) {
                     const int st = it & 1;
@@ -795,15 +793,24 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tmem_ld32(s_tmem + 32, s1);
                 ptx::tmem_wait_ld();
                 const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
-                const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
-                float x0[32], x1[32];
-                float tmax = -CUDART_INF_F;
+                if (vmask != ~0ull) {
+                    // entries that do not take part (padding, the end of the list): -inf before the scale
+                    const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    x0[i] = ((vm0 >> i) & 1u) ? __uint_as_float(s0[i]) * a.scale_log2 : -CUDART_INF_F;
-                    x1[i] = ((vm1 >> i) & 1u) ? __uint_as_float(s1[i]) * a.scale_log2 : -CUDART_INF_F;
-                    tmax = fmaxf(tmax, fmaxf(x0[i], x1[i]));
+                    for (int i = 0; i < 32; ++i) {
+                        if (!((vm0 >> i) & 1u)) s0[i] = 0xFF800000u;
+                        if (!((vm1 >> i) & 1u)) s1[i] = 0xFF800000u;
+                    }
                 }
+                // maximum of the raw logits (the scale is positive), four chains
+                float t4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        t4[k] = fmaxf(t4[k], fmaxf(__uint_as_float(s0[i + k]), __uint_as_float(s1[i + k])));
+                }
+                const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * a.scale_log2;
                 // Lazy reference maximum: move it only when the true maximum exceeds it by
                 // more than the threshold (exp2 of the excess stays <= 2^threshold).
                 float alpha = 1.f;
@@ -813,21 +820,25 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     m_ref = tmax;
                     moved = true;
                 }
-                const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-                float psum = 0.f;
+                const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
+                // p = 2^(s * scale - m): one fused multiply-add and one exp2 per element
+                float ps4[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = ptx::ex2(x0[2 * i] - m_use), p1 = ptx::ex2(x0[2 * i + 1] - m_use);
-                    psum += p0 + p1;
+                    const float p0 = ptx::ex2(fmaf(__uint_as_float(s0[2 * i]), a.scale_log2, neg_m));
+                    const float p1 = ptx::ex2(fmaf(__uint_as_float(s0[2 * i + 1]), a.scale_log2, neg_m));
+                    ps4[i & 3] += p0 + p1;
                     pk[i] = ptx::pack_bf16x2(p0, p1);
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = ptx::ex2(x1[2 * i] - m_use), p1 = ptx::ex2(x1[2 * i + 1] - m_use);
-                    psum += p0 + p1;
+                    const float p0 = ptx::ex2(fmaf(__uint_as_float(s1[2 * i]), a.scale_log2, neg_m));
+                    const float p1 = ptx::ex2(fmaf(__uint_as_float(s1[2 * i + 1]), a.scale_log2, neg_m));
+                    ps4[i & 3] += p0 + p1;
                     pk[16 + i] = ptx::pack_bf16x2(p0, p1);
                 }
+                const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
                 l_sum = l_sum * alpha + psum;
                 // Rescale O where the reference maximum moved.  The PV MMAs of the previous
                 // tile must have finished first (their commit is that stage's kv_free).
