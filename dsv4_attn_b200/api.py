@@ -387,3 +387,27 @@ def hca_packed_decode(q, kv_pages, block_table, m_cur, swa_pages, swa_block_tabl
         partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
     _rc(_lib.LIB.dsv4_hca_packed_decode_fwd(C.byref(p), _stream(q.device)), "dsv4_hca_packed_decode_fwd")
     return out, lse
+
+
+def rope_norm(x, positions, *, norm_weight=None, eps=1e-6, n_rope=64, theta=10000.0, inverse=False, out=None):
+    """Partial RoPE on the last n_rope dims of x [rows, vecs, c] (bf16) by positions [rows]
+    (int32), then an RMS norm over the whole vector when norm_weight [c] is given (the
+    reference's apply_rope followed by rms_norm, bench/bench/reference.py:35-70, 281-287).
+    `inverse=True` rotates by -position (the inverse RoPE on the attention output,
+    reference.py:308-309).  `out` may be x itself."""
+    _cuda_contig(x, "x", torch.bfloat16, 3)
+    rows, vecs, c = x.shape
+    _cuda_contig(positions, "positions", torch.int32, 1)
+    _check(positions.shape[0] == rows, "positions must be [rows]")
+    _check(n_rope == 64 and c >= 64 and (c - 64) % 8 == 0 and c - 64 <= 512, "unsupported vector width")
+    if norm_weight is not None:
+        _cuda_contig(norm_weight, "norm_weight", torch.bfloat16, 1)
+        _check(norm_weight.shape[0] == c, "norm_weight must be [c]")
+    if out is None:
+        out = torch.empty_like(x)
+    _cuda_contig(out, "out", torch.bfloat16, 3)
+    _check(out.shape == x.shape, "out must have the shape of x")
+    p = _lib.RopeNormParams(n_rows=rows, vecs_per_row=vecs, c=c, n_rope=n_rope, inverse=1 if inverse else 0, eps=float(eps),
+                            theta=float(theta), x=_ptr(x), out=_ptr(out), positions=_ptr(positions), norm_weight=_ptr(norm_weight))
+    _rc(_lib.LIB.dsv4_rope_norm_fwd(C.byref(p), _stream(x.device)), "dsv4_rope_norm_fwd")
+    return out

@@ -11,6 +11,7 @@
 #include "combine.cuh"
 #include "compress_reduce.cuh"
 #include "cache_write.cuh"
+#include "rope_norm.cuh"
 #include "decode_kernel.cuh"
 #include "decode_pair.cuh"
 #include "decode_simt.cuh"
@@ -549,4 +550,27 @@ extern "C" int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, vo
         e = launch_combine(cb, s);
     }
     return int(e);
+}
+
+
+extern "C" int dsv4_rope_norm_fwd(const Dsv4RopeNormParams* p, void* stream) {
+    if (p == nullptr || p->n_rows <= 0 || p->vecs_per_row <= 0 || p->x == nullptr || p->out == nullptr || p->positions == nullptr)
+        return int(cudaErrorInvalidValue);
+    if (p->n_rope != 64 || p->c < p->n_rope || (p->c - p->n_rope) % 8 != 0 || p->c - p->n_rope > 512) return int(cudaErrorInvalidValue);
+    if (!aligned(p->x, 16) || !aligned(p->out, 16) || (p->norm_weight != nullptr && !aligned(p->norm_weight, 16))) return int(cudaErrorInvalidValue);
+    if (!(p->theta > 1.f) || !std::isfinite(p->theta) || !(p->eps >= 0.f)) return int(cudaErrorInvalidValue);
+    RopeNormArgs a{};
+    a.n_rows = p->n_rows;  a.vecs_per_row = p->vecs_per_row;  a.c = p->c;  a.n_rope = p->n_rope;  a.inverse = p->inverse ? 1 : 0;
+    a.eps = p->eps;  a.theta = p->theta;
+    a.x = static_cast<const __nv_bfloat16*>(p->x);
+    a.out = static_cast<__nv_bfloat16*>(p->out);
+    a.positions = p->positions;
+    a.weight = static_cast<const __nv_bfloat16*>(p->norm_weight);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t vecs = a.n_rows * a.vecs_per_row;
+    const int64_t want = (vecs + kRopeNormThreads / 32 - 1) / (kRopeNormThreads / 32);
+    const int64_t cap = int64_t(sms) * 8;
+    rope_norm_kernel<<<int(want < cap ? want : cap), kRopeNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return int(cudaGetLastError());
 }

@@ -245,6 +245,34 @@ typedef struct Dsv4CsaCompressReduceParams {
 int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream);
 
 /*
+ * Pre- and post-pass around the attention: partial RoPE on the last n_rope dimensions
+ * of each vector (split-halves pairing, frequencies 1 / theta^(2i / n_rope); the
+ * reference's apply_rope, bench/bench/reference.py:35-65), then - when norm_weight
+ * is given - an RMS norm over the whole vector (rms_norm, reference.py:68-70), in
+ * the order the reference's attention applies them to queries and keys
+ * (reference.py:281-287).  inverse = 1 rotates by -position: the inverse RoPE the
+ * reference applies to the attention output (reference.py:308-309), normally with
+ * norm_weight = NULL.  x and out BF16 [n_rows, vecs_per_row, c] contiguous (out may
+ * alias x); all vecs_per_row vectors of a row (the heads of a query token) share
+ * positions[row].  n_rope = 64; c - 64 a multiple of 8, at most 512.
+ */
+typedef struct Dsv4RopeNormParams {
+    int64_t n_rows;
+    int32_t vecs_per_row;
+    int32_t c;
+    int32_t n_rope;
+    int32_t inverse;
+    float   eps;
+    float   theta;              /* 10000 in the reference */
+    const void*    x;
+    void*          out;
+    const int32_t* positions;   /* int32 [n_rows] */
+    const void*    norm_weight; /* bf16 [c] or NULL */
+} Dsv4RopeNormParams;
+
+int dsv4_rope_norm_fwd(const Dsv4RopeNormParams* p, void* stream);
+
+/*
  * HCA dense decode over a serving engine's packed cache pages, read in place, with
  * per-request lengths.  The bytes are the reference cache's (448 e4m3 latent with one
  * UE8M0 scale byte per 64 elements, 64 BF16 RoPE values; hca/params.h:27-46), laid out

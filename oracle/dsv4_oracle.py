@@ -418,6 +418,28 @@ def hca_decode_ref_layout(Q, Kc, Kc_s, Kc_rope, Kswa, Kswa_s, Kswa_rope, sink, s
     return out, lse
 
 
+def rope_norm(x, positions, weight=None, eps=1e-6, n_rope=64, theta=10000.0, inverse=False):
+    """Partial RoPE on the last n_rope dims, then (with `weight`) an RMS norm over the whole
+    vector.  x [rows, vecs, c] float32 (BF16-representable), positions [rows].  Restates
+    apply_rope (bench/bench/reference.py:35-65: split-halves pairing, freqs =
+    1 / theta^(2i/n_rope), x_rot = [x1 cos - x2 sin, x1 sin + x2 cos]) followed by
+    rms_norm (reference.py:68-70), the order of the reference's attention
+    (reference.py:281-287); inverse=True is its output-side rotation by -position
+    (reference.py:308-309).  Returns float32, not yet rounded."""
+    x = np.asarray(x, np.float32)
+    half = n_rope // 2
+    freqs = (np.float32(1.0) / (np.float32(theta) ** (np.arange(0, n_rope, 2, dtype=np.float32) / np.float32(n_rope)))).astype(np.float32)
+    pos = np.asarray(positions, np.float32) * (np.float32(-1.0) if inverse else np.float32(1.0))
+    ang = (pos[:, None, None] * freqs).astype(np.float32)
+    cs, sn = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    x1, x2 = x[..., -n_rope:-half], x[..., -half:]
+    out = np.concatenate([x[..., :-n_rope], x1 * cs - x2 * sn, x1 * sn + x2 * cs], axis=-1).astype(np.float32)
+    if weight is not None:
+        rms = np.sqrt((out * out).mean(axis=-1, keepdims=True, dtype=np.float32) + np.float32(eps)).astype(np.float32)
+        out = (out / rms * np.asarray(weight, np.float32)).astype(np.float32)
+    return out
+
+
 REF_TOKEN_BYTES = 576        # 448 e4m3 latent + 64 BF16 RoPE values
 REF_SCALE_BYTES = 8          # 7 UE8M0 bytes + 1 pad
 

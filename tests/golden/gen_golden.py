@@ -153,6 +153,29 @@ def gen_hca_compress(ref, name, **kw):
     print(name, tuple(out.shape))
 
 
+def make_rope_norm_inputs(seed, rows, vecs, c, max_pos):
+    rng = np.random.default_rng(seed)
+    x = orc.bf16_round(rng.standard_normal((rows, vecs, c), dtype=np.float32))
+    pos = rng.integers(0, max_pos, size=rows).astype(np.int32)
+    w = orc.bf16_round((1.0 + 0.1 * rng.standard_normal(c)).astype(np.float32))
+    return x, pos, w
+
+
+def gen_rope_norm(ref, name, **kw):
+    """apply_rope (+ rms_norm) of the reference on BF16-representable float32 inputs:
+    `q` = RoPE by +pos then norm (reference.py:281-287), `o` = RoPE by -pos, no norm
+    (reference.py:308-309).  Stored as float32."""
+    import torch
+    x, pos, w = make_rope_norm_inputs(**kw)
+    xt = torch.from_numpy(x)
+    p = torch.from_numpy(pos).unsqueeze(1).expand(-1, x.shape[1])
+    q = ref.rms_norm(ref.apply_rope(xt, p, 64), torch.from_numpy(w), 1e-6)
+    o = ref.apply_rope(xt, -p, 64)
+    np.savez_compressed(HERE / f"{name}.npz", q=q.numpy().astype(np.float32), o=o.numpy().astype(np.float32),
+                        inputs_sha=sha(x, pos, w), kwargs=repr(kw))
+    print(name, tuple(q.shape))
+
+
 # The cases; tests/test_oracle.py rebuilds the inputs from the same kwargs.
 CSA_CASES = {
     "csa_cfg0": dict(seed=0, B=2, s_q=1, H=16, n_entries=1024, topk=256),
@@ -169,6 +192,10 @@ COMPRESS_CASES = {
 HCA_COMPRESS_CASES = {
     "hca_compress": dict(seed=8, B=2, n=256, c=576),
     "hca_compress_m16": dict(seed=9, B=1, n=48, c=40, m=16),
+}
+ROPE_NORM_CASES = {
+    "rope_norm_q576": dict(seed=12, rows=6, vecs=16, c=576, max_pos=4096),
+    "rope_norm_o512": dict(seed=13, rows=5, vecs=8, c=512, max_pos=100000),
 }
 REF_CASES = {
     "ref_layout": dict(seed=4, B=1, H=128, M_cur=192, swa_len=64),
@@ -194,6 +221,8 @@ def main() -> int:
         gen_compress(ref, name, **kw)
     for name, kw in HCA_COMPRESS_CASES.items():
         gen_hca_compress(ref, name, **kw)
+    for name, kw in ROPE_NORM_CASES.items():
+        gen_rope_norm(ref, name, **kw)
     return 0
 
 

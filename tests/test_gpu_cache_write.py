@@ -167,3 +167,32 @@ def test_written_entries_are_read_by_the_decode_kernel(lib):
     want_out, want_lse = orc.hca_dense_decode(q, want_pool, bt, kv_len, win, win_len, sm)
     gu.check_out(gu.out_to_f32(out), want_out, "decode over inserted entries")
     gu.check_lse(lse.cpu().numpy(), want_lse, "decode over inserted entries")
+
+
+@pytest.mark.parametrize("name", ["rope_norm_q576", "rope_norm_o512"])
+def test_rope_norm_vs_reference_outputs(lib, name):
+    """Query pre-pass (RoPE then RMS norm) and output post-pass (inverse RoPE) against the
+    reference's apply_rope / rms_norm outputs: within 2 BF16 ulps (a few at large angles,
+    where float32 cos/sin of different libraries differ in the last place)."""
+    from tests.golden.gen_golden import make_rope_norm_inputs
+    from tests.test_oracle import bf16_ulp_diff
+    z, kw = golden(name)
+    x, pos, w = make_rope_norm_inputs(**kw)
+    dx, dpos, dw = bf(x), gu.dev(pos), bf(w)
+    q = lib.rope_norm(dx, dpos, norm_weight=dw, eps=1e-6)
+    o = lib.rope_norm(dx, dpos, inverse=True)
+    torch.cuda.synchronize()
+    bits = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    big = kw["max_pos"] > 10000
+    for got, want in ((q, z["q"]), (o, z["o"])):
+        d = bf16_ulp_diff(bits(got), orc.f32_to_bf16_bits(want), abs_ok=5e-3 if big else 2e-6)
+        assert d.max() <= 2 and (d > 1).mean() < 1e-3
+    # in place, and forth-and-back = identity up to BF16 rounding of the rotated pair
+    y = dx.clone()
+    lib.rope_norm(y, dpos, out=y)
+    lib.rope_norm(y, dpos, inverse=True, out=y)
+    torch.cuda.synchronize()
+    assert torch.equal(y[..., :-64], dx[..., :-64])
+    assert (y[..., -64:].float() - dx[..., -64:].float()).abs().max().item() <= 4e-2
+    with pytest.raises(ValueError):
+        lib.rope_norm(dx[..., :100].contiguous(), dpos)

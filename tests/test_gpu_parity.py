@@ -411,3 +411,19 @@ def test_packed_pages_decode_bad_tables_and_arguments(lib):
     with pytest.raises(ValueError):
         lib.hca_packed_decode(q, gu.dev(kv_pages), gu.dev(bt), gu.dev(m_cur), gu.dev(sw_pages), gu.dev(sbt), gu.dev(swa), c.sm_scale,
                               page_size=48)
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_csa_with_attention_sink(lib, splits):
+    """The sink option of the CSA entry point (the reference applies the sink in its dense
+    softmax, bench/bench/reference.py:294-303, and in its merge, hca/sm100/combine.cu:83-89):
+    it enters the denominator only, unsplit and split alike; the LSE stays sink-free."""
+    case = orc.make_csa_case(seed=91, B=2, s_q=2, H=32, n_entries=[400, 77], topk=256, ragged=True)
+    sink = np.random.default_rng(91).standard_normal(32).astype(np.float32)
+    want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale,
+                                               kv_len=case.kv_len, sink=sink)
+    out, lse = run_csa(lib, case, num_splits=splits, attn_sink=gu.dev(sink))
+    gu.check_out(out, want_out, f"csa sink splits={splits}")
+    gu.check_lse(lse, want_lse, f"csa sink splits={splits}")
+    no_sink, _ = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale, kv_len=case.kv_len)
+    assert np.abs(gu.bits_to_f32(no_sink) - gu.bits_to_f32(want_out)).max() > 1e-2     # the sink matters in this case

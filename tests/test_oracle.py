@@ -227,3 +227,18 @@ def test_packed_pages_oracle_matches_reference_output():
                                                  c.Kswa[b:b + 1, :s2[b]], c.Kswa_s[b:b + 1, :s2[b]], c.Kswa_rope[b:b + 1, :s2[b]],
                                                  c.sink, c.sm_scale)
             assert np.array_equal(out2[b], want[0]) and np.array_equal(lse2[b], wl[0])
+
+
+@pytest.mark.parametrize("name", ["rope_norm_q576", "rope_norm_o512"])
+def test_rope_norm_oracle_vs_reference(name):
+    from tests.golden.gen_golden import make_rope_norm_inputs
+    z, kw = load(name)
+    x, pos, w = make_rope_norm_inputs(**kw)
+    assert sha(x, pos, w) == str(z["inputs_sha"])
+    # angles reach 1e5 rad in the second case: float32 pow/cos differ between libraries in the last place
+    tol = dict(rtol=1e-4, atol=5e-3 if kw["max_pos"] > 10000 else 5e-4)
+    np.testing.assert_allclose(orc.rope_norm(x, pos, w, eps=1e-6), z["q"], **tol)
+    np.testing.assert_allclose(orc.rope_norm(x, pos, None, inverse=True), z["o"], **tol)
+    # rotating forth and back is the identity
+    back = orc.rope_norm(orc.rope_norm(x, pos), pos, inverse=True)
+    np.testing.assert_allclose(back, x, rtol=1e-4, atol=1e-4)
