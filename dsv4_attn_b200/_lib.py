@@ -59,7 +59,7 @@ EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", 
            "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error", "dsv4_csa_compress_reduce_fwd",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
            "dsv4_attn_workspace_bytes", "hca_decode_fwd", "dsv4_hca_compress_fwd", "dsv4_kv_quantize_insert",
-           "dsv4_hca_packed_decode_fwd", "dsv4_rope_norm_fwd")
+           "dsv4_hca_packed_decode_fwd", "dsv4_rope_norm_fwd", "dsv4_indexer_topk_fwd")
 
 
 class CsaCompressReduceParams(C.Structure):
@@ -89,6 +89,15 @@ class RopeNormParams(C.Structure):
         ("n_rows", C.c_int64), ("vecs_per_row", C.c_int32), ("c", C.c_int32), ("n_rope", C.c_int32), ("inverse", C.c_int32),
         ("eps", C.c_float), ("theta", C.c_float), ("x", C.c_void_p), ("out", C.c_void_p), ("positions", C.c_void_p),
         ("norm_weight", C.c_void_p),
+    ]
+
+
+class IndexerTopkParams(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("s_q", C.c_int32), ("max_pages", C.c_int32), ("k", C.c_int32),
+        ("num_pages", C.c_int64), ("score_stride", C.c_int64),
+        ("q_fp8", C.c_void_p), ("q_weight", C.c_void_p), ("key_pages", C.c_void_p), ("block_table", C.c_void_p),
+        ("n_vis", C.c_void_p), ("scores", C.c_void_p), ("out_indices", C.c_void_p), ("status", C.c_void_p),
     ]
 
 
@@ -134,6 +143,7 @@ def _load() -> C.CDLL:
                      ("dsv4_hca_dense_decode_simt", HcaDenseDecodeParams),
                      ("dsv4_csa_compress_reduce_fwd", CsaCompressReduceParams),
                      ("dsv4_hca_compress_fwd", HcaCompressParams),
+                     ("dsv4_indexer_topk_fwd", IndexerTopkParams),
                      ("dsv4_rope_norm_fwd", RopeNormParams),
                      ("dsv4_hca_packed_decode_fwd", HcaPackedDecodeParams),
                      ("dsv4_kv_quantize_insert", KvQuantizeInsertParams),

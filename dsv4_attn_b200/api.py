@@ -411,3 +411,43 @@ def rope_norm(x, positions, *, norm_weight=None, eps=1e-6, n_rope=64, theta=1000
                             theta=float(theta), x=_ptr(x), out=_ptr(out), positions=_ptr(positions), norm_weight=_ptr(norm_weight))
     _rc(_lib.LIB.dsv4_rope_norm_fwd(C.byref(p), _stream(x.device)), "dsv4_rope_norm_fwd")
     return out
+
+
+INDEXER_HEADS = 64
+INDEXER_DIM = 128
+INDEXER_PAGE_BYTES = 64 * 128 + 64 * 4
+
+
+def indexer_topk(q_fp8, q_weight, key_pages, block_table, n_vis, k, *, scores=None, out=None, status=None):
+    """CSA indexer for decode: top-k visible entries per query token (see
+    Dsv4IndexerTopkParams).  q_fp8 uint8 [B, s_q, 64, 128] (e4m3), q_weight f32 [B, s_q, 64],
+    key_pages uint8 [pages, 8448], block_table int32 [B, max_pages], n_vis int32 [B, s_q].
+    Returns (indices int32 [B, s_q, k], scores f32 [B*s_q, stride])."""
+    _cuda_contig(q_fp8, "q_fp8", torch.uint8, 4)
+    B, s_q, nh, dim = q_fp8.shape
+    _check(nh == INDEXER_HEADS and dim == INDEXER_DIM, "q_fp8 must be [B, s_q, 64, 128]")
+    _check(s_q in (1, 2), "s_q must be 1 or 2")
+    _cuda_contig(q_weight, "q_weight", torch.float32, 3)
+    _check(tuple(q_weight.shape) == (B, s_q, nh), "q_weight must be [B, s_q, 64]")
+    _cuda_contig(key_pages, "key_pages", torch.uint8, 2)
+    _check(key_pages.shape[1] == INDEXER_PAGE_BYTES, f"key_pages must be [pages, {INDEXER_PAGE_BYTES}]")
+    _cuda_contig(block_table, "block_table", torch.int32, 2)
+    _check(block_table.shape[0] == B, "block_table must have one row per request")
+    _cuda_contig(n_vis, "n_vis", torch.int32, 2)
+    _check(tuple(n_vis.shape) == (B, s_q), "n_vis must be [B, s_q]")
+    _check(k >= 1, "k must be positive")
+    stride = block_table.shape[1] * 64
+    if scores is None:
+        scores = torch.empty(B * s_q, stride, dtype=torch.float32, device=q_fp8.device)
+    _cuda_contig(scores, "scores", torch.float32, 2)
+    _check(scores.shape[0] == B * s_q and scores.shape[1] >= stride, "scores must be [B*s_q, >= max_pages*64]")
+    if out is None:
+        out = torch.empty(B, s_q, k, dtype=torch.int32, device=q_fp8.device)
+    _cuda_contig(out, "out", torch.int32, 3)
+    _check(tuple(out.shape) == (B, s_q, k), "out must be [B, s_q, k]")
+    p = _lib.IndexerTopkParams(B=B, s_q=s_q, max_pages=block_table.shape[1], k=k, num_pages=key_pages.shape[0],
+                               score_stride=scores.shape[1], q_fp8=_ptr(q_fp8), q_weight=_ptr(q_weight), key_pages=_ptr(key_pages),
+                               block_table=_ptr(block_table), n_vis=_ptr(n_vis), scores=_ptr(scores), out_indices=_ptr(out),
+                               status=_ptr(status))
+    _rc(_lib.LIB.dsv4_indexer_topk_fwd(C.byref(p), _stream(q_fp8.device)), "dsv4_indexer_topk_fwd")
+    return out, scores

@@ -12,6 +12,7 @@
 #include "compress_reduce.cuh"
 #include "cache_write.cuh"
 #include "rope_norm.cuh"
+#include "indexer.cuh"
 #include "decode_kernel.cuh"
 #include "decode_pair.cuh"
 #include "decode_simt.cuh"
@@ -572,5 +573,60 @@ extern "C" int dsv4_rope_norm_fwd(const Dsv4RopeNormParams* p, void* stream) {
     const int64_t want = (vecs + kRopeNormThreads / 32 - 1) / (kRopeNormThreads / 32);
     const int64_t cap = int64_t(sms) * 8;
     rope_norm_kernel<<<int(want < cap ? want : cap), kRopeNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return int(cudaGetLastError());
+}
+
+
+namespace {
+cudaError_t make_byte_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows, bool swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {128, cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {128};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+}  // namespace
+
+extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* stream) {
+    if (p == nullptr || p->B <= 0 || p->B > 65535 || (p->s_q != 1 && p->s_q != 2) || p->max_pages <= 0 || p->num_pages <= 0 || p->k <= 0)
+        return int(cudaErrorInvalidValue);
+    if (p->q_fp8 == nullptr || p->q_weight == nullptr || p->key_pages == nullptr || p->block_table == nullptr || p->n_vis == nullptr ||
+        p->scores == nullptr || p->out_indices == nullptr)
+        return int(cudaErrorInvalidValue);
+    if (!aligned(p->q_fp8, 128) || !aligned(p->key_pages, 128) || !aligned(p->scores, 16)) return int(cudaErrorInvalidValue);
+    if (p->score_stride < int64_t(p->max_pages) * kIdxPageKeys) return int(cudaErrorInvalidValue);
+    if (p->num_pages * kIdxPageRows > 0x7FFFFFFFll) return int(cudaErrorInvalidValue);      // TMA coordinates are 32-bit
+    IndexerArgs a{};
+    cudaError_t e = make_byte_map(&a.key_map, p->key_pages, uint64_t(p->num_pages) * kIdxPageRows, kIdxPageKeys, true);
+    if (e == cudaSuccess) e = make_byte_map(&a.scale_map, p->key_pages, uint64_t(p->num_pages) * kIdxPageRows, 2, false);
+    if (e == cudaSuccess) e = make_byte_map(&a.q_map, p->q_fp8, uint64_t(p->B) * p->s_q * kIdxHeads, uint32_t(p->s_q * kIdxHeads), true);
+    if (e != cudaSuccess) return int(e);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles_cap = (p->max_pages + 1) / 2;
+    int ctas = (4 * sms + p->B - 1) / p->B;
+    if (ctas < 1) ctas = 1;
+    if (ctas > tiles_cap) ctas = tiles_cap;
+    a.tiles_per_cta = (tiles_cap + ctas - 1) / ctas;
+    const int grid_x = (tiles_cap + a.tiles_per_cta - 1) / a.tiles_per_cta;
+    a.B = p->B;  a.s_q = p->s_q;  a.max_pages = p->max_pages;  a.num_pages = p->num_pages;
+    a.q_weight = p->q_weight;  a.block_table = p->block_table;  a.n_vis = p->n_vis;
+    a.scores = p->scores;  a.score_stride = p->score_stride;  a.status = p->status;
+    static bool done[kMaxDevices] = {};
+    e = ensure_smem(indexer_logits_kernel, kIdxSmemBytes, done);
+    if (e != cudaSuccess) return int(e);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    indexer_logits_kernel<<<dim3(grid_x, p->B), kIdxThreads, kIdxSmemBytes, s>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return int(e);
+    TopkArgs t{};
+    t.rows = p->B * p->s_q;  t.k = p->k;  t.scores = p->scores;  t.stride = p->score_stride;  t.n_vis = p->n_vis;
+    t.out = p->out_indices;  t.n_cap = p->max_pages * kIdxPageKeys;
+    topk_select_kernel<<<t.rows, kTopkThreads, 0, s>>>(t);
     return int(cudaGetLastError());
 }

@@ -1,0 +1,315 @@
+// CSA indexer for decode: which compressed entries does each query token attend to?
+//
+//   score[t, s] = sum_h  w[t, h] * relu( q[t, h, :] . k[s, :] ) * kscale[s]
+//   top-k over the s < n_vis[t] visible entries.
+//
+// Two kernels.
+//  * indexer_logits_kernel: FP8 x FP8 -> FP32 on the tensor cores
+//    (tcgen05.mma kind::f8f6f4).  The keys are the M side - 128 keys of two cache
+//    pages per MMA, brought into shared memory by TMA straight from the paged
+//    pool - and the 64 heads of each query token the N side, so that the head
+//    reduction (ReLU, weight, sum) runs inside one thread of the epilogue: tensor
+//    memory lane = key, columns = (token, head).  Warp roles: one TMA producer
+//    lane, one MMA-issuing lane, four epilogue warps; a ring of key stages and two
+//    accumulator buffers in tensor memory decouple the three.
+//  * topk_select_kernel: per (request, token) row a radix select over the FP32
+//    scores (four 8-bit rounds, histograms in shared memory), then a compaction
+//    pass that writes the indices of the k best (unordered; -1 padded).
+//
+// Key page: 64 keys x 128 e4m3 bytes, then the 64 FP32 scales of those keys
+// (8448 bytes = 66 rows of 128 bytes).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "decode_kernel.cuh"   // report_timeout, status codes, kWaitTimeoutNs
+
+namespace dsv4 {
+
+constexpr int kIdxHeads = 64;
+constexpr int kIdxDim = 128;
+constexpr int kIdxPageKeys = 64;
+constexpr int kIdxPageRows = 66;                        // 128-byte rows per page: 64 of keys, 2 of scales
+constexpr int kIdxPageBytes = kIdxPageRows * 128;       // 8448
+constexpr int kIdxTileKeys = 128;                       // keys per MMA tile (two pages)
+constexpr int kIdxStages = 4;
+constexpr int kIdxThreads = 192;                        // producer warp, MMA warp, four epilogue warps
+constexpr int kIdxTmemCols = 256;                       // two accumulator buffers of up to 128 columns
+constexpr int kStatusWaitIndexer = 32;
+
+struct IndexerArgs {
+    alignas(64) CUtensorMap key_map;     // pool as [num_pages*66, 128] bytes, box 64 rows, 128-byte swizzle
+    alignas(64) CUtensorMap scale_map;   // same memory, box 2 rows, no swizzle
+    alignas(64) CUtensorMap q_map;       // q as [B*s_q*64, 128] bytes, box s_q*64 rows, 128-byte swizzle
+    int B, s_q, max_pages, tiles_per_cta;
+    int64_t num_pages;
+    const float* q_weight;               // [B, s_q, 64]
+    const int32_t* block_table;          // [B, max_pages]
+    const int32_t* n_vis;                // [B, s_q]
+    float* scores;                       // [B*s_q, score_stride]
+    int64_t score_stride;
+    int32_t* status;
+};
+
+struct IdxSmem {
+    uint64_t full[kIdxStages];
+    uint64_t empty[kIdxStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint64_t q_full;
+    uint32_t tmem_base;
+    uint32_t page_ok[kIdxStages];        // bit j: page j of the stage was loaded
+    float weight[2 * kIdxHeads];
+};
+
+constexpr int kIdxQBytes = 2 * kIdxHeads * kIdxDim;                 // up to two query tokens
+constexpr int kIdxStageKeyBytes = kIdxTileKeys * kIdxDim;           // 16 KB
+constexpr int kIdxScaleBytes = 2 * 256;                             // two pages x 64 floats
+constexpr int kIdxSmemBytes = 1024 + kIdxQBytes + kIdxStages * kIdxStageKeyBytes + kIdxStages * kIdxScaleBytes + 1024;
+
+// Instruction descriptor for kind::f8f6f4 with e4m3 operands (format code 0), K-major, FP32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int M, int N) {
+    return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __grid_constant__ IndexerArgs a) {
+    extern __shared__ uint8_t idx_smem_raw[];
+    const uint32_t base = (ptx::smem_u32(idx_smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = idx_smem_raw + (base - ptx::smem_u32(idx_smem_raw));
+    const uint32_t q_smem = base;
+    const uint32_t key_smem = base + kIdxQBytes;
+    const uint32_t scale_smem = key_smem + kIdxStages * kIdxStageKeyBytes;
+    const float* scale_gen = reinterpret_cast<const float*>(gen + kIdxQBytes + kIdxStages * kIdxStageKeyBytes);
+    IdxSmem* sm = reinterpret_cast<IdxSmem*>(gen + kIdxQBytes + kIdxStages * kIdxStageKeyBytes + kIdxStages * kIdxScaleBytes);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.y;
+    const int N = a.s_q * kIdxHeads;
+
+    int vis_max = 0;
+    for (int t = 0; t < a.s_q; ++t) vis_max = max(vis_max, __ldg(a.n_vis + b * a.s_q + t));
+    vis_max = min(vis_max, a.max_pages * kIdxPageKeys);
+    const int tiles_total = (vis_max + kIdxTileKeys - 1) / kIdxTileKeys;
+    const int tile0 = min(int(blockIdx.x) * a.tiles_per_cta, tiles_total);
+    const int tile1 = min(tile0 + a.tiles_per_cta, tiles_total);
+    const int ntiles = tile1 - tile0;
+    if (ntiles <= 0) return;                                  // whole block, before any barrier or allocation
+
+    const uint32_t bar_full = ptx::smem_u32(&sm->full[0]), bar_empty = ptx::smem_u32(&sm->empty[0]);
+    const uint32_t bar_acc_full = ptx::smem_u32(&sm->acc_full[0]), bar_acc_empty = ptx::smem_u32(&sm->acc_empty[0]);
+    const uint32_t bar_q = ptx::smem_u32(&sm->q_full);
+
+    if (tid == 0) {
+        for (int s = 0; s < kIdxStages; ++s) { ptx::mbar_init(bar_full + 8 * s, 1);  ptx::mbar_init(bar_empty + 8 * s, 1 + 4); }
+        for (int d = 0; d < 2; ++d) { ptx::mbar_init(bar_acc_full + 8 * d, 1);  ptx::mbar_init(bar_acc_empty + 8 * d, 4); }
+        ptx::mbar_init(bar_q, 1);
+        ptx::fence_mbar_init();
+    }
+    if (tid < N) sm->weight[tid] = __ldg(a.q_weight + int64_t(b) * N + tid);
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&sm->tmem_base), kIdxTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = sm->tmem_base;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ───────────── producer: Q once, then key pages and their scales, stage by stage ─────────────
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(bar_q, uint32_t(N) * kIdxDim);
+            ptx::tma_load_2d(q_smem, &a.q_map, 0, b * N, bar_q);
+            const int pages_vis = (vis_max + kIdxPageKeys - 1) / kIdxPageKeys;
+            for (int i = 0; i < ntiles && ok; ++i) {
+                const int st = i % kIdxStages;
+                if (i >= kIdxStages && !ptx::mbar_wait(bar_empty + 8 * st, uint32_t(i / kIdxStages - 1) & 1u, kWaitTimeoutNs)) {
+                    report_timeout(a.status, kStatusWaitIndexer, 0, tile0 + i);
+                    ok = false;
+                    break;
+                }
+                int page[2];
+                uint32_t okmask = 0, bytes = 0;
+                for (int j = 0; j < 2; ++j) {
+                    const int lp = 2 * (tile0 + i) + j;            // logical page of the request
+                    page[j] = (lp < pages_vis) ? __ldg(a.block_table + int64_t(b) * a.max_pages + lp) : -1;
+                    if (page[j] >= 0 && page[j] < a.num_pages) { okmask |= 1u << j;  bytes += kIdxPageKeys * kIdxDim + 256; }
+                }
+                sm->page_ok[st] = okmask;
+                ptx::mbar_arrive_expect_tx(bar_full + 8 * st, bytes);
+                for (int j = 0; j < 2; ++j) {
+                    if (!((okmask >> j) & 1u)) continue;
+                    ptx::tma_load_2d(key_smem + st * kIdxStageKeyBytes + j * (kIdxPageKeys * kIdxDim), &a.key_map, 0,
+                                     page[j] * kIdxPageRows, bar_full + 8 * st);
+                    ptx::tma_load_2d(scale_smem + st * kIdxScaleBytes + j * 256, &a.scale_map, 0,
+                                     page[j] * kIdxPageRows + kIdxPageKeys, bar_full + 8 * st);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ───────────── MMA issue: S^T[128 keys x N] = K[128 x 128] . Q[N x 128]^T, four K steps of 32 ─────────────
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_e4m3(kIdxTileKeys, N);
+            if (!ptx::mbar_wait(bar_q, 0u, kWaitTimeoutNs)) { report_timeout(a.status, kStatusWaitIndexer, 1, -1);  ok = false; }
+            for (int i = 0; i < ntiles && ok; ++i) {
+                const int st = i % kIdxStages, d = i & 1;
+                if (!ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kWaitTimeoutNs) ||
+                    (i >= 2 && !ptx::mbar_wait(bar_acc_empty + 8 * d, uint32_t(i / 2 - 1) & 1u, kWaitTimeoutNs))) {
+                    report_timeout(a.status, kStatusWaitIndexer, 1, tile0 + i);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < kIdxDim / 32; ++k) {
+                    const uint64_t ad = ptx::make_smem_desc(key_smem + st * kIdxStageKeyBytes + k * 32, 16, 1024);
+                    const uint64_t bd = ptx::make_smem_desc(q_smem + k * 32, 16, 1024);
+                    mma_f8_ss(tmem + d * 128, ad, bd, idesc, k ? 1u : 0u);
+                }
+                ptx::mma_commit(bar_empty + 8 * st);
+                ptx::mma_commit(bar_acc_full + 8 * d);
+            }
+        }
+    } else {
+        // ───────────── epilogue: lane = key; ReLU, head weights, sum over heads, key scale ─────────────
+        const int quarter = warp & 3;                                  // tensor-memory lanes 32*quarter .. +31
+        const int r = quarter * 32 + lane;                             // key row inside the tile
+        const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+        int vis[2];
+        vis[0] = min(__ldg(a.n_vis + b * a.s_q), a.max_pages * kIdxPageKeys);
+        vis[1] = (a.s_q > 1) ? min(__ldg(a.n_vis + b * a.s_q + 1), a.max_pages * kIdxPageKeys) : 0;
+        for (int i = 0; i < ntiles && ok; ++i) {
+            const int st = i % kIdxStages, d = i & 1;
+            const bool w = ptx::mbar_wait(bar_acc_full + 8 * d, uint32_t(i / 2) & 1u, kWaitTimeoutNs) &&
+                           ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kWaitTimeoutNs);
+            if (!__all_sync(0xFFFFFFFFu, w)) {
+                report_timeout(a.status, kStatusWaitIndexer, 2, tile0 + i);
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const float kscale = scale_gen[st * (kIdxScaleBytes / 4) + r];
+            const bool page_loaded = (sm->page_ok[st] >> (r >> 6)) & 1u;
+            const int key = (tile0 + i) * kIdxTileKeys + r;
+            for (int t = 0; t < a.s_q; ++t) {
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < kIdxHeads / 32; ++c) {
+                    uint32_t v[32];
+                    ptx::tmem_ld32(tmem + lane_addr + d * 128 + t * kIdxHeads + c * 32, v);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        acc = fmaf(fmaxf(__uint_as_float(v[j]), 0.f), sm->weight[t * kIdxHeads + c * 32 + j], acc);
+                }
+                if (key < vis[t])
+                    a.scores[(int64_t(b) * a.s_q + t) * a.score_stride + key] = page_loaded ? acc * kscale : -CUDART_INF_F;
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(bar_acc_empty + 8 * d);
+                ptx::mbar_arrive(bar_empty + 8 * st);
+            }
+        }
+    }
+    // common exit: every role arrives; the MMA warp frees tensor memory after all accumulator reads
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, kIdxTmemCols);
+    }
+}
+
+// ───────────────────────── top-k ─────────────────────────
+
+constexpr int kTopkThreads = 1024;
+
+// order-preserving map float -> uint32 (larger float = larger key; -inf lowest of the finite order, NaN above +inf)
+__device__ __forceinline__ uint32_t float_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct TopkArgs {
+    int rows, k;
+    const float* scores;        // [rows, stride]
+    int64_t stride;
+    const int32_t* n_vis;       // [rows]
+    int32_t* out;               // [rows, k]
+    int n_cap;                  // entries the score rows can hold
+};
+
+__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_need, s_cnt_gt, s_cnt_eq;
+    const int row = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int n = max(0, min(__ldg(a.n_vis + row), a.n_cap));
+    const float* s = a.scores + int64_t(row) * a.stride;
+    int32_t* out = a.out + int64_t(row) * a.k;
+    if (n <= a.k) {
+        for (int i = tid; i < a.k; i += kTopkThreads) out[i] = (i < n) ? i : -1;
+        return;
+    }
+    // radix select: after the four rounds `prefix` is the key of the k-th largest score and
+    // `need` the number of entries equal to it that belong to the selection
+    if (tid == 0) { s_prefix = 0;  s_need = uint32_t(a.k); }
+    for (int round = 0; round < 4; ++round) {
+        const int shift = 24 - 8 * round;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const uint32_t mask = (round == 0) ? 0u : (0xFFFFFFFFu << (shift + 8));
+        for (int i = tid; i < n; i += kTopkThreads) {
+            const uint32_t key = float_key(s[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t need = s_need, bin = 255;
+            for (;; --bin) {                                  // from the largest digit down
+                const uint32_t c = hist[bin];
+                if (c >= need || bin == 0) break;
+                need -= c;
+            }
+            s_prefix = prefix | (bin << shift);
+            s_need = need;
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix, need_eq = s_need;
+    if (tid == 0) { s_cnt_gt = 0;  s_cnt_eq = 0; }
+    __syncthreads();
+    const uint32_t n_gt = uint32_t(a.k) - need_eq;            // entries strictly above the k-th
+    for (int i = tid; i < n; i += kTopkThreads) {
+        const uint32_t key = float_key(s[i]);
+        if (key > kth) {
+            const uint32_t p = atomicAdd(&s_cnt_gt, 1u);
+            if (p < n_gt) out[p] = i;
+        } else if (key == kth) {
+            const uint32_t p = atomicAdd(&s_cnt_eq, 1u);
+            if (p < need_eq) out[n_gt + p] = i;
+        }
+    }
+}
+
+}  // namespace dsv4

@@ -245,6 +245,43 @@ typedef struct Dsv4CsaCompressReduceParams {
 int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p, void* stream);
 
 /*
+ * CSA indexer for decode (the step before the sparse decode): for every query token the
+ * top-k visible compressed entries by
+ *     score[t, s] = sum_h w[t, h] * relu(q[t, h, :] . k[s, :])
+ * - the scoring and selection of the reference's lightning_indexer_topk after its
+ * projections (bench/bench/reference.py:193-204; causal rule :197-201 expressed as
+ * n_vis[t] = number of entries token t may see).  64 indexer heads of 128 dimensions.
+ * Queries and keys are FP8 e4m3: q_fp8 [B, s_q, 64, 128] with the per-(token, head)
+ * dequantisation scale folded by the caller into q_weight [B, s_q, 64] (= w * q_scale);
+ * keys in pages of 64: 64 x 128 e4m3 bytes followed by the 64 FP32 scales of those keys
+ * (8448 bytes per page), addressed through block_table [B, max_pages].  The FP8 x FP8
+ * products are exact and accumulate in FP32 on the tensor cores.
+ * Output: out_indices int32 [B, s_q, k], the k best entries in no particular order, -1
+ * padded when fewer than k are visible; entries of equal score at the cut are chosen
+ * arbitrarily.  `scores` is a caller-provided workspace, float [B*s_q, score_stride],
+ * score_stride >= max_pages*64, holding the scores of the visible entries afterwards.
+ * s_q is 1 or 2.  Pages the block table does not map into the pool score -inf.
+ */
+typedef struct Dsv4IndexerTopkParams {
+    int32_t B;
+    int32_t s_q;
+    int32_t max_pages;
+    int32_t k;
+    int64_t num_pages;
+    int64_t score_stride;
+    const void*    q_fp8;        /* uint8 [B, s_q, 64, 128], 128-byte aligned */
+    const float*   q_weight;     /* float [B, s_q, 64] */
+    const void*    key_pages;    /* uint8 [num_pages, 8448], 128-byte aligned */
+    const int32_t* block_table;  /* int32 [B, max_pages] */
+    const int32_t* n_vis;        /* int32 [B, s_q] */
+    float*         scores;       /* float [B*s_q, score_stride] workspace / optional result */
+    int32_t*       out_indices;  /* int32 [B, s_q, k] */
+    int32_t*       status;       /* optional int32[4], zeroed by the caller */
+} Dsv4IndexerTopkParams;
+
+int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* stream);
+
+/*
  * Pre- and post-pass around the attention: partial RoPE on the last n_rope dimensions
  * of each vector (split-halves pairing, frequencies 1 / theta^(2i / n_rope); the
  * reference's apply_rope, bench/bench/reference.py:35-65), then - when norm_weight

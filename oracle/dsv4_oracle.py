@@ -440,6 +440,105 @@ def rope_norm(x, positions, weight=None, eps=1e-6, n_rope=64, theta=10000.0, inv
     return out
 
 
+# ── CSA indexer (decode form) ───────────────────────────────────────────
+
+IDX_HEADS = 64
+IDX_DIM = 128
+IDX_PAGE_KEYS = 64
+IDX_PAGE_BYTES = IDX_PAGE_KEYS * IDX_DIM + IDX_PAGE_KEYS * 4      # 64 x 128 e4m3 bytes, then 64 FP32 scales
+
+
+def quantize_indexer_keys(K):
+    """K [..., 128] float32 -> (e4m3 bytes [..., 128], FP32 scale [...]): one absmax/448
+    scale per key (the recipe of bench/bench/decode.py:92-114 with one tile per key)."""
+    K = np.asarray(K, np.float32)
+    absmax = np.abs(K).max(axis=-1)
+    scale = (absmax / np.float32(E4M3_MAX)).astype(np.float32)
+    scale = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
+    return f32_to_e4m3((K / scale[..., None]).astype(np.float32)), scale
+
+
+def pack_indexer_pages(k8, kscale, rng=None):
+    """k8 [B, n, 128] e4m3 bytes, kscale [B, n] -> (pages uint8 [P, 8448], block_table
+    int32 [B, ceil(n/64)]); pages handed out in a shuffled order, unused bytes are noise."""
+    rng = rng or np.random.default_rng(0)
+    B, n, _ = k8.shape
+    per = max(1, -(-n // IDX_PAGE_KEYS))
+    P = B * per + 3
+    pages = rng.integers(0, 255, size=(P, IDX_PAGE_BYTES), dtype=np.uint8)
+    pages[:, IDX_PAGE_KEYS * IDX_DIM:] = 0          # noise scales must at least be finite
+    bt = rng.permutation(P)[:B * per].astype(np.int32).reshape(B, per)
+    for b in range(B):
+        for t in range(n):
+            pg, slot = bt[b, t // IDX_PAGE_KEYS], t % IDX_PAGE_KEYS
+            pages[pg, slot * IDX_DIM:(slot + 1) * IDX_DIM] = k8[b, t]
+            o = IDX_PAGE_KEYS * IDX_DIM + 4 * slot
+            pages[pg, o:o + 4] = np.frombuffer(np.float32(kscale[b, t]).tobytes(), np.uint8)
+    return pages, bt
+
+
+def indexer_scores(q_fp8, q_weight, pages, block_table, n_vis):
+    """score[b, t, s] = sum_h q_weight[b, t, h] * relu(q[b, t, h] . k[s]) * kscale[s] for the
+    s < n_vis[b, t] visible entries, -inf beyond (Eq 16 and the causal mask of the
+    reference's lightning_indexer_topk, bench/bench/reference.py:193-201; the per-key and
+    per-query scales are positive and commute with the ReLU).  Returns float32
+    [B, s_q, max n_vis]."""
+    B, s_q = n_vis.shape
+    q = e4m3_to_f32(q_fp8).astype(np.float32)                    # [B, s_q, 64, 128]
+    n_max = int(n_vis.max()) if n_vis.size else 0
+    out = np.full((B, s_q, n_max), -np.inf, np.float32)
+    for b in range(B):
+        n = int(n_vis[b].max())
+        if n == 0:
+            continue
+        pg = block_table[b, np.arange(n) // IDX_PAGE_KEYS]
+        slot = np.arange(n) % IDX_PAGE_KEYS
+        raw = pages[pg]                                           # [n, 8448]
+        k8 = e4m3_to_f32(raw[np.arange(n)[:, None], slot[:, None] * IDX_DIM + np.arange(IDX_DIM)[None, :]])
+        ksc = np.ascontiguousarray(raw[:, IDX_PAGE_KEYS * IDX_DIM:]).view(np.float32)[np.arange(n), slot]
+        for t in range(s_q):
+            dots = np.einsum("hc,sc->hs", q[b, t], k8.astype(np.float32)).astype(np.float32)
+            sc = (np.maximum(dots, 0) * np.asarray(q_weight[b, t], np.float32)[:, None]).sum(axis=0).astype(np.float32) * ksc
+            v = int(n_vis[b, t])
+            out[b, t, :v] = sc[:v]
+    return out
+
+
+def indexer_topk(scores, n_vis, k):
+    """Indices of the k largest visible scores per (request, token), as a list of sorted
+    index arrays (fewer than k when fewer are visible) - torch.topk of the masked scores
+    in the reference (reference.py:203-204), as a set."""
+    B, s_q = n_vis.shape
+    res = [[None] * s_q for _ in range(B)]
+    for b in range(B):
+        for t in range(s_q):
+            v = int(n_vis[b, t])
+            order = np.argsort(-scores[b, t, :v], kind="stable")[:min(k, v)]
+            res[b][t] = np.sort(order)
+    return res
+
+
+@dataclass
+class IndexerCase:
+    q_fp8: np.ndarray        # [B, s_q, 64, 128] e4m3 bytes
+    q_scale: np.ndarray      # [B, s_q, 64] positive
+    w: np.ndarray            # [B, s_q, 64] head weights
+    K: np.ndarray            # [B, n, 128] float32 keys before quantisation
+    n_vis: np.ndarray        # [B, s_q]
+
+
+def make_indexer_case(seed, B, s_q, n, n_vis=None) -> IndexerCase:
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((B, s_q, IDX_HEADS, IDX_DIM), dtype=np.float32) * np.float32(2)
+    q_fp8 = f32_to_e4m3(q)
+    q_scale = rng.uniform(0.5, 2.0, size=(B, s_q, IDX_HEADS)).astype(np.float32)
+    w = rng.standard_normal((B, s_q, IDX_HEADS)).astype(np.float32)
+    K = rng.standard_normal((B, n, IDX_DIM), dtype=np.float32) * rng.uniform(0.2, 3.0, size=(B, n, 1)).astype(np.float32)
+    if n_vis is None:
+        n_vis = np.full((B, s_q), n, np.int32)
+    return IndexerCase(q_fp8, q_scale, w, K, np.asarray(n_vis, np.int32).reshape(B, s_q))
+
+
 REF_TOKEN_BYTES = 576        # 448 e4m3 latent + 64 BF16 RoPE values
 REF_SCALE_BYTES = 8          # 7 UE8M0 bytes + 1 pad
 

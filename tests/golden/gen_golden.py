@@ -176,6 +176,34 @@ def gen_rope_norm(ref, name, **kw):
     print(name, tuple(q.shape))
 
 
+def gen_indexer(ref, name, **kw):
+    """lightning_indexer_topk (reference.py:169-205) with identity projections, so that its
+    q_I / w_I are the given ones: n = nb * m tokens, only the two query tokens of the case
+    carry a query; their visible blocks are floor(t / m).  Stores the selected block ids."""
+    import torch
+    m, top_k = kw["m"], kw["top_k"]
+    kwc = {k: v for k, v in kw.items() if k not in ("m", "top_k", "tokens")}
+    c = orc.make_indexer_case(**kwc)
+    B, s_q = c.n_vis.shape
+    nb = c.K.shape[1]
+    n = nb * m
+    k8, ksc = orc.quantize_indexer_keys(c.K)
+    K_deq = (orc.e4m3_to_f32(k8) * ksc[..., None]).astype(np.float32)
+    d = orc.IDX_HEADS * orc.IDX_DIM
+    c_Q = np.zeros((B, n, d), np.float32)
+    Hw = np.zeros((B, n, orc.IDX_HEADS), np.float32)
+    toks = kw["tokens"]
+    for j, t in enumerate(toks):
+        c_Q[:, t] = (orc.e4m3_to_f32(c.q_fp8[:, j]) * c.q_scale[:, j, :, None]).reshape(B, d)
+        Hw[:, t] = c.w[:, j]
+    w = ref.IndexerWeights(W_IUQ=torch.eye(d), W_w=torch.eye(orc.IDX_HEADS), n_heads=orc.IDX_HEADS, head_dim=orc.IDX_DIM)
+    sel = ref.lightning_indexer_topk(torch.from_numpy(Hw), torch.from_numpy(c_Q), torch.from_numpy(K_deq), w, m, top_k)
+    sel = sel[:, toks].numpy().astype(np.int32)                       # [B, s_q, top_k], best first
+    np.savez_compressed(HERE / f"{name}.npz", sel=sel, n_vis=np.array([[t // m for t in toks]] * B, np.int32),
+                        inputs_sha=sha(c.q_fp8, c.q_scale, c.w, c.K), kwargs=repr(kw))
+    print(name, sel.shape)
+
+
 # The cases; tests/test_oracle.py rebuilds the inputs from the same kwargs.
 CSA_CASES = {
     "csa_cfg0": dict(seed=0, B=2, s_q=1, H=16, n_entries=1024, topk=256),
@@ -196,6 +224,9 @@ HCA_COMPRESS_CASES = {
 ROPE_NORM_CASES = {
     "rope_norm_q576": dict(seed=12, rows=6, vecs=16, c=576, max_pos=4096),
     "rope_norm_o512": dict(seed=13, rows=5, vecs=8, c=512, max_pos=100000),
+}
+INDEXER_CASES = {
+    "indexer_topk": dict(seed=14, B=1, s_q=2, n=300, m=4, top_k=64, tokens=[1195, 1199]),
 }
 REF_CASES = {
     "ref_layout": dict(seed=4, B=1, H=128, M_cur=192, swa_len=64),
@@ -223,6 +254,8 @@ def main() -> int:
         gen_hca_compress(ref, name, **kw)
     for name, kw in ROPE_NORM_CASES.items():
         gen_rope_norm(ref, name, **kw)
+    for name, kw in INDEXER_CASES.items():
+        gen_indexer(ref, name, **kw)
     return 0
 
 

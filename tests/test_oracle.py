@@ -242,3 +242,28 @@ def test_rope_norm_oracle_vs_reference(name):
     # rotating forth and back is the identity
     back = orc.rope_norm(orc.rope_norm(x, pos), pos, inverse=True)
     np.testing.assert_allclose(back, x, rtol=1e-4, atol=1e-4)
+
+
+def indexer_inputs(c, rng):
+    """Device-facing inputs of an IndexerCase: quantised keys in pages, folded weights."""
+    k8, ksc = orc.quantize_indexer_keys(c.K)
+    pages, bt = orc.pack_indexer_pages(k8, ksc, rng)
+    return pages, bt, (c.w * c.q_scale).astype(np.float32)
+
+
+def test_indexer_oracle_vs_reference():
+    z, kw = load("indexer_topk")
+    kwc = {k: v for k, v in kw.items() if k not in ("m", "top_k", "tokens")}
+    c = orc.make_indexer_case(**kwc)
+    assert sha(c.q_fp8, c.q_scale, c.w, c.K) == str(z["inputs_sha"])
+    pages, bt, qw = indexer_inputs(c, np.random.default_rng(1))
+    n_vis = z["n_vis"]
+    scores = orc.indexer_scores(c.q_fp8, qw, pages, bt, n_vis)
+    sel = orc.indexer_topk(scores, n_vis, kw["top_k"])
+    for b in range(n_vis.shape[0]):
+        for t in range(n_vis.shape[1]):
+            assert np.array_equal(sel[b][t], np.sort(z["sel"][b, t])), (b, t)
+            assert (z["sel"][b, t] < n_vis[b, t]).all()
+            # the reference lists its selection best first
+            ref_scores = scores[b, t, z["sel"][b, t]]
+            assert (np.diff(ref_scores) <= 1e-4 * np.abs(ref_scores[:-1]) + 1e-6).all()
