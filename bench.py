@@ -501,6 +501,33 @@ def run_ours(args):
                                                   "hbm_frac": qbytes / (qms * 1e-3) / 1e9 / peak, "bytes": qbytes}
         del rows_q, pool_q, pool_h
         torch.cuda.empty_cache()
+    if "indexer" in args.extras and world == 1:
+        # the step before the sparse decode: FP8 scoring of every visible entry + top-k
+        import dsv4_attn_b200 as lib
+        Bi, ni, ki = 64, 25000, 2048
+        pages_per = (ni + 63) // 64
+        qf = torch.randint(0, 120, (Bi, 1, 64, 128), dtype=torch.uint8, device=dev)       # positive e4m3 bytes below NaN
+        qf = qf | (torch.randint(0, 2, qf.shape, dtype=torch.uint8, device=dev) << 7)      # random signs
+        qw = torch.randn(Bi, 1, 64, device=dev)
+        kp = torch.randint(0, 120, (Bi * pages_per, 8448), dtype=torch.uint8, device=dev)
+        kp[:, :8192] |= (torch.randint(0, 2, (Bi * pages_per, 8192), dtype=torch.uint8, device=dev) << 7)
+        kp[:, 8192:] = torch.rand(Bi * pages_per, 64, device=dev).add_(0.5).view(torch.uint8).view(Bi * pages_per, 256)
+        bti = torch.randperm(Bi * pages_per, device=dev).to(torch.int32).view(Bi, pages_per)
+        nv = torch.full((Bi, 1), ni, dtype=torch.int32, device=dev)
+        sc_ws = torch.empty(Bi, pages_per * 64, dtype=torch.float32, device=dev)
+        oi = torch.empty(Bi, 1, ki, dtype=torch.int32, device=dev)
+        st_i = lib.new_status(dev)
+        it = time_steps(lambda: lib.indexer_topk(qf, qw, kp, bti, nv, ki, scores=sc_ws, out=oi, status=st_i),
+                        max(3, min(args.steps, 10)), 3, flush, barrier)
+        if st_i.cpu().tolist() != [0, 0, 0, 0]:
+            raise RuntimeError("indexer: a kernel wait timed out")
+        ibytes = Bi * ni * 132
+        ims = statistics.mean(it)
+        others["indexer_topk_b64_n25000_k2048"] = {"us": ims * 1e3, "key_gb_per_s": ibytes / (ims * 1e-3) / 1e9,
+                                                   "hbm_frac": ibytes / (ims * 1e-3) / 1e9 / peak, "key_bytes": ibytes,
+                                                   "launches": 2}
+        del qf, kp, sc_ws
+        torch.cuda.empty_cache()
     if "decode" in args.extras and world == 1:
         for name in WORKLOADS:
             if name == args.workload:
@@ -591,8 +618,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads")
-    ap.add_argument("--extras", default="mixed,cache_write,decode",
-                    help="which groups of other workloads to run: mixed, cache_write, decode (comma-separated)")
+    ap.add_argument("--extras", default="mixed,cache_write,indexer,decode",
+                    help="which groups of other workloads to run: mixed, cache_write, indexer, decode (comma-separated)")
     args = ap.parse_args()
     args.extras = set() if args.no_extras else {x for x in args.extras.split(",") if x}
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -609,9 +609,20 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles_cap = (p->max_pages + 1) / 2;
-    int ctas = (4 * sms + p->B - 1) / p->B;
-    if (ctas < 1) ctas = 1;
-    if (ctas > tiles_cap) ctas = tiles_cap;
+    // Blocks per request: two blocks are resident per SM; the time is (waves of resident blocks) x
+    // (tiles per block + a fixed set-up of about two tiles).  Pick the count that minimises it.
+    int ctas = 1;
+    {
+        const int64_t slots = 2 * int64_t(sms);
+        double best = 1e300;
+        const int c_max = tiles_cap < 64 ? tiles_cap : 64;
+        for (int c = 1; c <= c_max; ++c) {
+            const int tpc = (tiles_cap + c - 1) / c;
+            const int64_t blocks = int64_t(p->B) * ((tiles_cap + tpc - 1) / tpc);
+            const double cost = double((blocks + slots - 1) / slots) * (tpc + 2.0);
+            if (cost < best - 1e-9) { best = cost;  ctas = c; }
+        }
+    }
     a.tiles_per_cta = (tiles_cap + ctas - 1) / ctas;
     const int grid_x = (tiles_cap + a.tiles_per_cta - 1) / a.tiles_per_cta;
     a.B = p->B;  a.s_q = p->s_q;  a.max_pages = p->max_pages;  a.num_pages = p->num_pages;
@@ -627,6 +638,12 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     TopkArgs t{};
     t.rows = p->B * p->s_q;  t.k = p->k;  t.scores = p->scores;  t.stride = p->score_stride;  t.n_vis = p->n_vis;
     t.out = p->out_indices;  t.n_cap = p->max_pages * kIdxPageKeys;
-    topk_select_kernel<<<t.rows, kTopkThreads, 0, s>>>(t);
+    // a copy of the score row in shared memory when it fits next to the kernel's static 38 KB
+    const int row_bytes = t.n_cap * int(sizeof(float));
+    t.row_in_smem = row_bytes <= 180 * 1024 ? 1 : 0;
+    static bool done_topk[kMaxDevices] = {};
+    e = ensure_smem(topk_select_kernel, 180 * 1024, done_topk);
+    if (e != cudaSuccess) return int(e);
+    topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
     return int(cudaGetLastError());
 }

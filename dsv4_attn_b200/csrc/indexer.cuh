@@ -242,8 +242,10 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
 // ───────────────────────── top-k ─────────────────────────
 
 constexpr int kTopkThreads = 1024;
+constexpr int kTopkBins = 1024;          // one bin per thread in the suffix scan
+constexpr int kTopkCand = 4096;          // candidates of the threshold bin kept in shared memory
 
-// order-preserving map float -> uint32 (larger float = larger key; -inf lowest of the finite order, NaN above +inf)
+// order-preserving map float -> uint32 (larger float = larger key)
 __device__ __forceinline__ uint32_t float_key(float f) {
     const uint32_t u = __float_as_uint(f);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -256,59 +258,200 @@ struct TopkArgs {
     const int32_t* n_vis;       // [rows]
     int32_t* out;               // [rows, k]
     int n_cap;                  // entries the score rows can hold
+    int row_in_smem;            // the launch provides n_cap floats of dynamic shared memory for a copy of the row
 };
 
-__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
-    __shared__ uint32_t hist[256];
-    __shared__ uint32_t s_prefix, s_need, s_cnt_gt, s_cnt_eq;
-    const int row = blockIdx.x;
+struct TopkShared {
+    uint32_t hist[kTopkBins];
+    uint32_t cand_key[kTopkCand];
+    int32_t cand_idx[kTopkCand];
+    float red_lo[32], red_hi[32];
+    uint32_t warp_sum[32];
+    uint32_t radix[256];
+    uint32_t t_bin, n_gt, need, n_cand, prefix, rneed, cnt_gt, cnt_eq;
+};
+
+// Exact selection of the `need` largest keys among the elements `src` enumerates
+// (four 8-bit radix rounds, then a compaction), written to out[0 .. need).  Used on
+// the few hundred candidates of the threshold bin, where contention is harmless.
+// src(j, key, idx) returns false for positions that hold no element.
+template <typename Src>
+__device__ __forceinline__ void radix_select_emit(TopkShared& sh, int count, uint32_t need, int32_t* out, Src src) {
     const int tid = threadIdx.x;
+    if (tid == 0) { sh.prefix = 0;  sh.rneed = need; }
+    for (int round = 0; round < 4; ++round) {
+        const int shift = 24 - 8 * round;
+        if (tid < 256) sh.radix[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = sh.prefix;
+        const uint32_t mask = (round == 0) ? 0u : (0xFFFFFFFFu << (shift + 8));
+        for (int j = tid; j < count; j += kTopkThreads) {
+            uint32_t key;  int32_t idx;
+            if (src(j, key, idx) && (key & mask) == prefix) atomicAdd(&sh.radix[(key >> shift) & 0xFFu], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // the digit that holds the nd-th largest remaining key: lane l owns digits 8l .. 8l+7,
+            // a suffix scan over the lanes finds the lane, a short loop the digit
+            const uint32_t nd = sh.rneed;
+            uint32_t c[8], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { c[j] = sh.radix[8 * tid + j];  sum += c[j]; }
+            uint32_t incl = sum;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t o = __shfl_down_sync(0xFFFFFFFFu, incl, d);
+                if (tid + d < 32) incl += o;
+            }
+            const uint32_t higher = incl - sum;
+            if (higher < nd && incl >= nd) {
+                uint32_t rem = nd - higher, bin = 8u * tid;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    if (c[j] >= rem) { bin = 8u * tid + uint32_t(j);  break; }
+                    rem -= c[j];
+                }
+                sh.prefix = prefix | (bin << shift);
+                sh.rneed = rem;
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = sh.prefix, need_eq = sh.rneed, above = need - need_eq;
+    if (tid == 0) { sh.cnt_gt = 0;  sh.cnt_eq = 0; }
+    __syncthreads();
+    for (int j = tid; j < count; j += kTopkThreads) {
+        uint32_t key;  int32_t idx;
+        if (!src(j, key, idx)) continue;
+        if (key > kth) {
+            const uint32_t p = atomicAdd(&sh.cnt_gt, 1u);
+            if (p < above) out[p] = idx;
+        } else if (key == kth) {
+            const uint32_t p = atomicAdd(&sh.cnt_eq, 1u);
+            if (p < need_eq) out[above + p] = idx;
+        }
+    }
+}
+
+// One block per (request, token) row.  The scores of a row share a handful of floating-point
+// exponents, so a radix histogram over the raw bits would have every lane of a warp hit the same
+// counter.  Instead: (A) minimum and maximum of the row; (B) a histogram over 1024 equal-width
+// value bins - spread out, so the shared-memory atomics rarely collide; a block-wide suffix scan
+// finds the bin that holds the k-th largest score; (C) everything in higher bins is part of the
+// selection and is written out at once, the entries of the threshold bin (a few hundred) are
+// collected in shared memory and the remaining places are filled from them by an exact radix
+// select.  Binning is monotone in the score, so the result is the exact top-k (as a set).
+__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
+    __shared__ TopkShared sh;
+    extern __shared__ float topk_row[];
+    const int row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = max(0, min(__ldg(a.n_vis + row), a.n_cap));
-    const float* s = a.scores + int64_t(row) * a.stride;
+    const float* g = a.scores + int64_t(row) * a.stride;
+    // the three passes read the row from shared memory when it fits (copied during pass A)
+    const float* s = a.row_in_smem ? topk_row : g;
     int32_t* out = a.out + int64_t(row) * a.k;
     if (n <= a.k) {
         for (int i = tid; i < a.k; i += kTopkThreads) out[i] = (i < n) ? i : -1;
         return;
     }
-    // radix select: after the four rounds `prefix` is the key of the k-th largest score and
-    // `need` the number of entries equal to it that belong to the selection
-    if (tid == 0) { s_prefix = 0;  s_need = uint32_t(a.k); }
-    for (int round = 0; round < 4; ++round) {
-        const int shift = 24 - 8 * round;
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
-        const uint32_t prefix = s_prefix;
-        const uint32_t mask = (round == 0) ? 0u : (0xFFFFFFFFu << (shift + 8));
-        for (int i = tid; i < n; i += kTopkThreads) {
-            const uint32_t key = float_key(s[i]);
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+    // (A) range of the finite scores
+    float lo = CUDART_INF_F, hi = -CUDART_INF_F;
+    for (int i0 = tid; i0 < n; i0 += 8 * kTopkThreads) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {                        // eight loads in flight per thread
+            const int i = i0 + u * kTopkThreads;
+            v[u] = (i < n) ? __ldg(g + i) : CUDART_NAN_F;
         }
-        __syncthreads();
-        if (tid == 0) {
-            uint32_t need = s_need, bin = 255;
-            for (;; --bin) {                                  // from the largest digit down
-                const uint32_t c = hist[bin];
-                if (c >= need || bin == 0) break;
-                need -= c;
-            }
-            s_prefix = prefix | (bin << shift);
-            s_need = need;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * kTopkThreads;
+            if (a.row_in_smem && i < n) topk_row[i] = v[u];
+            if (v[u] > -CUDART_INF_F && v[u] < CUDART_INF_F) { lo = fminf(lo, v[u]);  hi = fmaxf(hi, v[u]); }
         }
-        __syncthreads();
     }
-    const uint32_t kth = s_prefix, need_eq = s_need;
-    if (tid == 0) { s_cnt_gt = 0;  s_cnt_eq = 0; }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+    }
+    if (lane == 0) { sh.red_lo[warp] = lo;  sh.red_hi[warp] = hi; }
+    sh.hist[tid] = 0;
+    if (tid == 0) { sh.n_cand = 0;  sh.cnt_gt = 0; }
     __syncthreads();
-    const uint32_t n_gt = uint32_t(a.k) - need_eq;            // entries strictly above the k-th
-    for (int i = tid; i < n; i += kTopkThreads) {
-        const uint32_t key = float_key(s[i]);
-        if (key > kth) {
-            const uint32_t p = atomicAdd(&s_cnt_gt, 1u);
-            if (p < n_gt) out[p] = i;
-        } else if (key == kth) {
-            const uint32_t p = atomicAdd(&s_cnt_eq, 1u);
-            if (p < need_eq) out[n_gt + p] = i;
+    lo = sh.red_lo[lane];  hi = sh.red_hi[lane];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+    }
+    const float inv = (hi > lo) ? float(kTopkBins) / (hi - lo) : 0.f;
+    // -inf and NaN go to bin 0, +inf to the last bin; monotone in v otherwise
+    auto bin_of = [&](float v) -> int {
+        if (!(v > -CUDART_INF_F)) return 0;
+        const float x = (v - lo) * inv;
+        return x >= float(kTopkBins - 1) ? kTopkBins - 1 : (x > 0.f ? int(x) : 0);
+    };
+    // (B) histogram, then for every bin the number of entries in higher bins
+    for (int i = tid; i < n; i += kTopkThreads) atomicAdd(&sh.hist[bin_of(s[i])], 1u);
+    __syncthreads();
+    {
+        const uint32_t mine = sh.hist[tid];
+        uint32_t incl = mine;                               // suffix sum inside the warp (higher lanes = higher bins)
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t o = __shfl_down_sync(0xFFFFFFFFu, incl, d);
+            if (lane + d < 32) incl += o;
         }
+        if (lane == 0) sh.warp_sum[warp] = incl;
+        __syncthreads();
+        uint32_t higher = 0;                                // entries in the warps above this one
+        for (int w = warp + 1; w < 32; ++w) higher += sh.warp_sum[w];
+        incl += higher;
+        const uint32_t excl = incl - mine;
+        if (excl < uint32_t(a.k) && incl >= uint32_t(a.k)) { sh.t_bin = uint32_t(tid);  sh.n_gt = excl;  sh.need = uint32_t(a.k) - excl; }
+    }
+    __syncthreads();
+    const int t_bin = int(sh.t_bin);
+    const uint32_t n_gt = sh.n_gt, need = sh.need;
+    // (C) higher bins straight to the output, the threshold bin to the candidate list
+    for (int i0 = 0; i0 < n; i0 += kTopkThreads) {
+        const int i = i0 + tid;
+        float v = 0.f;
+        int bn = -1;
+        if (i < n) { v = s[i];  bn = bin_of(v); }
+        const bool gt = bn > t_bin, eq = bn == t_bin;
+        const uint32_t m_gt = __ballot_sync(0xFFFFFFFFu, gt), m_eq = __ballot_sync(0xFFFFFFFFu, eq);
+        const uint32_t below = (1u << lane) - 1u;
+        uint32_t base_gt = 0, base_eq = 0;
+        if (lane == 0) {
+            if (m_gt) base_gt = atomicAdd(&sh.cnt_gt, uint32_t(__popc(m_gt)));
+            if (m_eq) base_eq = atomicAdd(&sh.n_cand, uint32_t(__popc(m_eq)));
+        }
+        base_gt = __shfl_sync(0xFFFFFFFFu, base_gt, 0);
+        base_eq = __shfl_sync(0xFFFFFFFFu, base_eq, 0);
+        if (gt) {
+            out[base_gt + uint32_t(__popc(m_gt & below))] = i;       // exactly n_gt such entries exist
+        } else if (eq) {
+            const uint32_t p = base_eq + uint32_t(__popc(m_eq & below));
+            if (p < uint32_t(kTopkCand)) { sh.cand_key[p] = float_key(v);  sh.cand_idx[p] = i; }
+        }
+    }
+    __syncthreads();
+    const uint32_t n_cand = sh.n_cand;
+    if (n_cand <= uint32_t(kTopkCand)) {
+        radix_select_emit(sh, int(n_cand), need, out + n_gt, [&](int j, uint32_t& key, int32_t& idx) {
+            key = sh.cand_key[j];  idx = sh.cand_idx[j];
+            return true;
+        });
+    } else {
+        // a threshold bin too crowded for the list (many equal scores): select among its entries in place
+        radix_select_emit(sh, n, need, out + n_gt, [&](int j, uint32_t& key, int32_t& idx) {
+            const float v = s[j];
+            key = float_key(v);  idx = j;
+            return bin_of(v) == t_bin;
+        });
     }
 }
 
