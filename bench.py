@@ -50,6 +50,8 @@ WORKLOADS = {
     "hca_b64_h128_ctx100k": ("hca", dict(B=64, s_q=1, H=128, kv_len=782, win_len=128)),
     "csa_b64_h128_topk512_ctx3072": ("csa", dict(B=64, s_q=1, H=128, n_entries=768, topk=512, num_splits=1)),
     "csa_b128_nextn2_topk2048_ctx100k_split8": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048, num_splits=8)),
+    # the same shape with the split count left to the library's planner
+    "csa_b128_nextn2_topk2048_ctx100k_planned": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048)),
     "csa_b64_h128_topk2048_ctx100k": ("csa", dict(B=64, s_q=1, H=128, n_entries=25000, topk=2048)),
 }
 # The mixed data-parallel workload: a global batch of 1024 requests with log-normal raw
