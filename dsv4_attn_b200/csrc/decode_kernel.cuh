@@ -70,6 +70,15 @@ enum SourceKind : int {
 // both kinds with the reference's quantisation (448 latent elements, one UE8M0 byte per 64)
 __host__ __device__ constexpr bool is_ref_layout(int src) { return src == kSrcRef || src == kSrcRefPaged; }
 
+// Operand format of the MMAs.  The packed 656-byte layout goes through FP16: FP8 -> FP16 is one
+// exact conversion instruction per two elements and one packed multiply by the scale (the BF16
+// route costs five integer/FP instructions per two elements, and that arithmetic is a third of
+// the loaders' time), and FP16 keeps three more mantissa bits of fp8 x scale than BF16.  Q
+// and P are converted to FP16 as well (exact for Q inside FP16's normal range; P <= 2^8).
+// Limits: |fp8 x scale| and |q| below 65504 (the BF16 route's own limit on scales is 128).
+// The reference layouts keep BF16: their power-of-two scales span BF16's exponent range.
+__host__ __device__ constexpr bool use_f16(int src) { return !is_ref_layout(src); }
+
 enum StatusCode : int {
     kStatusOk = 0,
     kStatusWaitKvFull = 1,
@@ -189,6 +198,15 @@ __device__ __forceinline__ void dequant4(uint32_t w, __nv_bfloat162 scale2, uint
     __nv_bfloat162 b = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&r23), scale2);
     lo = *reinterpret_cast<uint32_t*>(&a);
     hi = *reinterpret_cast<uint32_t*>(&b);
+}
+
+// Four FP8 e4m3 (one 32-bit word) times the block scale -> 4 FP16 (two packed words).
+__device__ __forceinline__ void dequant4_f16(uint32_t w, __half2 scale2, uint32_t& lo, uint32_t& hi) {
+    const uint32_t a = ptx::e4m3x2_to_f16x2(w & 0xFFFFu), b = ptx::e4m3x2_to_f16x2(w >> 16);
+    const __half2 x = __hmul2(*reinterpret_cast<const __half2*>(&a), scale2);
+    const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&b), scale2);
+    lo = *reinterpret_cast<const uint32_t*>(&x);
+    hi = *reinterpret_cast<const uint32_t*>(&y);
 }
 
 // Registers one loader thread holds for one tile.  A loader warp owns 8
@@ -400,12 +418,20 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
             } else {
                 s120 = __uint_as_float(r.sc[g][j]) * 1.329227995784916e36f;   // one FP32 scale per 128 elements; x 2^120
             }
-            const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
             const uint4 x = r.lat[g][j];
-            dequant4(x.x, scale2, w0.x, w0.y);
-            dequant4(x.y, scale2, w0.z, w0.w);
-            dequant4(x.z, scale2, w1.x, w1.y);
-            dequant4(x.w, scale2, w1.z, w1.w);
+            if constexpr (use_f16(SRC)) {
+                const __half2 scale2 = __float2half2_rn(__uint_as_float(r.sc[g][j]));
+                dequant4_f16(x.x, scale2, w0.x, w0.y);
+                dequant4_f16(x.y, scale2, w0.z, w0.w);
+                dequant4_f16(x.z, scale2, w1.x, w1.y);
+                dequant4_f16(x.w, scale2, w1.z, w1.w);
+            } else {
+                const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
+                dequant4(x.x, scale2, w0.x, w0.y);
+                dequant4(x.y, scale2, w0.z, w0.w);
+                dequant4(x.z, scale2, w1.x, w1.y);
+                dequant4(x.w, scale2, w1.z, w1.w);
+            }
         }
         // A 16-byte store is served per quarter-warp: 8 lanes = one row, both chunks.  The two
         // chunks are 8 KB apart (same banks), so the lanes of the second chunk write their
@@ -427,9 +453,27 @@ __device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int la
         const int t = t0 + i;
         const bool valid = (r.vmask >> i) & 1u;
         const uint32_t base = kv_st + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
-        const uint4 w = valid ? r.rope[g] : make_uint4(0, 0, 0, 0);
+        uint4 w = valid ? r.rope[g] : make_uint4(0, 0, 0, 0);
+        if constexpr (use_f16(SRC)) {
+            w.x = ptx::bf16x2_to_f16x2(w.x);  w.y = ptx::bf16x2_to_f16x2(w.y);
+            w.z = ptx::bf16x2_to_f16x2(w.z);  w.w = ptx::bf16x2_to_f16x2(w.w);
+        }
         ptx::sts_v4(base + ((piece ^ uint32_t(t & 7)) << 4), w);
     }
+}
+
+// BF16 -> FP16 in place over the Q chunks that stay in shared memory, one share per thread of
+// the softmax and loader warps (threads 0 .. kStageThreads-1), then the proxy fence that makes
+// the result visible to the MMAs' reads.  Element-wise, so the swizzled layout is untouched.
+template <int BYTES>
+__device__ __forceinline__ void convert_q_smem(uint32_t q_base, int tid) {
+    for (int i = tid; i < BYTES / 16; i += kStageThreads) {
+        uint4 x = ptx::lds_v4(q_base + uint32_t(i) * 16u);
+        x.x = ptx::bf16x2_to_f16x2(x.x);  x.y = ptx::bf16x2_to_f16x2(x.y);
+        x.z = ptx::bf16x2_to_f16x2(x.z);  x.w = ptx::bf16x2_to_f16x2(x.w);
+        ptx::sts_v4(q_base + uint32_t(i) * 16u, x);
+    }
+    ptx::fence_proxy_async_smem();
 }
 
 template <int NCHUNK, int SRC>
@@ -492,7 +536,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
         ptx::mbar_init(bar_o_full, 1);
         ptx::mbar_init(bar_q_full, 1);
-        ptx::mbar_init(bar_q_ready, kNumSoftmaxWarps);
+        ptx::mbar_init(bar_q_ready, use_f16(SRC) ? kNumSoftmaxWarps + kNumLoaderWarps : kNumSoftmaxWarps);
         ptx::fence_mbar_init();
         if (ntiles > 0) {
             // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
@@ -562,6 +606,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         if (lw == 0 && lane == 0) trace_mark(a, 3, 8);
         if (ntiles > 0) {
             bool lok = true;
+            if constexpr (use_f16(SRC)) {
+                // the loaders' share of the Q conversion, while their first loads are in flight
+                const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
+                if (!__all_sync(0xFFFFFFFFu, w)) {
+                    report_timeout(a.status, kStatusWaitQ, 2, tile0);
+                    lok = false;
+                } else {
+                    convert_q_smem<L::kQBytes>(q_base, tid);
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_q_ready);     // also after a time-out, so that nobody waits for this warp
+            }
             auto tile_step = [&](LoaderRegs<SRC>& regs, int it) {
                 const int st = it & 1;
                 if (it == 1) {
@@ -583,12 +639,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                 }
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it);
-                if (it == 0) {
-                    // loads of tile 1 queue up behind those of tile 0, then the records of tiles 2 and 3
-                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
-                    loader_prefetch_l2<SRC>(key2, vm2, lane);
-                    loader_prefetch_l2<SRC>(key3, vm3, lane);
-                } else if (!(a.dbg & 2)) {
+                if (it != 0 && !(a.dbg & 2)) {
                     // the key resolved during the previous step has arrived by now: start pulling
                     // its records into L2 (using it earlier would stall on the block-table load)
                     loader_prefetch_l2<SRC>(key4, vm4, lane);
@@ -605,6 +656,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 0);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 1);
                 group_done(0);
+                if (it == 0) {
+                    // The first QK MMAs can start now.  The loads of tile 1 and the records of tiles 2
+                    // and 3 are requested only here: queued earlier they would hold up the stores above.
+                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
+                    loader_prefetch_l2<SRC>(key2, vm2, lane);
+                    loader_prefetch_l2<SRC>(key3, vm3, lane);
+                }
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 2);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 3);
                 loader_store_rope<NCHUNK, SRC>(kv_st, lw * 8, lane, regs);
@@ -634,8 +692,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         const uint32_t tmem = misc->tmem_base;
         if (ntiles > 0 && warp == kMmaWarp) {
             if (lane == 0) {
-                constexpr uint32_t idesc_qk = ptx::make_idesc_bf16(128, kTileN, false, false);
-                constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(128, kDvHalf, false, true);
+                constexpr uint32_t idesc_qk = use_f16(SRC) ? ptx::make_idesc_f16(128, kTileN, false, false)
+                                                            : ptx::make_idesc_bf16(128, kTileN, false, false);
+                constexpr uint32_t idesc_pv = use_f16(SRC) ? ptx::make_idesc_f16(128, kDvHalf, false, true)
+                                                            : ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 bool ok = true;
                 // Q: shared-memory chunks landed (TMA) and tensor-memory chunks copied
                 if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs)) {
@@ -759,10 +819,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     uint32_t w32[32];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const uint4 x = ptx::lds_v4(srow + uint32_t(g) * kQChunkBytes + ((uint32_t(j) ^ sw) << 4));
+                        uint4 x = ptx::lds_v4(srow + uint32_t(g) * kQChunkBytes + ((uint32_t(j) ^ sw) << 4));
+                        if constexpr (use_f16(SRC)) {
+                            x.x = ptx::bf16x2_to_f16x2(x.x);  x.y = ptx::bf16x2_to_f16x2(x.y);
+                            x.z = ptx::bf16x2_to_f16x2(x.z);  x.w = ptx::bf16x2_to_f16x2(x.w);
+                        }
                         w32[4 * j + 0] = x.x;  w32[4 * j + 1] = x.y;  w32[4 * j + 2] = x.z;  w32[4 * j + 3] = x.w;
                     }
                     ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w32);
+                }
+                if constexpr (use_f16(SRC)) {
+                    // the Q chunks that stay in shared memory: BF16 -> FP16 in place (element-wise, so
+                    // the swizzled layout is untouched), then made visible to the MMAs' reads
+                    // (shared with the loader warps: see convert_q_smem)
+                    convert_q_smem<L::kQBytes>(q_base, tid);
                 }
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before_sync();
@@ -829,14 +899,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     const float p0 = ptx::ex2(fmaf(__uint_as_float(s0[2 * i]), a.scale_log2, neg_m));
                     const float p1 = ptx::ex2(fmaf(__uint_as_float(s0[2 * i + 1]), a.scale_log2, neg_m));
                     ps4[i & 3] += p0 + p1;
-                    pk[i] = ptx::pack_bf16x2(p0, p1);
+                    pk[i] = use_f16(SRC) ? ptx::pack_f16x2(p0, p1) : ptx::pack_bf16x2(p0, p1);
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = ptx::ex2(fmaf(__uint_as_float(s1[2 * i]), a.scale_log2, neg_m));
                     const float p1 = ptx::ex2(fmaf(__uint_as_float(s1[2 * i + 1]), a.scale_log2, neg_m));
                     ps4[i & 3] += p0 + p1;
-                    pk[16 + i] = ptx::pack_bf16x2(p0, p1);
+                    pk[16 + i] = use_f16(SRC) ? ptx::pack_f16x2(p0, p1) : ptx::pack_bf16x2(p0, p1);
                 }
                 const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
                 l_sum = l_sum * alpha + psum;

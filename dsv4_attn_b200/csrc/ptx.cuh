@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace dsv4 {
@@ -221,6 +222,15 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
            | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// The same with FP16 operands (format code 0); both kinds of operand go through kind::f16.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4)
+           | (static_cast<uint32_t>(a_mn_major) << 15)
+           | (static_cast<uint32_t>(b_mn_major) << 16)
+           | (static_cast<uint32_t>(N >> 3) << 17)
+           | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -335,6 +345,24 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t saddr) {
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(lo), "f"(hi));     // first source -> upper half
+    return r;
+}
+
+// two BF16 in one word -> the same two values as FP16 (exact for magnitudes in FP16's normal range)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+    return pack_f16x2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
+// two FP8 e4m3 in the low 16 bits -> two FP16 (exact), element order kept
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(r) : "r"(two_bytes));
+    return r;
 }
 
 }  // namespace ptx
