@@ -49,7 +49,7 @@ extern "C" {
  * Takes the place of the reference's gather + attention core on pre-projected
  * tensors (bench/bench/reference.py:576-580 followed by :516-545); the
  * parameter-struct style follows hca/params.h:10-77 and csa/params.h:12-39.
-  * Arithmetic: FP32 accumulation; Q, P and the dequantised entries pass through FP16 operands,
+ * Arithmetic: FP32 accumulation; Q, P and the dequantised entries pass through FP16 operands,
  * so |q| and |fp8 * scale| must stay below 65504.
  */
 typedef struct Dsv4CsaSparseDecodeParams {
