@@ -960,34 +960,61 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 const float inv = (l_sum > 0.f) ? 1.f / denom : 0.f;
                 const float lse2 = (l_sum > 0.f) ? m_ref + log2f(l_sum) : -CUDART_INF_F;
                 const int64_t row = int64_t(n) * a.H + h;
+                // O leaves through shared memory (Q and the KV stages are free by now): each thread owns a
+                // row in tensor memory, but rows are 1 KB apart in global memory, so the rows are first
+                // laid down in shared memory (pitch = row + 16 bytes: conflict-free both ways) and then
+                // written out 512 contiguous bytes per warp instruction.
+                const uint32_t row_bytes = final_out ? uint32_t(kDvHalf) * 2u : uint32_t(kDvHalf) * 4u;
+                const uint32_t pitch = row_bytes + 16u;
+                static_assert(4 * 32 * (kDvHalf * 4 + 16) <= L::kQBytes + 2 * L::kKvStageBytes, "epilogue staging must fit in the Q + KV area");
+                const uint32_t stg = q_base + uint32_t(warp) * (32u * (uint32_t(kDvHalf) * 4u + 16u));
+                const uint32_t my = stg + uint32_t(lane) * pitch;
 #pragma unroll 1
                 for (int c = 0; c < kDvHalf / 32; ++c) {
                     uint32_t o[32];
                     ptx::tmem_ld32(tmem + lane_addr + kTmemO + c * 32, o);
                     ptx::tmem_wait_ld();
-                    if (write) {
-                        const int col = half * kDvHalf + c * 32;
-                        if (final_out) {
-                            uint4* dst = reinterpret_cast<uint4*>(a.out + row * 512 + col);
+                    if (final_out) {
 #pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 w;
-                                w.x = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                                w.y = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                                w.z = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                                w.w = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                                dst[v] = w;
-                            }
-                        } else {
-                            float4* dst = reinterpret_cast<float4*>(
-                                a.partial_o + (int64_t(split) * gridDim.y * a.H + row) * 512 + col);
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 w;
+                            w.x = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                            w.y = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                            w.z = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                            w.w = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                            ptx::sts_v4(my + uint32_t(c) * 64u + uint32_t(v) * 16u, w);
+                        }
+                    } else {
 #pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                dst[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                                                     __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                        for (int v = 0; v < 8; ++v) {
+                            uint4 w;
+                            w.x = __float_as_uint(__uint_as_float(o[4 * v + 0]) * inv);
+                            w.y = __float_as_uint(__uint_as_float(o[4 * v + 1]) * inv);
+                            w.z = __float_as_uint(__uint_as_float(o[4 * v + 2]) * inv);
+                            w.w = __float_as_uint(__uint_as_float(o[4 * v + 3]) * inv);
+                            ptx::sts_v4(my + uint32_t(c) * 128u + uint32_t(v) * 16u, w);
                         }
                     }
                 }
+                __syncwarp();
+                if (tid == 0) trace_mark(a, 3, 12);
+                {
+                    const uint32_t vecs_per_row = row_bytes / 16u;                  // 32 or 64
+                    const int h0 = hg * kHeadsPerCta + warp * 32;                   // first head row of this warp
+                    uint8_t* gbase = final_out
+                        ? reinterpret_cast<uint8_t*>(a.out + (int64_t(n) * a.H) * 512 + half * kDvHalf)
+                        : reinterpret_cast<uint8_t*>(a.partial_o + ((int64_t(split) * gridDim.y + n) * a.H) * 512 + half * kDvHalf);
+                    const int64_t grow = final_out ? 512 * 2 : 512 * 4;             // bytes between head rows in global memory
+#pragma unroll 4
+                    for (uint32_t q = uint32_t(lane); q < 32u * vecs_per_row; q += 32u) {
+                        const uint32_t rl = q / vecs_per_row, vc = q % vecs_per_row;
+                        if (h0 + int(rl) < a.H) {
+                            const uint4 w = ptx::lds_v4(stg + rl * pitch + vc * 16u);
+                            *reinterpret_cast<uint4*>(gbase + int64_t(h0 + int(rl)) * grow + vc * 16u) = w;
+                        }
+                    }
+                }
+                if (tid == 0) trace_mark(a, 3, 13);
                 if (write && half == 0) {
                     if (final_out) {
                         if (a.lse != nullptr) a.lse[row] = (l_sum > 0.f) ? lse2 * 0.6931471805599453f : -CUDART_INF_F;
