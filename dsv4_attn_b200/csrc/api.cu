@@ -336,7 +336,8 @@ extern "C" int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms) 
     // Cost model in units of one tile's time: a block costs a fixed set-up (Q
     // load, tensor-memory allocation, epilogue) plus its tiles; blocks run in
     // waves of `num_sms`; splitting adds the partial write + merge read.
-    const double fixed = 3.0, merge_per_split = 0.6;
+    // constants fitted to measurements on B200 (split sweep at 512 units x 32 tiles)
+    const double fixed = 4.0, merge_per_split = 3.2, merge_launch = 2.0;
     double best = 1e300;
     int best_s = 1;
     const int max_s = tiles < DSV4_MAX_SPLITS ? tiles : DSV4_MAX_SPLITS;
@@ -346,7 +347,7 @@ extern "C" int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms) 
         const int64_t blocks = units * s;
         const double waves = std::ceil(double(blocks) / num_sms);
         double cost = waves * (fixed + tps);
-        if (s > 1) cost += merge_per_split * s * std::ceil(double(units) / num_sms);
+        if (s > 1) cost += merge_per_split * s * (double(units) / num_sms) + merge_launch;   // partials written and re-read, one more launch
         if (cost < best - 1e-9) { best = cost;  best_s = s; }
     }
     return best_s;
