@@ -75,7 +75,8 @@ __host__ __device__ constexpr bool is_ref_layout(int src) { return src == kSrcRe
 // route costs five integer/FP instructions per two elements, and that arithmetic is a third of
 // the loaders' time), and FP16 keeps three more mantissa bits of fp8 x scale than BF16.  Q
 // and P are converted to FP16 as well (exact for Q inside FP16's normal range; P <= 2^8).
-// Limits: |fp8 x scale| and |q| below 65504 (the BF16 route's own limit on scales is 128).
+// Limits: |q| below 65504; block scales above 146 (entries beyond +-65408) are clamped to 146 (the
+// BF16 route's own limit on scales is 128).
 // The reference layouts keep BF16: their power-of-two scales span BF16's exponent range.
 __host__ __device__ constexpr bool use_f16(int src) { return !is_ref_layout(src); }
 
@@ -420,7 +421,8 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
             }
             const uint4 x = r.lat[g][j];
             if constexpr (use_f16(SRC)) {
-                const __half2 scale2 = __float2half2_rn(__uint_as_float(r.sc[g][j]));
+                // scales above 146 would take 448 x scale past FP16's largest finite value: such blocks saturate
+                const __half2 scale2 = __float2half2_rn(fminf(__uint_as_float(r.sc[g][j]), 146.f));
                 dequant4_f16(x.x, scale2, w0.x, w0.y);
                 dequant4_f16(x.y, scale2, w0.z, w0.w);
                 dequant4_f16(x.z, scale2, w1.x, w1.y);

@@ -50,7 +50,7 @@ extern "C" {
  * tensors (bench/bench/reference.py:576-580 followed by :516-545); the
  * parameter-struct style follows hca/params.h:10-77 and csa/params.h:12-39.
  * Arithmetic: FP32 accumulation; Q, P and the dequantised entries pass through FP16 operands,
- * so |q| and |fp8 * scale| must stay below 65504.
+ * so |q| must stay below 65504 and block scales above 146 (entries beyond +-65408) saturate.
  */
 typedef struct Dsv4CsaSparseDecodeParams {
     int32_t B;                  /* requests */

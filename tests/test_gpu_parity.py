@@ -427,3 +427,35 @@ def test_csa_with_attention_sink(lib, splits):
     gu.check_lse(lse, want_lse, f"csa sink splits={splits}")
     no_sink, _ = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale, kv_len=case.kv_len)
     assert np.abs(gu.bits_to_f32(no_sink) - gu.bits_to_f32(want_out)).max() > 1e-2     # the sink matters in this case
+
+
+def test_large_and_tiny_magnitudes_stay_finite_and_close(lib):
+    """The packed layout runs through FP16 operands: entries up to a few tens of thousands and
+    blocks of very small values must neither overflow nor lose the result.  Entry magnitudes vary
+    by page (x 1e-4 ... x 1e4); tolerance relative to the largest output value."""
+    rng = np.random.default_rng(93)
+    B, H, n_ent, W = 2, 32, 300, 128
+    pages = 5
+    mag = np.array([1e-4, 1.0, 300.0, 1e4, 3.0], np.float32)     # largest entries ~4.5e4, inside the 65504 limit
+    lat = rng.standard_normal((B * pages, orc.PAGE_ENTRIES, orc.D_LATENT), dtype=np.float32) * np.tile(mag, B)[:, None, None]
+    rope = rng.standard_normal((B * pages, orc.PAGE_ENTRIES, orc.D_ROPE), dtype=np.float32)
+    pool = orc.pack_entries(lat, rope)
+    bt = rng.permutation(B * pages).astype(np.int32).reshape(B, pages)
+    win = orc.pack_entries(rng.standard_normal((B, W, orc.D_LATENT), dtype=np.float32) * np.float32(50),
+                           rng.standard_normal((B, W, orc.D_ROPE), dtype=np.float32))
+    q = orc.bf16_round(rng.standard_normal((B, 1, H, orc.D_QK), dtype=np.float32) * np.float32(0.05))
+    kv_len = np.full((B, 1), n_ent, np.int32)
+    win_len = np.full((B, 1), 77, np.int32)
+    sm = orc.D_QK ** -0.5
+    want_out, want_lse = orc.hca_dense_decode(q, pool, bt, kv_len, win, win_len, sm)
+    out, lse = lib.hca_dense_decode(gu.dev(q, torch.bfloat16), gu.dev(pool), gu.dev(bt), gu.dev(kv_len), gu.dev(win),
+                                    gu.dev(win_len), sm, num_splits=1)
+    torch.cuda.synchronize()
+    got = gu.out_to_f32(out)
+    want = gu.bits_to_f32(want_out)
+    assert np.isfinite(got).all() and np.isfinite(lse.cpu().numpy()).all()
+    scale = np.abs(want).max()
+    assert scale > 100          # the large entries do carry weight here
+    assert np.abs(got - want).max() <= 2e-2 * scale
+    assert np.abs(got - want).mean() <= 2e-3 * scale
+    gu.check_lse(lse.cpu().numpy(), want_lse, "large magnitudes")
