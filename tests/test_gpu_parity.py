@@ -459,3 +459,50 @@ def test_large_and_tiny_magnitudes_stay_finite_and_close(lib):
     assert np.abs(got - want).max() <= 2e-2 * scale
     assert np.abs(got - want).mean() <= 2e-3 * scale
     gu.check_lse(lse.cpu().numpy(), want_lse, "large magnitudes")
+
+
+def test_entry_points_replay_from_a_cuda_graph(lib):
+    """The entry points only enqueue kernels on the caller's stream (tensor maps travel by value
+    as kernel parameters), so they can be captured into a CUDA graph and replayed, which is how
+    the reference's graph candidate calls hca_decode_fwd
+    (bench/bench/candidates/hca_custom_decode_graph.py:49-53).  Replays after the inputs changed
+    in place give the new inputs' results."""
+    z, kw = golden("ref_layout")
+    c = orc.make_ref_layout_case(**kw)
+    d = gu.dev
+    Q = d(c.Q, torch.bfloat16)
+    args = (Q, d(c.Kc), d(c.Kc_s), d(c.Kc_rope, torch.bfloat16), d(c.Kswa), d(c.Kswa_s), d(c.Kswa_rope, torch.bfloat16),
+            d(c.sink), c.sm_scale)
+    B, n_h, dq = Q.shape
+    O = torch.empty(B, n_h, dq, dtype=torch.bfloat16, device="cuda")
+    S = (kw["M_cur"] + kw["swa_len"]) // 128
+    pO = torch.empty(max(S, 1), B, n_h, dq, dtype=torch.float32, device="cuda")
+    pl = torch.empty(max(S, 1), B, n_h, dtype=torch.float32, device="cuda")
+    case = orc.make_csa_case(seed=31, B=2, s_q=1, H=32, n_entries=[400, 130], topk=128, ragged=True)
+    cargs = gu.csa_to_dev(case)
+    c_out = torch.empty(2, 1, 32, 512, dtype=torch.bfloat16, device="cuda")
+    c_lse = torch.empty(2, 1, 32, dtype=torch.float32, device="cuda")
+    ws = lib.alloc_workspace(2, 32, 2, "cuda")
+
+    def both():
+        lib.hca_decode_fwd(*args, M_cur=kw["M_cur"], swa_len=kw["swa_len"], O=O, partial_O=pO, partial_lse=pl)
+        lib.csa_sparse_decode(**cargs, num_splits=2, out=c_out, lse=c_lse, workspace=ws)
+
+    both()                                   # one eager call first: per-device kernel attributes are set lazily
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        both()
+    O.zero_();  c_out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    gu.check_out(gu.out_to_f32(O), z["out_fp8_dequant"], "graph replay, reference entry point")
+    want_out, _ = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices, case.sm_scale, kv_len=case.kv_len)
+    gu.check_out(gu.out_to_f32(c_out), want_out, "graph replay, CSA")
+    # new queries in the same buffers, same graph
+    q2 = orc.bf16_round(np.random.default_rng(5).standard_normal(case.q.shape, dtype=np.float32))
+    cargs["q"].copy_(gu.dev(q2, torch.bfloat16))
+    g.replay()
+    torch.cuda.synchronize()
+    want2, _ = orc.csa_sparse_decode(q2, case.pool, case.block_table, case.indices, case.sm_scale, kv_len=case.kv_len)
+    gu.check_out(gu.out_to_f32(c_out), want2, "graph replay with new queries")
