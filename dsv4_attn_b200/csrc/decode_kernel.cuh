@@ -478,6 +478,32 @@ __device__ __forceinline__ void convert_q_smem(uint32_t q_base, int tid) {
     ptx::fence_proxy_async_smem();
 }
 
+// Copy Q chunks [g0, g1) of the 32 head rows of lane quarter `warp % 4` from the staging area to
+// tensor memory: head row = tensor-memory lane, two 16-bit values per 32-bit column, in K order
+// (the A-operand layout of the MMA); converted to FP16 on the way when the kernel runs on FP16.
+template <bool F16>
+__device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint32_t tmem, int warp, int lane, int g0, int g1) {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const uint32_t srow = stage_base + uint32_t(r) * 128u;
+    const uint32_t sw = uint32_t(r & 7);
+#pragma unroll 1
+    for (int g = g0; g < g1; ++g) {
+        uint32_t w32[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint4 x = ptx::lds_v4(srow + uint32_t(g) * kQChunkBytes + ((uint32_t(j) ^ sw) << 4));
+            if constexpr (F16) {
+                x.x = ptx::bf16x2_to_f16x2(x.x);  x.y = ptx::bf16x2_to_f16x2(x.y);
+                x.z = ptx::bf16x2_to_f16x2(x.z);  x.w = ptx::bf16x2_to_f16x2(x.w);
+            }
+            w32[4 * j + 0] = x.x;  w32[4 * j + 1] = x.y;  w32[4 * j + 2] = x.z;  w32[4 * j + 3] = x.w;
+        }
+        ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w32);
+    }
+}
+
 template <int NCHUNK, int SRC>
 __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid_constant__ DecodeArgs a) {
     using L = SmemLayout<NCHUNK>;
@@ -538,7 +564,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
         ptx::mbar_init(bar_o_full, 1);
         ptx::mbar_init(bar_q_full, 1);
-        ptx::mbar_init(bar_q_ready, use_f16(SRC) ? kNumSoftmaxWarps + kNumLoaderWarps : kNumSoftmaxWarps);
+        ptx::mbar_init(bar_q_ready, kNumSoftmaxWarps + kNumLoaderWarps);
         ptx::fence_mbar_init();
         if (ntiles > 0) {
             // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
@@ -608,14 +634,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         if (lw == 0 && lane == 0) trace_mark(a, 3, 8);
         if (ntiles > 0) {
             bool lok = true;
-            if constexpr (use_f16(SRC)) {
-                // the loaders' share of the Q conversion, while their first loads are in flight
+            {
+                // the loaders' share of the Q set-up, while their first loads are in flight: warps
+                // 4-7 copy chunk 2 to tensor memory, warps 8-11 chunk 3, and (FP16 route) every
+                // thread converts its part of the chunks that stay in shared memory
                 const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
                 if (!__all_sync(0xFFFFFFFFu, w)) {
                     report_timeout(a.status, kStatusWaitQ, 2, tile0);
                     lok = false;
                 } else {
-                    convert_q_smem<L::kQBytes>(q_base, tid);
+                    const uint32_t tmem_q = misc->tmem_base;
+                    const int g = 2 + (lw >> 2);
+                    copy_q_chunks_to_tmem<use_f16(SRC)>(smem_base + L::kQStageOff, tmem_q, warp, lane, g, g + 1);
+                    if constexpr (use_f16(SRC)) convert_q_smem<L::kQBytes>(q_base, tid);
+                    ptx::tmem_wait_st();
+                    ptx::tc_fence_before_sync();
                 }
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_q_ready);     // also after a time-out, so that nobody waits for this warp
@@ -803,8 +836,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         const uint32_t tmem = misc->tmem_base;
         bool ok = true;
         if (ntiles > 0) {
-            // head row r = this thread's tensor-memory lane: copy its staged Q columns there,
-            // two BF16 per 32-bit column, in K order (the A-operand layout of the MMA)
             const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
             if (!__all_sync(0xFFFFFFFFu, w)) {
                 report_timeout(a.status, kStatusWaitQ, 0, tile0);
@@ -812,24 +843,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             }
             if (tid == 0) trace_mark(a, 3, 11);
             if (ok) {
-                const int r = warp * 32 + lane;
-                const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-                const uint32_t srow = smem_base + L::kQStageOff + uint32_t(r) * 128u;
-                const uint32_t sw = uint32_t(r & 7);
-#pragma unroll 1
-                for (int g = 0; g < kQTmemChunks; ++g) {
-                    uint32_t w32[32];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        uint4 x = ptx::lds_v4(srow + uint32_t(g) * kQChunkBytes + ((uint32_t(j) ^ sw) << 4));
-                        if constexpr (use_f16(SRC)) {
-                            x.x = ptx::bf16x2_to_f16x2(x.x);  x.y = ptx::bf16x2_to_f16x2(x.y);
-                            x.z = ptx::bf16x2_to_f16x2(x.z);  x.w = ptx::bf16x2_to_f16x2(x.w);
-                        }
-                        w32[4 * j + 0] = x.x;  w32[4 * j + 1] = x.y;  w32[4 * j + 2] = x.z;  w32[4 * j + 3] = x.w;
-                    }
-                    ptx::tmem_st32(tmem + lane_addr + kTmemQ + g * 32, w32);
-                }
+                // chunks 0-1 here, chunks 2 and 3 by the loader warps (each warp serves its lane quarter)
+                static_assert(kQTmemChunks == 4, "the split of the copy below is written for four chunks");
+                copy_q_chunks_to_tmem<use_f16(SRC)>(smem_base + L::kQStageOff, tmem, warp, lane, 0, 2);
                 if constexpr (use_f16(SRC)) {
                     // the Q chunks that stay in shared memory: BF16 -> FP16 in place (element-wise, so
                     // the swizzled layout is untouched), then made visible to the MMAs' reads
