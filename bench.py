@@ -78,6 +78,22 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def tensor_view(kv_bytes, H, ms):
+    """Achieved tensor throughput of one step (QK over 576 columns + PV over 512 per head and
+    attended entry) against the measured dense BF16 GEMM peak, for context next to the HBM view."""
+    flops = 2.0 * H * (576 + 512) * (kv_bytes / ENTRY_BYTES)
+    peak = None
+    try:
+        peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+    except Exception:
+        pass
+    tf = flops / (ms * 1e-3) / 1e12
+    src = "measured" if peak else "fallback"
+    peak = peak or 1590.0
+    return {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_source": src,
+            "note": "useful FLOPs only; each block also recomputes QK for the other half of the value columns"}
+
+
 # ───────────────────────── clocks sampling ─────────────────────────
 
 class ClockSampler:
@@ -565,6 +581,8 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "traffic": NCU_DRAM_TRAFFIC.get(args.workload), "traffic_source": NCU_TRAFFIC_SOURCE if args.workload in NCU_DRAM_TRAFFIC else None,
                      "algorithmic_bytes": head["kv_bytes"], "peak_source": peak_src, "kernel": "decode_mma_kernel" + ("+combine_kernel" if head["launches"] > 1 else "")},
+        # the same launch against the tensor-core bound: 2 x H x (576 + 512) FLOP per attended entry
+        "roofline_tensor": tensor_view(head["kv_bytes"], kw["H"], head["total_ms"] / args.steps),
         "clocks": clocks,
         "other_workloads": others,
     }

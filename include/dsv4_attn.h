@@ -13,7 +13,7 @@
  *     (cudaErrorInvalidValue = 1 for rejected arguments).  Nothing throws and
  *     nothing aborts.
  *
- * Cache entry ("BASELINE layout"), 656 bytes, 16-byte aligned:
+ * Cache entry (the packed 656-byte layout), 16-byte aligned:
  *     [  0,512)  512 x FP8 e4m3 latent (also the value vector, d_v = 512)
  *     [512,528)  4 x FP32 scale, one per 128 latent elements (value = fp8*scale)
  *     [528,656)  64 x BF16 RoPE tail (already rotated)
