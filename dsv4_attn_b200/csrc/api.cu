@@ -93,6 +93,7 @@ cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
         // evaluated alternative, kept selectable for measurements: cluster pairs that split the
         // query/key columns and exchange halves of S through distributed shared memory
         static bool done[kMaxDevices] = {};
+        a.partial_f32 = 1;                     // that kernel writes its split partials as FP32
         e = ensure_smem(pair::decode_pair_kernel<NCHUNK, SRC>, pair::kSmemTotal, done);
         if (e != cudaSuccess) return e;
         pair::decode_pair_kernel<NCHUNK, SRC><<<grid, kNumThreads, pair::kSmemTotal, stream>>>(a);
@@ -120,8 +121,9 @@ cudaError_t launch_combine(const CombineArgs& c, cudaStream_t stream) {
 }
 
 CombineArgs contiguous_combine(int rows, int H, int S, const float* po, const float* pl, void* out, float* lse,
-                               const float* sink) {
+                               const float* sink, bool partial_bf16 = false) {
     CombineArgs c{};
+    c.partial_bf16 = partial_bf16 ? 1 : 0;
     c.N = rows;  c.H = H;  c.num_splits = S;
     c.partial_o = po;  c.partial_lse = pl;
     c.out = static_cast<__nv_bfloat16*>(out);  c.lse = lse;  c.attn_sink = sink;
@@ -223,7 +225,8 @@ int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
     cudaError_t e = launch_mma<9, SRC>(a, rows, stream);
     if (e != cudaSuccess) return int(e);
     if (a.num_splits > 1) {
-        CombineArgs c = contiguous_combine(rows, a.H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink);
+        CombineArgs c = contiguous_combine(rows, a.H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
+                                           !a.partial_f32);
         e = launch_combine(c, stream);
     }
     return int(e);
@@ -337,7 +340,7 @@ extern "C" int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms) 
     // load, tensor-memory allocation, epilogue) plus its tiles; blocks run in
     // waves of `num_sms`; splitting adds the partial write + merge read.
     // constants fitted to measurements on B200 (split sweep at 512 units x 32 tiles)
-    const double fixed = 4.0, merge_per_split = 3.2, merge_launch = 2.0;
+    const double fixed = 4.0, merge_per_split = 1.8, merge_launch = 2.0;
     double best = 1e300;
     int best_s = 1;
     const int max_s = tiles < DSV4_MAX_SPLITS ? tiles : DSV4_MAX_SPLITS;
@@ -408,7 +411,7 @@ extern "C" int hca_decode_fwd(const void* Q,
     cudaError_t e = launch_mma<8, kSrcRef>(a, B, s);
     if (e != cudaSuccess) return int(e);
     if (splits > 1) {
-        CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink);
+        CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink, !a.partial_f32);
         e = launch_combine(cb, s);
     }
     return int(e);
@@ -548,7 +551,8 @@ extern "C" int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, vo
     cudaError_t e = launch_mma<8, kSrcRefPaged>(a, p->B, s);
     if (e != cudaSuccess) return int(e);
     if (a.num_splits > 1) {
-        CombineArgs cb = contiguous_combine(p->B, p->H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink);
+        CombineArgs cb = contiguous_combine(p->B, p->H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
+                                            !a.partial_f32);
         e = launch_combine(cb, s);
     }
     return int(e);

@@ -24,6 +24,7 @@ struct CombineArgs {
     int64_t stride_pl_split, stride_pl_n;
     int64_t stride_out_n, stride_out_h;
     int64_t stride_lse_n;
+    int partial_bf16;          // partial_o holds BF16 (strides then count BF16 elements): the library's own split path
 };
 
 constexpr int kCombineWarps = 8;
@@ -85,6 +86,21 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
             const float w = __shfl_sync(0xFFFFFFFFu, w_mine, k);
             if (w == 0.f) continue;     // empty split: its partial may hold anything
             const float* src = po + int64_t(s0 + k) * a.stride_po_split;
+            if (a.partial_bf16) {
+                const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(a.partial_o) + int64_t(n) * a.stride_po_n +
+                                          int64_t(h) * a.stride_po_h + lane * 8 + int64_t(s0 + k) * a.stride_po_split;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(sb + i * 256));
+                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[i][2 * j] = fmaf(w, __uint_as_float(u[j] << 16), acc[i][2 * j]);
+                        acc[i][2 * j + 1] = fmaf(w, __uint_as_float(u[j] & 0xFFFF0000u), acc[i][2 * j + 1]);
+                    }
+                }
+                continue;
+            }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const float4 v0 = __ldg(reinterpret_cast<const float4*>(src + i * 256));

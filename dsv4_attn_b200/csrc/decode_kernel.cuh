@@ -113,6 +113,7 @@ struct DecodeArgs {
     float* partial_o;
     float* partial_lse;
     int32_t* status;
+    int partial_f32;             // split partials as FP32 (default: BF16 in the same workspace)
     int dbg;                     // profiling aid: bit1 no L2 prefetch
     unsigned long long* trace;   // optional profiling aid: block (0,0,0) records phase times here
     // reference layout planes (kSrcRef)
@@ -982,7 +983,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 // row in tensor memory, but rows are 1 KB apart in global memory, so the rows are first
                 // laid down in shared memory (pitch = row + 16 bytes: conflict-free both ways) and then
                 // written out 512 contiguous bytes per warp instruction.
-                const uint32_t row_bytes = final_out ? uint32_t(kDvHalf) * 2u : uint32_t(kDvHalf) * 4u;
+                // (split partials are written as BF16 too: the merge reads them back at once, and at
+                // eight splits their traffic exceeds the KV bytes; the FP32 form remains for a.partial_f32)
+                const bool bf16_out = final_out || !a.partial_f32;
+                const uint32_t row_bytes = bf16_out ? uint32_t(kDvHalf) * 2u : uint32_t(kDvHalf) * 4u;
                 const uint32_t pitch = row_bytes + 16u;
                 static_assert(4 * 32 * (kDvHalf * 4 + 16) <= L::kQBytes + 2 * L::kKvStageBytes, "epilogue staging must fit in the Q + KV area");
                 const uint32_t stg = q_base + uint32_t(warp) * (32u * (uint32_t(kDvHalf) * 4u + 16u));
@@ -992,7 +996,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     uint32_t o[32];
                     ptx::tmem_ld32(tmem + lane_addr + kTmemO + c * 32, o);
                     ptx::tmem_wait_ld();
-                    if (final_out) {
+                    if (bf16_out) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
                             uint4 w;
@@ -1019,10 +1023,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 {
                     const uint32_t vecs_per_row = row_bytes / 16u;                  // 32 or 64
                     const int h0 = hg * kHeadsPerCta + warp * 32;                   // first head row of this warp
+                    const int64_t prow = ((int64_t(split) * gridDim.y + n) * a.H) * 512 + half * kDvHalf;   // element index
                     uint8_t* gbase = final_out
                         ? reinterpret_cast<uint8_t*>(a.out + (int64_t(n) * a.H) * 512 + half * kDvHalf)
-                        : reinterpret_cast<uint8_t*>(a.partial_o + ((int64_t(split) * gridDim.y + n) * a.H) * 512 + half * kDvHalf);
-                    const int64_t grow = final_out ? 512 * 2 : 512 * 4;             // bytes between head rows in global memory
+                        : (bf16_out ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(a.partial_o) + prow)
+                                    : reinterpret_cast<uint8_t*>(a.partial_o + prow));
+                    const int64_t grow = bf16_out ? 512 * 2 : 512 * 4;              // bytes between head rows in global memory
 #pragma unroll 4
                     for (uint32_t q = uint32_t(lane); q < 32u * vecs_per_row; q += 32u) {
                         const uint32_t rl = q / vecs_per_row, vc = q % vecs_per_row;
@@ -1054,6 +1060,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             const int col = half * kDvHalf + v * 8;
             if (final_out) {
                 *reinterpret_cast<uint4*>(a.out + row * 512 + col) = make_uint4(0, 0, 0, 0);
+            } else if (!a.partial_f32) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.partial_o) +
+                                          (int64_t(split) * gridDim.y * a.H + row) * 512 + col) = make_uint4(0, 0, 0, 0);
             } else {
                 float4* dst = reinterpret_cast<float4*>(a.partial_o + (int64_t(split) * gridDim.y * a.H + row) * 512 + col);
                 dst[0] = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -73,7 +73,7 @@ typedef struct Dsv4CsaSparseDecodeParams {
     const float*   attn_sink;   /* optional float [H], natural-log units, added to the denominator */
     void*          out;         /* bf16  [B, s_q, H, 512] */
     float*         lse;         /* optional float [B, s_q, H], natural log, sink excluded, -inf if empty */
-    float*         partial_o;   /* float [num_splits, B*s_q, H, 512] when num_splits > 1 */
+    float*         partial_o;   /* scratch of num_splits*B*s_q*H*512 floats when num_splits > 1 (contents unspecified afterwards) */
     float*         partial_lse; /* float [num_splits, B*s_q, H], log2 units */
     int32_t*       status;      /* optional int32 [DSV4_STATUS_WORDS], zeroed by the caller */
 } Dsv4CsaSparseDecodeParams;
@@ -347,7 +347,7 @@ typedef struct Dsv4HcaPackedDecodeParams {
     const float*   attn_sink;       /* float [H] natural-log units, or NULL */
     void*          out;             /* bf16 [B, H, 512] */
     float*         lse;             /* float [B, H] natural log, or NULL */
-    float*         partial_o;       /* float [num_splits, B, H, 512] when num_splits > 1 */
+    float*         partial_o;       /* scratch of num_splits*B*H*512 floats when num_splits > 1 (contents unspecified afterwards) */
     float*         partial_lse;     /* float [num_splits, B, H] */
     int32_t*       status;          /* optional int32[4], zeroed by the caller */
 } Dsv4HcaPackedDecodeParams;
