@@ -692,18 +692,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 0);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 1);
                 group_done(0);
-                if (it == 0) {
-                    // The first QK MMAs can start now.  The loads of tile 1 and the records of tiles 2
-                    // and 3 are requested only here: queued earlier they would hold up the stores above.
-                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
-                    loader_prefetch_l2<SRC>(key2, vm2, lane);
-                    loader_prefetch_l2<SRC>(key3, vm3, lane);
-                }
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 2);
                 loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 3);
                 loader_store_rope<NCHUNK, SRC>(kv_st, lw * 8, lane, regs);
                 group_done(1);
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
+                if (it == 0) {
+                    // Tile 0 is complete.  The loads of tile 1 and the records of tiles 2 and 3 are
+                    // requested only here: queued earlier they would hold up the stores above (the
+                    // load/store unit takes about a microsecond to accept a tile's worth of loads).
+                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
+                    loader_prefetch_l2<SRC>(key2, vm2, lane);
+                    loader_prefetch_l2<SRC>(key3, vm3, lane);
+                }
                 // this set is free again: loads of tile it+2, keys of tile it+5
                 if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
                 key2 = key3;  vm2 = vm3;
