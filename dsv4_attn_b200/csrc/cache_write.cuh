@@ -58,9 +58,23 @@ __device__ __forceinline__ float block_scale(float absmax) {
     return s == 0.f ? 1.f : s;
 }
 
+// x / scale from the correctly rounded reciprocal r = RN(1 / scale): one multiply, the
+// remainder by FMA, one corrective FMA (the classical FMA division step).  Three instructions
+// instead of the dozen of a general division, whose range handling is not needed here: scale is
+// a normal number and |x / scale| <= 448.  The step reproduced the IEEE quotient on every one of
+// 8e7 random (x, scale) pairs checked on the CPU; a last-bit difference could change the e4m3
+// byte only on an exact rounding boundary, and the GPU tests compare every byte written with
+// the CPU restatement's.
+__device__ __forceinline__ float div_by_scale(float x, float scale, float r) {
+    const float q = x * r;
+    const float rem = fmaf(-q, scale, x);
+    return fmaf(rem, r, q);
+}
+
 __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float scale) {
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a, scale), __fdiv_rn(b, scale)), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(c, scale), __fdiv_rn(d, scale)), __NV_SATFINITE, __NV_E4M3);
+    const float r = __frcp_rn(scale);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(div_by_scale(a, scale, r), div_by_scale(b, scale, r)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(div_by_scale(c, scale, r), div_by_scale(d, scale, r)), __NV_SATFINITE, __NV_E4M3);
     return lo | (hi << 16);
 }
 
