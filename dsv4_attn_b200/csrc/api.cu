@@ -643,12 +643,15 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     TopkArgs t{};
     t.rows = p->B * p->s_q;  t.k = p->k;  t.scores = p->scores;  t.stride = p->score_stride;  t.n_vis = p->n_vis;
     t.out = p->out_indices;  t.n_cap = p->max_pages * kIdxPageKeys;
-    // a copy of the score row in shared memory when it fits next to the kernel's static 38 KB
-    const int row_bytes = t.n_cap * int(sizeof(float));
+    // With few rows a cluster pair shares each row, so that more SMs take part.  A copy of the
+    // block's slice of the score row goes to shared memory when it fits next to the static 38 KB.
+    const bool pair = t.rows * 2 <= sms;
+    const int row_bytes = (pair ? (t.n_cap + 1) / 2 : t.n_cap) * int(sizeof(float));
     t.row_in_smem = row_bytes <= 180 * 1024 ? 1 : 0;
-    static bool done_topk[kMaxDevices] = {};
-    e = ensure_smem(topk_select_kernel, 180 * 1024, done_topk);
+    static bool done_topk[kMaxDevices] = {}, done_pair[kMaxDevices] = {};
+    e = pair ? ensure_smem(topk_select_pair_kernel, 180 * 1024, done_pair) : ensure_smem(topk_select_kernel, 180 * 1024, done_topk);
     if (e != cudaSuccess) return int(e);
-    topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
+    if (pair) topk_select_pair_kernel<<<t.rows * 2, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
+    else topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
     return int(cudaGetLastError());
 }

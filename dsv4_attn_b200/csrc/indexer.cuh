@@ -333,41 +333,53 @@ __device__ __forceinline__ void radix_select_emit(TopkShared& sh, int count, uin
     }
 }
 
-// One block per (request, token) row.  The scores of a row share a handful of floating-point
-// exponents, so a radix histogram over the raw bits would have every lane of a warp hit the same
-// counter.  Instead: (A) minimum and maximum of the row; (B) a histogram over 1024 equal-width
-// value bins - spread out, so the shared-memory atomics rarely collide; a block-wide suffix scan
-// finds the bin that holds the k-th largest score; (C) everything in higher bins is part of the
-// selection and is written out at once, the entries of the threshold bin (a few hundred) are
-// collected in shared memory and the remaining places are filled from them by an exact radix
-// select.  Binning is monotone in the score, so the result is the exact top-k (as a set).
-__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
+// One block - or, when there are few rows, a cluster pair of blocks that share a row - per
+// (request, token).  The scores of a row share a handful of floating-point exponents, so a radix
+// histogram over the raw bits would have every lane of a warp hit the same counter.  Instead:
+// (A) minimum and maximum of the row; (B) a histogram over 1024 equal-width value bins - spread
+// out, so the shared-memory atomics rarely collide; a block-wide suffix scan finds the bin that
+// holds the k-th largest score; (C) everything in higher bins is part of the selection and is
+// written out at once, the entries of the threshold bin (a few hundred) are collected in shared
+// memory and the remaining places are filled from them by an exact radix select.  Binning is
+// monotone in the score, so the result is the exact top-k (as a set).
+//
+// With a pair (C = 2) each block takes half of the row; range, histograms, output offsets and
+// the candidate list are combined through distributed shared memory, with cluster barriers that
+// both blocks reach unconditionally; block 0 of the pair does the final select.
+template <int C>
+__device__ __forceinline__ void topk_select_body(const TopkArgs& a, float* topk_row) {
     __shared__ TopkShared sh;
-    extern __shared__ float topk_row[];
-    const int row = blockIdx.x;
+    __shared__ uint32_t sh_x[4];          // exchanged with the peer: own count above the threshold bin, own count in it
+    const uint32_t rank = (C == 2) ? (blockIdx.x & 1u) : 0u;
+    const uint32_t peer = rank ^ 1u;
+    const int row = blockIdx.x / C;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = max(0, min(__ldg(a.n_vis + row), a.n_cap));
     const float* g = a.scores + int64_t(row) * a.stride;
-    // the three passes read the row from shared memory when it fits (copied during pass A)
-    const float* s = a.row_in_smem ? topk_row : g;
     int32_t* out = a.out + int64_t(row) * a.k;
-    if (n <= a.k) {
-        for (int i = tid; i < a.k; i += kTopkThreads) out[i] = (i < n) ? i : -1;
+    if (n <= a.k) {                                          // same decision in both blocks of a pair
+        if (rank == 0)
+            for (int i = tid; i < a.k; i += kTopkThreads) out[i] = (i < n) ? i : -1;
         return;
     }
+    // this block's slice of the row
+    const int half = (C == 2) ? (n + 1) / 2 : n;
+    const int s0 = int(rank) * half, s1 = min(n, s0 + half);
+    // the passes read the slice from shared memory when it fits (copied during pass A)
+    const float* s = a.row_in_smem ? topk_row - s0 : g;      // indexed by the global position i
     // (A) range of the finite scores
     float lo = CUDART_INF_F, hi = -CUDART_INF_F;
-    for (int i0 = tid; i0 < n; i0 += 8 * kTopkThreads) {
+    for (int i0 = s0 + tid; i0 < s1; i0 += 8 * kTopkThreads) {
         float v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {                        // eight loads in flight per thread
             const int i = i0 + u * kTopkThreads;
-            v[u] = (i < n) ? __ldg(g + i) : CUDART_NAN_F;
+            v[u] = (i < s1) ? __ldg(g + i) : CUDART_NAN_F;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int i = i0 + u * kTopkThreads;
-            if (a.row_in_smem && i < n) topk_row[i] = v[u];
+            if (a.row_in_smem && i < s1) topk_row[i - s0] = v[u];
             if (v[u] > -CUDART_INF_F && v[u] < CUDART_INF_F) { lo = fminf(lo, v[u]);  hi = fmaxf(hi, v[u]); }
         }
     }
@@ -380,7 +392,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArg
     sh.hist[tid] = 0;
     if (tid == 0) { sh.n_cand = 0;  sh.cnt_gt = 0; }
     __syncthreads();
+    if (C == 2) ptx::cluster_sync();                        // the peer's partial ranges are written
     lo = sh.red_lo[lane];  hi = sh.red_hi[lane];
+    if (C == 2) {
+        lo = fminf(lo, __uint_as_float(ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh.red_lo[lane]), peer))));
+        hi = fmaxf(hi, __uint_as_float(ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh.red_hi[lane]), peer))));
+    }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
@@ -393,34 +410,52 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArg
         const float x = (v - lo) * inv;
         return x >= float(kTopkBins - 1) ? kTopkBins - 1 : (x > 0.f ? int(x) : 0);
     };
-    // (B) histogram, then for every bin the number of entries in higher bins
-    for (int i = tid; i < n; i += kTopkThreads) atomicAdd(&sh.hist[bin_of(s[i])], 1u);
+    // (B) histogram of the slice, then for every bin the number of entries of the row in higher bins
+    for (int i = s0 + tid; i < s1; i += kTopkThreads) atomicAdd(&sh.hist[bin_of(s[i])], 1u);
     __syncthreads();
+    if (C == 2) ptx::cluster_sync();                        // both histograms complete
+    const uint32_t own = sh.hist[tid];
+    const uint32_t theirs = (C == 2) ? ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh.hist[tid]), peer)) : 0u;
     {
-        const uint32_t mine = sh.hist[tid];
-        uint32_t incl = mine;                               // suffix sum inside the warp (higher lanes = higher bins)
+        // two suffix scans in one: low 32 bits the row's counts, high 32 bits this block's own
+        unsigned long long incl = (unsigned long long)(own + theirs) | ((unsigned long long)own << 32);
+        const unsigned long long mine = incl;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const uint32_t o = __shfl_down_sync(0xFFFFFFFFu, incl, d);
+            const unsigned long long o = __shfl_down_sync(0xFFFFFFFFu, incl, d);
             if (lane + d < 32) incl += o;
         }
-        if (lane == 0) sh.warp_sum[warp] = incl;
+        unsigned long long* wsum = reinterpret_cast<unsigned long long*>(sh.cand_key);   // free until pass C
+        if (lane == 0) wsum[warp] = incl;
         __syncthreads();
-        uint32_t higher = 0;                                // entries in the warps above this one
-        for (int w = warp + 1; w < 32; ++w) higher += sh.warp_sum[w];
+        unsigned long long higher = 0;                      // entries in the warps above this one
+        for (int w = warp + 1; w < 32; ++w) higher += wsum[w];
         incl += higher;
-        const uint32_t excl = incl - mine;
-        if (excl < uint32_t(a.k) && incl >= uint32_t(a.k)) { sh.t_bin = uint32_t(tid);  sh.n_gt = excl;  sh.need = uint32_t(a.k) - excl; }
+        const unsigned long long excl = incl - mine;
+        const uint32_t incl_row = uint32_t(incl), excl_row = uint32_t(excl);
+        if (excl_row < uint32_t(a.k) && incl_row >= uint32_t(a.k)) {
+            sh.t_bin = uint32_t(tid);  sh.n_gt = excl_row;  sh.need = uint32_t(a.k) - excl_row;
+            sh_x[0] = uint32_t(excl >> 32);                 // this block's entries above the threshold bin
+            sh_x[1] = own;                                  // and inside it
+        }
     }
     __syncthreads();
+    if (C == 2) ptx::cluster_sync();                        // the peer's counts are written
     const int t_bin = int(sh.t_bin);
     const uint32_t n_gt = sh.n_gt, need = sh.need;
-    // (C) higher bins straight to the output, the threshold bin to the candidate list
-    for (int i0 = 0; i0 < n; i0 += kTopkThreads) {
+    // block 1 writes after block 0: offsets from block 0's counts
+    const uint32_t base_out = (rank == 0) ? 0u : ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh_x[0]), 0));
+    const uint32_t base_cand = (rank == 0) ? 0u : ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh_x[1]), 0));
+    const uint32_t peer_cand = (C == 2) ? ptx::lds_cluster_u32(ptx::mapa(ptx::smem_u32(&sh_x[1]), peer)) : 0u;
+    const uint32_t cand_key0 = (C == 2) ? ptx::mapa(ptx::smem_u32(&sh.cand_key[0]), 0) : 0u;
+    const uint32_t cand_idx0 = (C == 2) ? ptx::mapa(ptx::smem_u32(&sh.cand_idx[0]), 0) : 0u;
+    __syncthreads();                                        // the scan scratch (cand_key) is free again
+    // (C) higher bins straight to the output, the threshold bin to block 0's candidate list
+    for (int i0 = s0; i0 < s1; i0 += kTopkThreads) {
         const int i = i0 + tid;
         float v = 0.f;
         int bn = -1;
-        if (i < n) { v = s[i];  bn = bin_of(v); }
+        if (i < s1) { v = s[i];  bn = bin_of(v); }
         const bool gt = bn > t_bin, eq = bn == t_bin;
         const uint32_t m_gt = __ballot_sync(0xFFFFFFFFu, gt), m_eq = __ballot_sync(0xFFFFFFFFu, eq);
         const uint32_t below = (1u << lane) - 1u;
@@ -432,27 +467,47 @@ __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArg
         base_gt = __shfl_sync(0xFFFFFFFFu, base_gt, 0);
         base_eq = __shfl_sync(0xFFFFFFFFu, base_eq, 0);
         if (gt) {
-            out[base_gt + uint32_t(__popc(m_gt & below))] = i;       // exactly n_gt such entries exist
+            out[base_out + base_gt + uint32_t(__popc(m_gt & below))] = i;   // exactly n_gt such entries in the row
         } else if (eq) {
-            const uint32_t p = base_eq + uint32_t(__popc(m_eq & below));
-            if (p < uint32_t(kTopkCand)) { sh.cand_key[p] = float_key(v);  sh.cand_idx[p] = i; }
+            const uint32_t p = base_cand + base_eq + uint32_t(__popc(m_eq & below));
+            if (p < uint32_t(kTopkCand)) {
+                if (C == 2) {
+                    ptx::sts_cluster_u32(cand_key0 + 4u * p, float_key(v));
+                    ptx::sts_cluster_u32(cand_idx0 + 4u * p, uint32_t(i));
+                } else {
+                    sh.cand_key[p] = float_key(v);  sh.cand_idx[p] = i;
+                }
+            }
         }
     }
     __syncthreads();
-    const uint32_t n_cand = sh.n_cand;
+    if (C == 2) ptx::cluster_sync();                        // the candidate list in block 0 is complete
+    if (rank != 0) return;                                  // block 0 touches no memory of block 1 from here on
+    const uint32_t n_cand = sh.n_cand + peer_cand;
     if (n_cand <= uint32_t(kTopkCand)) {
         radix_select_emit(sh, int(n_cand), need, out + n_gt, [&](int j, uint32_t& key, int32_t& idx) {
             key = sh.cand_key[j];  idx = sh.cand_idx[j];
             return true;
         });
     } else {
-        // a threshold bin too crowded for the list (many equal scores): select among its entries in place
+        // a threshold bin too crowded for the list (many equal scores): select among its entries in
+        // place, over the whole row in global memory
         radix_select_emit(sh, n, need, out + n_gt, [&](int j, uint32_t& key, int32_t& idx) {
-            const float v = s[j];
+            const float v = g[j];
             key = float_key(v);  idx = j;
             return bin_of(v) == t_bin;
         });
     }
+}
+
+__global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
+    extern __shared__ float topk_row[];
+    topk_select_body<1>(a, topk_row);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTopkThreads) topk_select_pair_kernel(const TopkArgs a) {
+    extern __shared__ float topk_row[];
+    topk_select_body<2>(a, topk_row);
 }
 
 }  // namespace dsv4

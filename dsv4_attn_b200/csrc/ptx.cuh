@@ -94,6 +94,14 @@ __device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
     return r;
 }
+__device__ __forceinline__ uint32_t lds_cluster_u32(uint32_t caddr) {
+    uint32_t r;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(r) : "r"(caddr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void sts_cluster_u32(uint32_t caddr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(caddr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void sts_cluster_v4(uint32_t caddr, uint4 v) {
     asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(caddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");

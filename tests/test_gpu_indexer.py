@@ -108,3 +108,30 @@ def test_indexer_invalid_arguments(lib):
         lib.indexer_topk(gu.dev(c.q_fp8), gu.dev(qw), gu.dev(pages)[:, :8000].contiguous(), gu.dev(bt), gu.dev(c.n_vis), 8)
     with pytest.raises(ValueError):
         lib.indexer_topk(gu.dev(c.q_fp8), gu.dev(qw), gu.dev(pages), gu.dev(bt), gu.dev(c.n_vis), 0)
+
+
+def test_indexer_many_rows_single_block_per_row(lib):
+    """With more rows than half the SMs the selection runs one block per row (fewer rows share a
+    row between a cluster pair of blocks): both paths must agree with the oracle."""
+    B = 80
+    rng = np.random.default_rng(17)
+    n_vis = rng.integers(1, 400, size=(B, 1)).astype(np.int32)
+    n_vis[0, 0], n_vis[1, 0] = 400, 33
+    c = orc.make_indexer_case(seed=117, B=B, s_q=1, n=400, n_vis=n_vis)
+    pages, bt, qw = indexer_inputs(c, np.random.default_rng(6))
+    idx, scores = run(lib, c, pages, bt, qw, c.n_vis, 32)
+    want = orc.indexer_scores(c.q_fp8, qw, pages, bt, c.n_vis)
+    check_selection(idx, scores, want, c.n_vis, 32)
+
+
+def test_topk_with_many_equal_scores(lib):
+    """All keys equal: every score of a row is the same, the threshold bin holds the whole row and
+    the in-place fallback of the selection runs; any k distinct visible entries are a valid answer."""
+    c = orc.make_indexer_case(seed=118, B=2, s_q=1, n=6000)
+    c.K[:] = c.K[:, :1]                       # identical keys per request
+    pages, bt, qw = indexer_inputs(c, np.random.default_rng(7))
+    idx, scores = run(lib, c, pages, bt, qw, c.n_vis, 100)
+    for b in range(2):
+        taken = idx[b, 0]
+        assert (taken >= 0).all() and (taken < 6000).all() and len(np.unique(taken)) == 100
+        assert np.ptp(scores[b, :6000]) <= 1e-5 * np.abs(scores[b, :6000]).max() + 1e-6
