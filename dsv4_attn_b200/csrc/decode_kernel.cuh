@@ -605,6 +605,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         // pulled into L2), and of the tile four ahead (resolved, not yet prefetched)
         unsigned long long key1 = 0, key2 = 0, key3 = 0, key4 = 0;
         uint32_t vm1 = 0, vm2 = 0, vm3 = 0, vm4 = 0;
+        int e_ahead = -1;        // CSA: this lane's index-list value of the tile resolved next (lanes 0-7)
         if (lw == 0 && lane == 0) trace_mark(a, 3, 4);
         if (ntiles > 0) {
             // one round of dependent loads for the first four tiles: lanes 0-7, 8-15, 16-23, 24-31
@@ -618,6 +619,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             const uint32_t bal = __ballot_sync(0xFFFFFFFFu, valid);
             vm4 = __ballot_sync(0xFFFFFFFFu, valid4) & 0xFFu;
             key4 = k4;
+            if constexpr (SRC == kSrcCsa) {
+                // the index-list values of tile 5 (lanes 0-7), on their way one step before they are needed
+                const int v5 = (tile0 + 5) * kTileN + lw * 8 + lane;
+                if (lane < 8 && 5 < ntiles && v5 < n_tok) e_ahead = __ldg(a.indices + int64_t(n) * a.topk + v5);
+            }
             if (lw == 0 && lane == 0) trace_mark(a, 3, 5);
             vm2 = (bal >> 16) & 0xFFu;
             vm3 = (bal >> 24) & 0xFFu;
@@ -709,8 +715,24 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
                 key2 = key3;  vm2 = vm3;
                 key3 = key4;  vm3 = vm4;
-                key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 5) * kTileN + lw * 8, lane,
-                                                (it + 5 < ntiles) ? n_tok : 0, kv_len_n, vm4);
+                if constexpr (SRC == kSrcCsa) {
+                    // Tile it+5: its index-list values were requested one step ago, so the ballot below
+                    // does not wait for a load; the block-table load issued here is consumed a step
+                    // later, and the index-list values of tile it+6 are requested now.
+                    const bool valid = e_ahead >= 0 && e_ahead < kv_len_n;       // e_ahead is -1 past the list or the tiles
+                    unsigned long long key = 0;
+                    if (valid) {
+                        const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (e_ahead >> 6));
+                        key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (e_ahead & 63)) * 656);
+                    }
+                    vm4 = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
+                    key4 = key;
+                    const int v6 = (tile0 + it + 6) * kTileN + lw * 8 + lane;
+                    e_ahead = (lane < 8 && it + 6 < ntiles && v6 < n_tok) ? __ldg(a.indices + int64_t(n) * a.topk + v6) : -1;
+                } else {
+                    key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 5) * kTileN + lw * 8, lane,
+                                                    (it + 5 < ntiles) ? n_tok : 0, kv_len_n, vm4);
+                }
             };
             for (int it = 0; it < ntiles && lok; it += 2) {
                 tile_step(regs_a, it);
