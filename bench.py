@@ -516,6 +516,30 @@ def run_ours(args):
                          "sharding": "sorted by context, dealt round-robin"}
         del csa_w, hca_w
         torch.cuda.empty_cache()
+    if "head_sharded" in args.extras and world > 1 and 128 % world == 0:
+        # Optional variant, for comparison only: every rank holds the WHOLE headline batch (same seed) and
+        # computes 128 / world heads of every request; one NCCL all-gather of out (+ lse) over NVLink.
+        # The KV bytes counted are those of one copy of the batch; every rank streams all of them.
+        import dsv4_attn_b200 as lib
+        from dsv4_attn_b200 import dp
+        kind_h, wh, _ = build_workload(args.workload, seed=777, device=dev)
+        if kind_h == "hca":
+            Bh, sq_h, Hh, _ = wh.q.shape
+            h0, h1 = dp.head_shard(Hh, world, rank)
+            out_l = torch.empty(Bh, sq_h, h1 - h0, 512, dtype=torch.bfloat16, device=dev)
+            lse_l = torch.empty(Bh, sq_h, h1 - h0, dtype=torch.float32, device=dev)
+
+            def dec(qs, sink):
+                return lib.hca_dense_decode(qs, wh.kv_pool, wh.block_table, wh.kv_len, wh.win_pool, wh.win_len, wh.sm_scale,
+                                            attn_sink=sink, num_splits=1, out=out_l, lse=lse_l, max_len=wh.max_len)
+            hs = time_steps(lambda: dp.head_sharded_decode(dec, wh.q, wh.attn_sink), max(3, min(args.steps, 10)), 3, flush, barrier)
+            hs_ms = reduce_max(statistics.mean(hs))
+            others["head_sharded_" + args.workload] = {
+                "us_per_layer": hs_ms * 1e3, "kv_tb_per_s": wh.kv_bytes / (hs_ms * 1e-3) / 1e12, "kv_bytes_one_copy": wh.kv_bytes,
+                "kv_bytes_read_all_ranks": wh.kv_bytes * world, "heads_per_rank": h1 - h0, "collective": "all_gather(out) + all_gather(lse), NCCL",
+                "scaling": "strong", "timing": "isolated (L2 flushed, eager)"}
+        del wh
+        torch.cuda.empty_cache()
     if "cache_write" in args.extras and world == 1:
         # the cache-write side: CSA compressor second pass (a pure streaming kernel)
         import dsv4_attn_b200 as lib
@@ -679,8 +703,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads")
-    ap.add_argument("--extras", default="mixed,cache_write,indexer,decode",
-                    help="which groups of other workloads to run: mixed, cache_write, indexer, decode (comma-separated)")
+    ap.add_argument("--extras", default="mixed,head_sharded,cache_write,indexer,decode",
+                    help="which groups of other workloads to run: mixed, head_sharded (N > 1), cache_write, indexer, decode (comma-separated)")
     args = ap.parse_args()
     args.extras = set() if args.no_extras else {x for x in args.extras.split(",") if x}
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

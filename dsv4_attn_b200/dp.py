@@ -54,3 +54,44 @@ def aggregate_throughput(local_units: float, local_seconds: float, device=None) 
     total = reduce_scalar(local_units, "sum", device)
     slowest = reduce_scalar(local_seconds, "max", device)
     return total / slowest if slowest > 0 else 0.0
+
+
+# ── optional head-sharded variant ──────────────────────────────────────
+# Every rank holds the whole batch's KV cache and computes a slice of the heads for all
+# requests; one all-gather over the head dimension puts the outputs together.  It multiplies the
+# KV bytes read by the number of ranks (each rank streams every entry) and is measured only for
+# comparison with the request-sharded default, which needs no collective at all.
+
+def head_shard(n_heads: int, world: int, rank: int):
+    """[h0, h1): the heads rank `rank` of `world` computes; n_heads must divide evenly."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world {world}")
+    if n_heads % world != 0:
+        raise ValueError(f"{n_heads} heads do not divide over {world} ranks")
+    per = n_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def head_sharded_decode(decode_fn, q, attn_sink=None, group=None):
+    """q [B, s_q, H, D] on every rank (same values).  Calls decode_fn(q_slice, sink_slice) ->
+    (out [B, s_q, H/world, Dv], lse [B, s_q, H/world]) for this rank's heads and all-gathers both
+    along the head dimension (one collective each, NCCL over NVLink on GPUs).  Returns the full
+    (out [B, s_q, H, Dv], lse [B, s_q, H]) on every rank."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    H = q.shape[2]
+    h0, h1 = head_shard(H, world, rank)
+    out_l, lse_l = decode_fn(q[:, :, h0:h1].contiguous(), None if attn_sink is None else attn_sink[h0:h1].contiguous())
+    if world == 1:
+        return out_l, lse_l
+    B, s_q, Hl, Dv = out_l.shape
+    # gathered as a concatenation along the first dimension (the form every backend takes), then viewed per rank
+    out_g = torch.empty((world * B, s_q, Hl, Dv), dtype=out_l.dtype, device=out_l.device)
+    lse_g = torch.empty((world * B, s_q, Hl), dtype=lse_l.dtype, device=lse_l.device)
+    dist.all_gather_into_tensor(out_g, out_l.contiguous(), group=group)
+    dist.all_gather_into_tensor(lse_g, lse_l.contiguous(), group=group)
+    out = out_g.view(world, B, s_q, Hl, Dv).permute(1, 2, 0, 3, 4).reshape(B, s_q, H, Dv)
+    lse = lse_g.view(world, B, s_q, Hl).permute(1, 2, 0, 3).reshape(B, s_q, H)
+    return out, lse

@@ -68,3 +68,42 @@ def test_aggregate_over_two_gloo_ranks():
     for _, agg, n_total in res:
         assert n_total == 101
         assert agg == pytest.approx(101 * 656 / 2.0)   # all units over the slowest rank's time
+
+
+
+def _head_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(5)
+        q = torch.randn(3, 2, 8, 16, generator=g)                 # the same on every rank
+        sink = torch.arange(8, dtype=torch.float32)
+
+        def fake_decode(q_slice, sink_slice):                      # per-head work only, like attention
+            o = q_slice[..., :4] * 2.0 + sink_slice.view(1, 1, -1, 1)
+            return o, q_slice.sum(-1)
+
+        o, l = dp.head_sharded_decode(fake_decode, q, sink)
+        want_o = q[..., :4] * 2.0 + sink.view(1, 1, -1, 1)
+        out.put((rank, bool(torch.equal(o, want_o)), bool(torch.equal(l, q.sum(-1))), tuple(o.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_variant_over_two_gloo_ranks():
+    assert dp.head_shard(128, 8, 3) == (48, 64)
+    with pytest.raises(ValueError):
+        dp.head_shard(10, 4, 0)
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_head_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok_o, ok_l, shape in res:
+        assert ok_o and ok_l and shape == (3, 2, 8, 4)
