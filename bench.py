@@ -612,6 +612,32 @@ def run_ours(args):
         del qf, kp, sc_ws
         torch.cuda.empty_cache()
     if "decode" in args.extras and world == 1:
+        # the reference's own entry point and cache layout (448 e4m3 + 7 UE8M0 + 64 bf16 per token), at the
+        # shape the reference harness runs it: B=64, 128 heads, 768 compressed + 128 window tokens
+        import dsv4_attn_b200 as lib
+        Br, Mr, Wr = 64, 768, 128
+        Qr = (0.5 * torch.randn(Br, 128, 512, device=dev)).to(torch.bfloat16)
+        mk = lambda n: (torch.randint(0, 120, (Br, n, 448), dtype=torch.uint8, device=dev) |
+                        (torch.randint(0, 2, (Br, n, 448), dtype=torch.uint8, device=dev) << 7))
+        Kc, Ks = mk(Mr), mk(Wr)
+        Kc_s = torch.full((Br, Mr, 7), 119, dtype=torch.uint8, device=dev)          # 2^-8
+        Ks_s = torch.full((Br, Wr, 7), 119, dtype=torch.uint8, device=dev)
+        Kc_r = (0.5 * torch.randn(Br, Mr, 64, device=dev)).to(torch.bfloat16)
+        Ks_r = (0.5 * torch.randn(Br, Wr, 64, device=dev)).to(torch.bfloat16)
+        sink_r = 0.1 * torch.randn(128, device=dev)
+        Or = torch.empty(Br, 128, 512, dtype=torch.bfloat16, device=dev)
+        Sr = (Mr + Wr) // 128
+        pOr = torch.empty(Sr, Br, 128, 512, dtype=torch.float32, device=dev)
+        plr = torch.empty(Sr, Br, 128, dtype=torch.float32, device=dev)
+        rt = time_steps(lambda: lib.hca_decode_fwd(Qr, Kc, Kc_s, Kc_r, Ks, Ks_s, Ks_r, sink_r, 512 ** -0.5, M_cur=Mr, swa_len=Wr,
+                                                   O=Or, partial_O=pOr, partial_lse=plr), max(3, min(args.steps, 10)), 3, flush, barrier)
+        rbytes = Br * (Mr + Wr) * 583
+        rms = statistics.mean(rt)
+        others["hca_decode_fwd_reference_layout_b64_m768_w128"] = {
+            "isolated_us": rms * 1e3, "kv_tb_per_s": rbytes / (rms * 1e-3) / 1e12, "hbm_frac": rbytes / (rms * 1e-3) / 1e9 / peak,
+            "kv_bytes": rbytes, "timing": "isolated (L2 flushed, eager)"}
+        del Kc, Ks, pOr
+        torch.cuda.empty_cache()
         for name in WORKLOADS:
             if name == args.workload:
                 continue
