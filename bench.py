@@ -582,6 +582,17 @@ def run_ours(args):
         qms = statistics.mean(qt)
         others["kv_quantize_insert_65536rows"] = {"us": qms * 1e3, "gb_per_s": qbytes / (qms * 1e-3) / 1e9,
                                                   "hbm_frac": qbytes / (qms * 1e-3) / 1e9 / peak, "bytes": qbytes}
+        # RoPE + RMS norm pre-pass on a prefill-sized batch of query vectors (65536 tokens x 16 heads x 576)
+        xr = torch.randn(65536, 16, ch, device=dev).to(torch.bfloat16)
+        posr = torch.randint(0, 100000, (65536,), dtype=torch.int32, device=dev)
+        wr = torch.ones(ch, dtype=torch.bfloat16, device=dev)
+        outr = torch.empty_like(xr)
+        rt = time_steps(lambda: lib.rope_norm(xr, posr, norm_weight=wr, out=outr), max(3, min(args.steps, 10)), 3, flush, barrier)
+        rbytes = 2 * xr.numel() * 2
+        rms_ = statistics.mean(rt)
+        others["rope_norm_65536x16x576"] = {"us": rms_ * 1e3, "gb_per_s": rbytes / (rms_ * 1e-3) / 1e9,
+                                            "hbm_frac": rbytes / (rms_ * 1e-3) / 1e9 / peak, "bytes": rbytes}
+        del xr, outr
         del rows_q, pool_q, pool_h
         torch.cuda.empty_cache()
     if "indexer" in args.extras and world == 1:

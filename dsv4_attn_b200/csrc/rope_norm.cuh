@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeN
     const int nope = a.c - a.n_rope;
     const int half = a.n_rope >> 1;        // 32: one rotated pair per lane
     const int64_t total = a.n_rows * a.vecs_per_row;
+    // frequency of this lane's pair, 1 / theta^(2 i / n_rope): once per thread, not per vector
+    const float freq = (lane < half) ? float(1.0 / pow(double(a.theta), double(2 * lane) / double(a.n_rope))) : 0.f;
     for (int64_t v = int64_t(blockIdx.x) * (kRopeNormThreads / 32) + (threadIdx.x >> 5); v < total;
          v += int64_t(gridDim.x) * (kRopeNormThreads / 32)) {
         const int64_t row = v / a.vecs_per_row;
@@ -66,8 +68,7 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeN
         if (lane < half) {
             x1 = __bfloat162float(src[nope + lane]);
             x2 = __bfloat162float(src[nope + half + lane]);
-            // frequency 1 / theta^(2 i / n_rope); the angle in FP32 as the reference forms it
-            const float freq = float(1.0 / pow(double(a.theta), double(2 * lane) / double(a.n_rope)));
+            // the angle in FP32 as the reference forms it
             const float pos = float(__ldg(a.positions + row));
             float sn, cs;
             sincosf((a.inverse ? -pos : pos) * freq, &sn, &cs);
@@ -81,19 +82,20 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeN
             for (int k = 0; k < 16; ++k) ss = fmaf(f[k], f[k], ss);
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, d);
-            const float rms = sqrtf(ss / float(a.c) + a.eps);
+            // x / rms * w as x * (1 / rms) * w: the difference is far below the BF16 rounding of the result
+            const float inv_rms = 1.f / sqrtf(ss / float(a.c) + a.eps);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 if (have[h]) {
                     float w[8];
                     unpack8(__ldg(reinterpret_cast<const uint4*>(a.weight + 16 * lane + 8 * h)), w);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) f[8 * h + k] = __fdiv_rn(f[8 * h + k], rms) * w[k];
+                    for (int k = 0; k < 8; ++k) f[8 * h + k] = f[8 * h + k] * inv_rms * w[k];
                 }
             }
             if (lane < half) {
-                x1 = __fdiv_rn(x1, rms) * __bfloat162float(a.weight[nope + lane]);
-                x2 = __fdiv_rn(x2, rms) * __bfloat162float(a.weight[nope + half + lane]);
+                x1 = x1 * inv_rms * __bfloat162float(a.weight[nope + lane]);
+                x2 = x2 * inv_rms * __bfloat162float(a.weight[nope + half + lane]);
             }
         }
         // without a norm the part that is not rotated is unchanged: written only when out is another buffer
