@@ -574,8 +574,8 @@ extern "C" int dsv4_rope_norm_fwd(const Dsv4RopeNormParams* p, void* stream) {
     a.weight = static_cast<const __nv_bfloat16*>(p->norm_weight);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int64_t vecs = a.n_rows * a.vecs_per_row;
-    const int64_t want = (vecs + kRopeNormThreads / 32 - 1) / (kRopeNormThreads / 32);
+    const int64_t items = a.n_rows * ((a.vecs_per_row + kRopeGroup - 1) / kRopeGroup);
+    const int64_t want = (items + kRopeNormThreads / 32 - 1) / (kRopeNormThreads / 32);
     const int64_t cap = int64_t(sms) * 8;
     rope_norm_kernel<<<int(want < cap ? want : cap), kRopeNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return int(cudaGetLastError());

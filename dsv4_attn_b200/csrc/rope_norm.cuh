@@ -33,17 +33,30 @@ struct RopeNormArgs {
 };
 
 constexpr int kRopeNormThreads = 256;
+constexpr int kRopeGroup = 4;           // vectors of one row handled by one warp
 
 __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeNormArgs a) {
     const int lane = threadIdx.x & 31;
     const int nope = a.c - a.n_rope;
     const int half = a.n_rope >> 1;        // 32: one rotated pair per lane
-    const int64_t total = a.n_rows * a.vecs_per_row;
     // frequency of this lane's pair, 1 / theta^(2 i / n_rope): once per thread, not per vector
     const float freq = (lane < half) ? float(1.0 / pow(double(a.theta), double(2 * lane) / double(a.n_rope))) : 0.f;
-    for (int64_t v = int64_t(blockIdx.x) * (kRopeNormThreads / 32) + (threadIdx.x >> 5); v < total;
-         v += int64_t(gridDim.x) * (kRopeNormThreads / 32)) {
-        const int64_t row = v / a.vecs_per_row;
+    // A warp takes up to kRopeGroup vectors of one row in turn: they share the position, so the sine
+    // and cosine are computed once for them.
+    const int groups_per_row = (a.vecs_per_row + kRopeGroup - 1) / kRopeGroup;
+    const int64_t n_items = a.n_rows * groups_per_row;
+    for (int64_t item = int64_t(blockIdx.x) * (kRopeNormThreads / 32) + (threadIdx.x >> 5); item < n_items;
+         item += int64_t(gridDim.x) * (kRopeNormThreads / 32)) {
+      const int64_t row = item / groups_per_row;
+      const int vec0 = int(item % groups_per_row) * kRopeGroup;
+      float sn = 0.f, cs = 1.f;
+      if (lane < half) {
+          // the angle in FP32 as the reference forms it
+          const float pos = float(__ldg(a.positions + row));
+          sincosf((a.inverse ? -pos : pos) * freq, &sn, &cs);
+      }
+      for (int j = 0; j < kRopeGroup && vec0 + j < a.vecs_per_row; ++j) {
+        const int64_t v = row * a.vecs_per_row + vec0 + j;
         const __nv_bfloat16* src = a.x + v * a.c;
         __nv_bfloat16* dst = a.out + v * a.c;
         // elements [16 lane, 16 lane + 16) of the part that is not rotated, in two 16-byte halves
@@ -68,10 +81,6 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeN
         if (lane < half) {
             x1 = __bfloat162float(src[nope + lane]);
             x2 = __bfloat162float(src[nope + half + lane]);
-            // the angle in FP32 as the reference forms it
-            const float pos = float(__ldg(a.positions + row));
-            float sn, cs;
-            sincosf((a.inverse ? -pos : pos) * freq, &sn, &cs);
             const float r1 = x1 * cs - x2 * sn;
             const float r2 = x1 * sn + x2 * cs;
             x1 = r1;  x2 = r2;
@@ -114,6 +123,7 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_kernel(const RopeN
             dst[nope + lane] = __float2bfloat16_rn(x1);
             dst[nope + half + lane] = __float2bfloat16_rn(x2);
         }
+      }
     }
 }
 
