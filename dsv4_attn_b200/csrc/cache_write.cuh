@@ -18,6 +18,7 @@
 #include <cuda_fp8.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <type_traits>
 
 #include "ptx.cuh"
 #include "compress_reduce.cuh"   // unpack8
@@ -115,16 +116,23 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
     const int rows_per = (a.m + kHcaRowGroups - 1) / kHcaRowGroups;
     const int r0 = rg * rows_per, r1 = min(r0 + rows_per, a.m);
 
+    // The running maximum starts at a large negative finite value instead of -inf, so that the
+    // update below needs no special cases: with it every difference stays finite, a logit of -inf
+    // gets weight zero, and a block whose logits are all -inf ends with a zero denominator (NaN
+    // out, as in the reference's softmax).
+    constexpr float kLowest = -1e30f;
     float mx[8], l[8], acc[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) { mx[k] = -CUDART_INF_F;  l[k] = 0.f;  acc[k] = 0.f; }
+    for (int k = 0; k < 8; ++k) { mx[k] = kLowest;  l[k] = 0.f;  acc[k] = 0.f; }
     if (active) {
         const int64_t base = int64_t(b) * a.stride_b + int64_t(blk) * a.m * a.stride_n + ch;
-        for (int r = r0; r < r1; r += kHcaBatch) {
+        // one step = kHcaBatch rows; FULL: all of them exist (no per-row predicates in the code)
+        auto step = [&](int r, auto full_tag) {
+            constexpr bool FULL = decltype(full_tag)::value;
             uint4 zv[kHcaBatch], cv[kHcaBatch], bv[kHcaBatch];
 #pragma unroll
             for (int j = 0; j < kHcaBatch; ++j) {
-                if (r + j < r1) {
+                if (FULL || r + j < r1) {
                     zv[j] = ptx::ldg_nc_v4(a.Z + base + int64_t(r + j) * a.stride_n);
                     cv[j] = ptx::ldg_nc_v4(a.C + base + int64_t(r + j) * a.stride_n);
                     bv[j] = __ldg(reinterpret_cast<const uint4*>(a.bias + int64_t(r + j) * a.c + ch));
@@ -136,48 +144,43 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
             // registers; the logits themselves are formed in FP32 below.
             __nv_bfloat162 pm[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) pm[k] = __float2bfloat162_rn(-CUDART_INF_F);
+            for (int k = 0; k < 4; ++k) pm[k] = __float2bfloat162_rn(kLowest);
 #pragma unroll
             for (int j = 0; j < kHcaBatch; ++j) {
-                if (r + j < r1) {
+                if (FULL || r + j < r1) {
                     const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&zv[j]);
                     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&bv[j]);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) pm[k] = __hmax2(pm[k], __hadd2(z2[k], u2[k]));
                 }
             }
-            float bmax[8];
+            float nref[8];                       // -(new reference maximum) * log2(e)
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                bmax[2 * k] = fmaxf(mx[2 * k], __low2float(pm[k]));
-                bmax[2 * k + 1] = fmaxf(mx[2 * k + 1], __high2float(pm[k]));
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                // all logits so far -inf (or NaN): keep the subtraction finite
-                const float ref = (bmax[k] > -CUDART_INF_F && bmax[k] < CUDART_INF_F) ? bmax[k] : 0.f;
-                const float alpha = ptx::ex2((mx[k] - ref) * kLog2e);   // 0 while mx is -inf
-                l[k] *= alpha;
-                acc[k] *= alpha;
-                mx[k] = (bmax[k] > -CUDART_INF_F) ? ref : -CUDART_INF_F;
-                bmax[k] = -ref * kLog2e;
+                const float r_lo = fmaxf(mx[2 * k], __low2float(pm[k])), r_hi = fmaxf(mx[2 * k + 1], __high2float(pm[k]));
+                const float a_lo = ptx::ex2((mx[2 * k] - r_lo) * kLog2e), a_hi = ptx::ex2((mx[2 * k + 1] - r_hi) * kLog2e);
+                l[2 * k] *= a_lo;      acc[2 * k] *= a_lo;      mx[2 * k] = r_lo;      nref[2 * k] = -r_lo * kLog2e;
+                l[2 * k + 1] *= a_hi;  acc[2 * k + 1] *= a_hi;  mx[2 * k + 1] = r_hi;  nref[2 * k + 1] = -r_hi * kLog2e;
             }
 #pragma unroll
             for (int j = 0; j < kHcaBatch; ++j) {
-                if (r + j < r1) {
+                if (FULL || r + j < r1) {
                     float z[8], u[8], cf[8];
                     unpack8(zv[j], z);
                     unpack8(bv[j], u);
                     unpack8(cv[j], cf);
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
-                        const float e = ptx::ex2(fmaf(z[k] + u[k], kLog2e, bmax[k]));
+                        const float e = ptx::ex2(fmaf(z[k] + u[k], kLog2e, nref[k]));
                         l[k] += e;
                         acc[k] = fmaf(e, cf[k], acc[k]);
                     }
                 }
             }
-        }
+        };
+        const int r_full = r0 + ((r1 - r0) / kHcaBatch) * kHcaBatch;
+        for (int r = r0; r < r_full; r += kHcaBatch) step(r, std::true_type{});
+        if (r_full < r1) step(r_full, std::false_type{});
     }
     if (rg > 0) {
 #pragma unroll
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
         float mm = mx[k];
 #pragma unroll
         for (int g = 0; g < kHcaRowGroups - 1; ++g) mm = fmaxf(mm, sm_m[g][vl][k]);
-        const float ref = (mm > -CUDART_INF_F && mm < CUDART_INF_F) ? mm : 0.f;
+        const float ref = mm;
         float w = ptx::ex2((mx[k] - ref) * kLog2e);
         float ls = l[k] * w, as = acc[k] * w;
 #pragma unroll
