@@ -4,8 +4,8 @@
 #include "../ptx.cuh"
 using namespace dsv4;
 
-// mode: 0 = ss N=64, 1 = ts N=64, 2 = ss N=128, 3 = ts N=128, 4 = ss N=256 (B mn-major), 5 = ts N=256, 6 = ss N=256 k-major
-__global__ void __launch_bounds__(128, 1) k(int mode, int iters, long long* out, int* status, int sep) {
+// M = 128 or 64 rows.  mode: 0 = ss N=64, 1 = ts N=64, 2 = ss N=128, 3 = ts N=128, 4 = ss N=256 (B mn-major), 5 = ts N=256, 6 = ss N=256 k-major
+__global__ void __launch_bounds__(128, 1) k(int mode, int iters, long long* out, int* status, int sep, int M) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     __shared__ uint64_t bar;
@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(128, 1) k(int mode, int iters, long long* out,
         const int N = (mode < 2) ? 64 : (mode < 4 ? 128 : 256);
         const bool ts = mode & 1;
         const bool bmn = (mode == 4 || mode == 5);
-        const uint32_t idesc = ptx::make_idesc_bf16(128, N, false, bmn);
+        const uint32_t idesc = ptx::make_idesc_bf16(M, N, false, bmn);
         const uint32_t hi = ptx::smem_desc_hi(1024);
         const uint32_t a_lo0 = ptx::smem_desc_lo(base, 16);
         const uint32_t b_lo0 = bmn ? ptx::smem_desc_lo(base + 64 * 1024, 8192) : ptx::smem_desc_lo(base + 64 * 1024, 16);
@@ -55,12 +55,12 @@ int main() {
     cudaMallocManaged(&out, 16); cudaMallocManaged(&status, 4); *status = 0;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     const char* names[] = {"ss N=64", "ts N=64", "ss N=128", "ts N=128", "ss N=256 Bmn", "ts N=256 Bmn", "ss N=256 Bk"};
-    for (int sepv : {0, 1}) for (int grid : {148}) for (int mode = 0; mode < 7; ++mode) {
+    for (int M : {128, 64}) for (int sepv : {0, 1}) for (int grid : {148}) for (int mode = 0; mode < 7; ++mode) {
         if (sepv && mode >= 2) continue;
         const int iters = 512;
-        k<<<grid, 128, 200 * 1024>>>(mode, iters, out, status, sepv);
+        k<<<grid, 128, 200 * 1024>>>(mode, iters, out, status, sepv, M);
         cudaError_t e = cudaDeviceSynchronize();
-        printf("sep %d grid %3d %-14s issue %6.1f clk/mma  total %6.1f clk/mma  (err %d status %d)\n", sepv, grid, names[mode],
+        printf("M %3d sep %d grid %3d %-14s issue %6.1f clk/mma  total %6.1f clk/mma  (err %d status %d)\n", M, sepv, grid, names[mode],
                double(out[0]) / iters, double(out[1]) / iters, int(e), *status);
     }
     return 0;
