@@ -82,7 +82,26 @@ cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(2 * head_groups, rows, a.num_splits);
-    if (!(g_dbg & 16) || SRC == kSrcRefPaged) {
+    if ((g_dbg & 32) && !is_ref_layout(SRC)) {
+        if constexpr (!is_ref_layout(SRC)) {
+            // cluster pairs that share the fetch and dequantisation of every tile
+            static bool done[kMaxDevices] = {};
+            constexpr int smem = SmemLayout<NCHUNK>::kTotal;
+            e = ensure_smem(decode_mma_kernel<NCHUNK, SRC, true>, smem, done);
+            if (e != cudaSuccess) return e;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(kNumThreads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;  attr.val.clusterDim.y = 1;  attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            return cudaLaunchKernelEx(&cfg, decode_mma_kernel<NCHUNK, SRC, true>, a);
+        }
+    } else if (!(g_dbg & 16) || SRC == kSrcRefPaged) {
         // product path: each block computes the whole QK product for its half of the value columns
         static bool done[kMaxDevices] = {};
         constexpr int smem = SmemLayout<NCHUNK>::kTotal;

@@ -157,6 +157,10 @@ struct SmemMisc {
     uint64_t valid_mask[2];   // per stage: bit t = entry t of the tile takes part in the softmax
     uint32_t tmem_base;
     uint32_t pad;
+    // cluster-pair kernel: per stage, byte i = 4-bit mask of tile rows 4 i .. 4 i + 3 (written by the
+    // loader warp that owns them, in either block of the pair)
+    alignas(16) uint8_t valid_bytes[2][16];
+    uint64_t bar_loc[2][2];   // [stage][group]: this block's loader warps have written their half of the group
 };
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int code, int role, int tile) {
@@ -218,11 +222,15 @@ __device__ __forceinline__ void dequant4_f16(uint32_t w, __half2 scale2, uint32_
 // contiguous bytes: measured on this part, an SM pulls records about 1.6 times
 // faster in this shape than with 64 bytes per entry per instruction, and the
 // record fetch is what the loader warps spend most of their time on.
-template <int SRC>
+//
+// G = 2 groups (8 entries per warp) in the ordinary kernel; G = 1 (4 entries per warp) when the
+// two blocks of a cluster pair share the work: each block then fetches and dequantises half of
+// every tile and forwards it to the other block.
+template <int SRC, int G = 2>
 struct LoaderRegs {
-    uint4 lat[2][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
-    uint4 rope[2];           // [group]: RoPE 16-byte column lane%8 of that entry
-    uint32_t sc[2][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
+    uint4 lat[G][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
+    uint4 rope[G];           // [group]: RoPE 16-byte column lane%8 of that entry
+    uint32_t sc[G][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
     uint32_t vmask;          // bit i = entry i of this warp takes part (same in all lanes)
 };
 
@@ -307,24 +315,24 @@ __device__ __forceinline__ void loader_resolve2(const DecodeArgs& a, int b, int 
 
 // Warp-wide: resolve the 8 entries [v0, v0+8) (lanes 0..7), return the key in
 // those lanes and the valid mask in all lanes.
-template <int SRC>
+template <int SRC, int E = 8>
 __device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeArgs& a, int b, int n, int v0, int lane,
                                                                   int n_tok, int kv_len_n, uint32_t& vmask) {
     bool valid = false;
     unsigned long long key = 0;
-    if (lane < 8) key = loader_resolve<SRC>(a, b, n, v0 + lane, n_tok, kv_len_n, valid);
+    if (lane < E) key = loader_resolve<SRC>(a, b, n, v0 + lane, n_tok, kv_len_n, valid);
     vmask = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
     return key;
 }
 
 // Issue the loads of one tile for this lane's two entries (keys held by lanes 0..7).
-template <int SRC>
+template <int SRC, int G>
 __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
-                                             LoaderRegs<SRC>& r) {
+                                             LoaderRegs<SRC, G>& r) {
     r.vmask = vmask;
     const int piece = lane & 7;
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
+    for (int g = 0; g < G; ++g) {
         const int i = 4 * g + (lane >> 3);
         const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
         if (!((vmask >> i) & 1u)) continue;
@@ -396,13 +404,13 @@ __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint3
 // One store instruction writes 4 rows x 2 chunks x 4 column positions, arranged
 // (see the end of the function) so that it needs as few shared-memory wavefronts
 // as 512 bytes can: four.
-template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r, int j) {
+template <int NCHUNK, int SRC, int G>
+__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC, G>& r, int j) {
     const uint32_t piece = uint32_t(lane & 7);
     const uint32_t c = 2u * uint32_t(j) + (piece >> 2);        // this lane's chunk
     const uint32_t p = piece & 3u;                             // 16 latent bytes -> 16-byte columns 2p, 2p+1
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
+    for (int g = 0; g < G; ++g) {
         const int i = 4 * g + (lane >> 3);
         const int t = t0 + i;
         const bool valid = (r.vmask >> i) & 1u;
@@ -447,11 +455,11 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
 }
 
 // The RoPE tail (chunk NCHUNK-1, a plain copy): 4 rows x 8 columns per store instruction.
-template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r) {
+template <int NCHUNK, int SRC, int G>
+__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC, G>& r) {
     const uint32_t piece = uint32_t(lane & 7);
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
+    for (int g = 0; g < G; ++g) {
         const int i = 4 * g + (lane >> 3);
         const int t = t0 + i;
         const bool valid = (r.vmask >> i) & 1u;
@@ -505,9 +513,18 @@ __device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint3
     }
 }
 
-template <int NCHUNK, int SRC>
+// PAIR: launched as clusters of two blocks along x - the two blocks of a row and head group (the two
+// halves of the value columns).  Both need the whole dequantised tile, so each fetches and
+// dequantises half of its entries into its own stage, and a forwarder warp sends that half on to
+// the same place in the other block's stage by bulk copies through distributed shared memory;
+// everything after that is as in the ordinary kernel.  Bit-identical results; measured slower
+// than the ordinary kernel (the copy sits in the two-stage ring), so it is a selectable variant.
+template <int NCHUNK, int SRC, bool PAIR = false>
 __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid_constant__ DecodeArgs a) {
+    static_assert(!PAIR || !is_ref_layout(SRC), "the cluster-pair variant is written for the packed layout");
     using L = SmemLayout<NCHUNK>;
+    constexpr int G = PAIR ? 1 : 2;            // groups of 4 entries per loader warp and tile
+    constexpr int E = 4 * G;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -523,6 +540,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     const int n = blockIdx.y;                // row = b * s_q + query token
     const int split = blockIdx.z;
     const int b = n / a.s_q;
+    // the other block of the pair sees this block's shared memory at (address + peer_delta)
+    const uint32_t peer_delta = PAIR ? ptx::mapa(smem_base, uint32_t(half ^ 1)) - smem_base : 0u;
 
     // ── this block's tile range ──
     int n_tok, kv_len_n;
@@ -558,14 +577,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         trace_block(a, 0);
         for (int st = 0; st < 2; ++st) {
             for (int g = 0; g < kNumKvGroups; ++g)
-                ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps);
-            ptx::mbar_init(bar_kv_free + 8 * st, 1);
+                ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps + (PAIR ? 1 : 0));   // + the other block's forwarder
+            for (int g = 0; g < kNumKvGroups; ++g) ptx::mbar_init(ptx::smem_u32(&misc->bar_loc[st][g]), kNumLoaderWarps);
+            ptx::mbar_init(bar_kv_free + 8 * st, PAIR ? 2 : 1);     // PV commits of both blocks: a stage is refilled in both at once
             ptx::mbar_init(bar_s_full + 8 * st, 1);
             ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
         }
         ptx::mbar_init(bar_o_full, 1);
         ptx::mbar_init(bar_q_full, 1);
-        ptx::mbar_init(bar_q_ready, kNumSoftmaxWarps + kNumLoaderWarps);
+        ptx::mbar_init(bar_q_ready, (PAIR ? 2 : 1) * (kNumSoftmaxWarps + kNumLoaderWarps));
         ptx::fence_mbar_init();
         if (ntiles > 0) {
             // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
@@ -586,10 +606,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
 
     // Block-wide rendezvous.  Every role runs the same number of them (one before the
     // main loops, one at the exit), each from its own branch.
+    // (PAIR: a rendezvous of both blocks - nothing is written to, and no barrier is arrived on, in
+    // the other block before its barriers are initialised.)
     auto block_sync = [&]() {
         ptx::tc_fence_before_sync();
-        __syncthreads();
+        if constexpr (PAIR) ptx::cluster_sync(); else __syncthreads();
         ptx::tc_fence_after_sync();
+    };
+    // Q staging released / Q in tensor memory: in a pair the other block's loaders write into this
+    // block's stage 1 as well, so they are told too.
+    auto arrive_q_ready = [&]() {
+        ptx::mbar_arrive(bar_q_ready);
+        if constexpr (PAIR) ptx::mbar_arrive_cluster(bar_q_ready + peer_delta);
+    };
+    auto wait_q_ready = [&]() {
+        return PAIR ? ptx::mbar_wait_cluster(bar_q_ready, 0u, kWaitTimeoutNs) : ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs);
     };
 
     if (warp >= kFirstLoaderWarp && warp < kMmaWarp) {
@@ -599,8 +630,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         // records they name are pulled into L2 at that point.  The larger register allowance
         // holds for this branch only.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kLoaderRegs));
-        const int lw = warp - kFirstLoaderWarp;      // this warp's 8 entries: tile rows lw*8 .. lw*8+7
-        LoaderRegs<SRC> regs_a, regs_b;
+        const int lw = warp - kFirstLoaderWarp;
+        const int row0 = PAIR ? 32 * half + 4 * lw : 8 * lw;      // this warp's E entries: tile rows row0 .. row0+E-1
+        LoaderRegs<SRC, G> regs_a, regs_b;
         // keys of the tiles two and three ahead of the one being stored (records already
         // pulled into L2), and of the tile four ahead (resolved, not yet prefetched)
         unsigned long long key1 = 0, key2 = 0, key3 = 0, key4 = 0;
@@ -613,16 +645,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             bool valid = false, valid4 = false;
             const int which = lane >> 3;
             unsigned long long key, k4;
-            loader_resolve2<SRC>(a, b, n, (tile0 + which) * kTileN + lw * 8 + (lane & 7), (which < ntiles) ? n_tok : 0,
-                                 (tile0 + 4) * kTileN + lw * 8 + (lane & 7), (4 < ntiles && lane < 8) ? n_tok : 0,
+            loader_resolve2<SRC>(a, b, n, (tile0 + which) * kTileN + row0 + (lane & 7), (which < ntiles && (lane & 7) < E) ? n_tok : 0,
+                                 (tile0 + 4) * kTileN + row0 + (lane & 7), (4 < ntiles && lane < E) ? n_tok : 0,
                                  kv_len_n, key, valid, k4, valid4);
             const uint32_t bal = __ballot_sync(0xFFFFFFFFu, valid);
             vm4 = __ballot_sync(0xFFFFFFFFu, valid4) & 0xFFu;
             key4 = k4;
             if constexpr (SRC == kSrcCsa) {
                 // the index-list values of tile 5 (lanes 0-7), on their way one step before they are needed
-                const int v5 = (tile0 + 5) * kTileN + lw * 8 + lane;
-                if (lane < 8 && 5 < ntiles && v5 < n_tok) e_ahead = __ldg(a.indices + int64_t(n) * a.topk + v5);
+                const int v5 = (tile0 + 5) * kTileN + row0 + lane;
+                if (lane < E && 5 < ntiles && v5 < n_tok) e_ahead = __ldg(a.indices + int64_t(n) * a.topk + v5);
             }
             if (lw == 0 && lane == 0) trace_mark(a, 3, 5);
             vm2 = (bal >> 16) & 0xFFu;
@@ -658,13 +690,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     ptx::tc_fence_before_sync();
                 }
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_q_ready);     // also after a time-out, so that nobody waits for this warp
+                if (lane == 0) arrive_q_ready();     // also after a time-out, so that nobody waits for this warp
             }
-            auto tile_step = [&](LoaderRegs<SRC>& regs, int it) {
+            auto tile_step = [&](LoaderRegs<SRC, G>& regs, int it) {
                 const int st = it & 1;
                 if (it == 1) {
                     // stage 1 doubles as the Q staging area until the copy to tensor memory is done
-                    const bool w = ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs);
+                    const bool w = wait_q_ready();
                     if (!__all_sync(0xFFFFFFFFu, w)) {
                         report_timeout(a.status, kStatusWaitQ, 2, tile0 + it);
                         lok = false;
@@ -686,21 +718,28 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     // its records into L2 (using it earlier would stall on the block-table load)
                     loader_prefetch_l2<SRC>(key4, vm4, lane);
                 }
-                if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
+                if constexpr (PAIR) {
+                    if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_bytes[st][0])[8 * half + lw] = uint8_t(regs.vmask);
+                } else {
+                    if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
+                }
                 // in two groups (chunks 0-3, then the rest with the RoPE tail), so that the QK MMAs of this tile
                 // start while it is still being written; one proxy fence and one arrival per group
                 const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
                 auto group_done = [&](int g) {
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * g);
+                    if (lane == 0) {
+                        ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * g);
+                        if constexpr (PAIR) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][g]));   // the forwarder takes it from here
+                    }
                 };
-                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 0);
-                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 1);
+                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 0);
+                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 1);
                 group_done(0);
-                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 2);
-                loader_store_span<NCHUNK, SRC>(kv_st, lw * 8, lane, regs, 3);
-                loader_store_rope<NCHUNK, SRC>(kv_st, lw * 8, lane, regs);
+                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 2);
+                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 3);
+                loader_store_rope<NCHUNK, SRC, G>(kv_st, row0, lane, regs);
                 group_done(1);
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
                 if (it == 0) {
@@ -727,10 +766,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                     vm4 = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
                     key4 = key;
-                    const int v6 = (tile0 + it + 6) * kTileN + lw * 8 + lane;
-                    e_ahead = (lane < 8 && it + 6 < ntiles && v6 < n_tok) ? __ldg(a.indices + int64_t(n) * a.topk + v6) : -1;
+                    const int v6 = (tile0 + it + 6) * kTileN + row0 + lane;
+                    e_ahead = (lane < E && it + 6 < ntiles && v6 < n_tok) ? __ldg(a.indices + int64_t(n) * a.topk + v6) : -1;
                 } else {
-                    key4 = loader_resolve_warp<SRC>(a, b, n, (tile0 + it + 5) * kTileN + lw * 8, lane,
+                    key4 = loader_resolve_warp<SRC, E>(a, b, n, (tile0 + it + 5) * kTileN + row0, lane,
                                                     (it + 5 < ntiles) ? n_tok : 0, kv_len_n, vm4);
                 }
             };
@@ -757,7 +796,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                                                             : ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 bool ok = true;
                 // Q: shared-memory chunks landed (TMA) and tensor-memory chunks copied
-                if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs)) {
+                if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !wait_q_ready()) {
                     report_timeout(a.status, kStatusWaitQ, 1, tile0);
                     ok = false;
                 }
@@ -812,6 +851,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         ptx::mma_bf16_ts2(tmem + kTmemO, p_tmem + k * 8, v_lo + uint32_t((k * 2048) >> 4), kDescHi, idesc_pv,
                                           (it | k) ? 1u : 0u);
                     ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
+                    if constexpr (PAIR) ptx::mma_commit_cluster(bar_kv_free + 8 * st + peer_delta);   // the other block's forwarder copies into it
                     trace_mark(a, 1, 512 + 4 * it + 3);
                 };
                 // S(t) runs up to one tile ahead of O += P(t) . V(t), so that the softmax of
@@ -828,7 +868,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         ++pv_next;
                         progress = true;
                     } else if (qk_tile < ntiles && qk_tile <= pv_next + 1 &&
-                               ptx::mbar_test_wait(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u)) {
+                               (PAIR ? ptx::mbar_test_wait_cluster(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u)
+                                     : ptx::mbar_test_wait(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u))) {
                         ptx::tc_fence_after_sync();
                         if (qk_chunk == 0) trace_mark(a, 1, 2 * qk_tile);
                         issue_qk_group(qk_tile, qk_chunk);
@@ -851,6 +892,41 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                 }
                 if (ok) ptx::mma_commit(bar_o_full);
+            }
+            __syncwarp();
+        } else if (PAIR && ntiles > 0 && warp == kMmaWarp + 1) {
+            // ───────────── forwarder (cluster pair): this block's half of every group, once its loader
+            // warps have written it, goes to the same place in the other block by bulk copies that
+            // complete on the other block's kv_full barrier (no load/store-unit work, no registers)
+            if (lane == 0) {
+                constexpr uint32_t kHalfChunk = uint32_t(kKvChunkBytes) / 2;       // 32 rows x 128 bytes
+                for (int it = 0; it < ntiles; ++it) {
+                    const int st = it & 1;
+                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes + uint32_t(half) * kHalfChunk;
+                    bool fok = true;
+                    for (int g = 0; g < kNumKvGroups && fok; ++g) {
+                        if (!ptx::mbar_wait(ptx::smem_u32(&misc->bar_loc[st][g]), uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
+                            report_timeout(a.status, kStatusWaitKvFull, 3, tile0 + it);
+                            fok = false;
+                            break;
+                        }
+                        const uint32_t rbar = bar_kv_full + 80 * st + 8 * g + peer_delta;
+                        if (g == 0) {
+                            // this block's eight 4-bit validity masks of the tile
+                            const unsigned long long vb = *reinterpret_cast<volatile unsigned long long*>(&misc->valid_bytes[st][8 * half]);
+                            asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(ptx::smem_u32(&misc->valid_bytes[st][8 * half]) + peer_delta), "l"(vb) : "memory");
+                        }
+                        const int c0 = g == 0 ? 0 : 4, c1 = g == 0 ? 4 : NCHUNK;
+                        asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(rbar),
+                                     "r"(uint32_t(c1 - c0) * kHalfChunk) : "memory");
+                        for (int c = c0; c < c1; ++c) {
+                            const uint32_t src = kv_st + uint32_t(c) * kKvChunkBytes;
+                            asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(src + peer_delta),
+                                         "r"(src), "r"(kHalfChunk), "r"(rbar) : "memory");
+                        }
+                    }
+                    if (!fok) break;
+                }
             }
             __syncwarp();
         }
@@ -879,7 +955,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_q_ready);
+                if (lane == 0) arrive_q_ready();
             }
         }
         if (tid == 0) trace_mark(a, 3, 1);
@@ -904,7 +980,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 ptx::tmem_ld32(s_tmem, s0);
                 ptx::tmem_ld32(s_tmem + 32, s1);
                 ptx::tmem_wait_ld();
-                const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
+                uint64_t vmask;
+                if constexpr (PAIR) {
+                    // sixteen 4-bit masks, one per loader warp of the pair
+                    const uint4 vb = ptx::lds_v4(ptx::smem_u32(&misc->valid_bytes[st][0]));
+                    if ((vb.x & vb.y & vb.z & vb.w) == 0x0F0F0F0Fu) {
+                        vmask = ~0ull;
+                    } else {
+                        auto nib = [](uint32_t w) { return (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u); };
+                        vmask = uint64_t(nib(vb.x) | (nib(vb.y) << 16)) | (uint64_t(nib(vb.z) | (nib(vb.w) << 16)) << 32);
+                    }
+                } else {
+                    vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
+                }
                 if (vmask != ~0ull) {
                     // entries that do not take part (padding, the end of the list): -inf before the scale
                     const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
@@ -1106,8 +1194,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     }
 
     // ── common exit: every thread gets here, with or without an error ──
+    // (PAIR: both blocks, so that neither leaves while the other may still arrive on its barriers)
     ptx::tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) ptx::cluster_sync(); else __syncthreads();
     if (tid == 0) { trace_mark(a, 3, 3);  trace_block(a, 1); }
     if (warp == kMmaWarp) {
         ptx::tc_fence_after_sync();

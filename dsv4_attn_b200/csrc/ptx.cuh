@@ -111,6 +111,20 @@ __device__ __forceinline__ void sts_cluster_v4(uint32_t caddr, uint4 v) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cbar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cbar) : "memory");
 }
+// Non-blocking probe of a local barrier whose arrivals may come from another block.
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -303,6 +317,12 @@ __device__ __forceinline__ void mma_bf16_ts2(uint32_t d_tmem, uint32_t a_tmem, u
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
+}
+
+// The same for a barrier given by its cluster-wide address (mapa): it may live in the other
+// block of a cluster pair.
+__device__ __forceinline__ void mma_commit_cluster(uint32_t cbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cbar) : "memory");
 }
 
 // ── TMA ─────────────────────────────────────────────────────────────────
