@@ -35,8 +35,10 @@ constexpr int kDvHalf = 256;           // value columns per block (MMA N of PV)
 constexpr int kQChunkBytes = 128 * 128;   // 128 heads x 64 bf16
 constexpr int kKvChunkBytes = kTileN * 128;  // 64 entries x 64 bf16
 // Warp roles, four warpgroups of four warps.  Warps 0-3: softmax + epilogue.
-// Warps 4-11: loaders.  Warp 12: MMA issue and tensor-memory allocation; warps
-// 13-15 only take part in the block-wide barriers.  All 16 warps start with 128
+// Warps 4-11: loaders.  Warp 12: issue of the S = Q.K^T MMAs and tensor-memory allocation;
+// warp 13: issue of the O += P.V MMAs (its own thread, so that a ready P never waits for the
+// other thread to finish issuing a group: an issuing thread is held while the tensor pipe's
+// short queue is full); warps 14-15 only take part in the block-wide barriers.  All 16 warps start with 128
 // registers (the whole register file); the last warpgroup gives most of its
 // share back and the loaders take it, so that they can hold two tiles of cache
 // entries in flight.  setmaxnreg.inc waits for registers without a time limit,
@@ -792,8 +794,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             if (lane == 0) {
                 constexpr uint32_t idesc_qk = use_f16(SRC) ? ptx::make_idesc_f16(128, kTileN, false, false)
                                                             : ptx::make_idesc_bf16(128, kTileN, false, false);
-                constexpr uint32_t idesc_pv = use_f16(SRC) ? ptx::make_idesc_f16(128, kDvHalf, false, true)
-                                                            : ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 bool ok = true;
                 // Q: shared-memory chunks landed (TMA) and tensor-memory chunks copied
                 if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !wait_q_ready()) {
@@ -837,8 +837,42 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 4>{});
                     else issue_qk_range(it, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK>{});
                 };
-                auto issue_pv = [&](int it) {
+                // This thread issues only S = Q.K^T, group by group as the loaders deliver them; O += P.V is
+                // issued by a thread of the next warp.  No order is needed between the two streams beyond
+                // what the barriers already give: S(t+2) and the refill of stage t&1 both follow the
+                // kv_free arrival of P(t).V(t), and P(t) follows S(t).  A P that becomes ready then never
+                // waits for this thread to finish issuing a group.
+                for (int it = 0; it < ntiles && ok; ++it) {
                     const int st = it & 1;
+                    for (int g = 0; g < kNumGroups; ++g) {
+                        const uint32_t bar = bar_kv_full + 80 * st + 8 * g, par = uint32_t(it >> 1) & 1u;
+                        if (!(PAIR ? ptx::mbar_wait_cluster(bar, par, kWaitTimeoutNs) : ptx::mbar_wait(bar, par, kWaitTimeoutNs))) {
+                            report_timeout(a.status, kStatusWaitKvFull, 1, tile0 + it);
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        if (g == 0) trace_mark(a, 1, 2 * it);
+                        issue_qk_group(it, g);
+                    }
+                    if (ok) ptx::mma_commit(bar_s_full + 8 * st);
+                }
+            }
+            __syncwarp();
+        } else if (ntiles > 0 && warp == kMmaWarp + 1) {
+            // ───────────── O += P . V issue (one thread) ─────────────
+            if (lane == 0) {
+                constexpr uint32_t idesc_pv = use_f16(SRC) ? ptx::make_idesc_f16(128, kDvHalf, false, true)
+                                                            : ptx::make_idesc_bf16(128, kDvHalf, false, true);
+                constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);
+                bool ok = true;
+                for (int it = 0; it < ntiles; ++it) {
+                    const int st = it & 1;
+                    if (!ptx::mbar_wait(bar_p_full + 8 * st, uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
+                        report_timeout(a.status, kStatusWaitPFull, 1, tile0 + it);
+                        ok = false;
+                        break;
+                    }
                     const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
                     ptx::tc_fence_after_sync();
                     trace_mark(a, 1, 2 * it + 1);
@@ -853,48 +887,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
                     if constexpr (PAIR) ptx::mma_commit_cluster(bar_kv_free + 8 * st + peer_delta);   // the other block's forwarder copies into it
                     trace_mark(a, 1, 512 + 4 * it + 3);
-                };
-                // S(t) runs up to one tile ahead of O += P(t) . V(t), so that the softmax of
-                // tile t overlaps the QK MMAs of tile t+1.  Between the QK groups a ready P goes
-                // first, so that its stage is handed back to the loaders early.
-                int qk_tile = 0, qk_chunk = 0, pv_next = 0;
-                uint64_t t_last = 0;
-                uint32_t polls = 0;
-                while (ok && pv_next < ntiles) {
-                    bool progress = false;
-                    if (pv_next < qk_tile &&
-                        ptx::mbar_test_wait(bar_p_full + 8 * (pv_next & 1), uint32_t(pv_next >> 1) & 1u)) {
-                        issue_pv(pv_next);
-                        ++pv_next;
-                        progress = true;
-                    } else if (qk_tile < ntiles && qk_tile <= pv_next + 1 &&
-                               (PAIR ? ptx::mbar_test_wait_cluster(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u)
-                                     : ptx::mbar_test_wait(bar_kv_full + 80 * (qk_tile & 1) + 8 * qk_chunk, uint32_t(qk_tile >> 1) & 1u))) {
-                        ptx::tc_fence_after_sync();
-                        if (qk_chunk == 0) trace_mark(a, 1, 2 * qk_tile);
-                        issue_qk_group(qk_tile, qk_chunk);
-                        if (++qk_chunk == kNumGroups) {
-                            ptx::mma_commit(bar_s_full + 8 * (qk_tile & 1));
-                            qk_chunk = 0;
-                            ++qk_tile;
-                        }
-                        progress = true;
-                    }
-                    if (progress) {
-                        polls = 0;
-                    } else {
-                        if (polls == 0) t_last = ptx::globaltimer_ns();
-                        if ((++polls & 255u) != 0u || ptx::globaltimer_ns() - t_last <= kWaitTimeoutNs) continue;
-                        report_timeout(a.status, (pv_next < qk_tile) ? kStatusWaitPFull : kStatusWaitKvFull, 1,
-                                       tile0 + pv_next);
-                        ok = false;
-                        break;
-                    }
                 }
                 if (ok) ptx::mma_commit(bar_o_full);
             }
             __syncwarp();
-        } else if (PAIR && ntiles > 0 && warp == kMmaWarp + 1) {
+        } else if (PAIR && ntiles > 0 && warp == kMmaWarp + 2) {
             // ───────────── forwarder (cluster pair): this block's half of every group, once its loader
             // warps have written it, goes to the same place in the other block by bulk copies that
             // complete on the other block's kv_full barrier (no load/store-unit work, no registers)
