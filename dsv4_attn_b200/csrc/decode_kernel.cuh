@@ -162,7 +162,7 @@ struct SmemMisc {
     // cluster-pair kernel: per stage, byte i = 4-bit mask of tile rows 4 i .. 4 i + 3 (written by the
     // loader warp that owns them, in either block of the pair)
     alignas(16) uint8_t valid_bytes[2][16];
-    uint64_t bar_loc[2][2];   // [stage][group]: this block's loader warps have written their half of the group
+    uint64_t bar_loc[2][4];   // [stage][span]: this block's loader warps have written their half of chunks 2 span, 2 span + 1 (span 3: and the RoPE tail)
 };
 
 __device__ __forceinline__ void report_timeout(int32_t* status, int code, int role, int tile) {
@@ -580,7 +580,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         for (int st = 0; st < 2; ++st) {
             for (int g = 0; g < kNumKvGroups; ++g)
                 ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps + (PAIR ? 1 : 0));   // + the other block's forwarder
-            for (int g = 0; g < kNumKvGroups; ++g) ptx::mbar_init(ptx::smem_u32(&misc->bar_loc[st][g]), kNumLoaderWarps);
+            for (int j = 0; j < 4; ++j) ptx::mbar_init(ptx::smem_u32(&misc->bar_loc[st][j]), kNumLoaderWarps);
             ptx::mbar_init(bar_kv_free + 8 * st, PAIR ? 2 : 1);     // PV commits of both blocks: a stage is refilled in both at once
             ptx::mbar_init(bar_s_full + 8 * st, 1);
             ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
@@ -733,13 +733,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     __syncwarp();
                     if (lane == 0) {
                         ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * g);
-                        if constexpr (PAIR) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][g]));   // the forwarder takes it from here
+                        if constexpr (PAIR) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][2 * g + 1]));   // the forwarder takes it from here
+                    }
+                };
+                // (pair: the forwarder is told span by span, so that its copies run beside the stores)
+                auto span_done = [&](int j) {
+                    if constexpr (PAIR) {
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][j]));
                     }
                 };
                 loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 0);
+                span_done(0);
                 loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 1);
                 group_done(0);
                 loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 2);
+                span_done(2);
                 loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 3);
                 loader_store_rope<NCHUNK, SRC, G>(kv_st, row0, lane, regs);
                 group_done(1);
@@ -901,21 +911,25 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     const int st = it & 1;
                     const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes + uint32_t(half) * kHalfChunk;
                     bool fok = true;
-                    for (int g = 0; g < kNumKvGroups && fok; ++g) {
-                        if (!ptx::mbar_wait(ptx::smem_u32(&misc->bar_loc[st][g]), uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
+                    for (int j = 0; j < 4 && fok; ++j) {
+                        if (!ptx::mbar_wait(ptx::smem_u32(&misc->bar_loc[st][j]), uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
                             report_timeout(a.status, kStatusWaitKvFull, 3, tile0 + it);
                             fok = false;
                             break;
                         }
+                        const int g = j >> 1;
                         const uint32_t rbar = bar_kv_full + 80 * st + 8 * g + peer_delta;
-                        if (g == 0) {
+                        if (j == 0) {
                             // this block's eight 4-bit validity masks of the tile
                             const unsigned long long vb = *reinterpret_cast<volatile unsigned long long*>(&misc->valid_bytes[st][8 * half]);
                             asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(ptx::smem_u32(&misc->valid_bytes[st][8 * half]) + peer_delta), "l"(vb) : "memory");
                         }
-                        const int c0 = g == 0 ? 0 : 4, c1 = g == 0 ? 4 : NCHUNK;
-                        asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(rbar),
-                                     "r"(uint32_t(c1 - c0) * kHalfChunk) : "memory");
+                        if ((j & 1) == 0) {
+                            // one arrival per group, announcing all of the group's bytes
+                            asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(rbar),
+                                         "r"(uint32_t(g == 0 ? 4 : NCHUNK - 4) * kHalfChunk) : "memory");
+                        }
+                        const int c0 = 2 * j, c1 = j == 3 ? NCHUNK : 2 * j + 2;
                         for (int c = c0; c < c1; ++c) {
                             const uint32_t src = kv_st + uint32_t(c) * kKvChunkBytes;
                             asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(src + peer_delta),
