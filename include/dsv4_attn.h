@@ -448,7 +448,10 @@ void dsv4_debug_set_trace(void* device_buffer);
 /* Profiling aid: pipeline experiment switches for the next launches (0 = product
  * behaviour).  bit1: no L2 prefetch of the cache entries; bit4: use the cluster-pair
  * kernel (two blocks split the query/key columns and exchange halves of S through
- * distributed shared memory) instead of the default kernel.  No counterpart in the reference. */
+ * distributed shared memory) instead of the default kernel; bit5 (packed layout only): the two
+ * blocks of a row and head group run as a cluster pair in which each fetches and dequantises half
+ * of every tile and forwards it to the other (results bit-identical to the default kernel).
+ * No counterpart in the reference. */
 void dsv4_debug_set_flags(int flags);
 
 /* Library identification: (major << 16) | minor. */
