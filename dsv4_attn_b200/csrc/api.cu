@@ -458,13 +458,13 @@ extern "C" int dsv4_csa_compress_reduce_fwd(const Dsv4CsaCompressReduceParams* p
                      aligned(p->B_b, 16) && aligned(p->out, 16);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int64_t items = int64_t(a.B) * a.n_blocks * (vec ? a.c_out / 8 : a.c_out);
+    const int64_t items = int64_t(a.B) * a.n_blocks * (vec ? a.c_out / 4 : a.c_out);
     const int64_t want = (items + kCompressThreads - 1) / kCompressThreads;
-    // at most 8 blocks per SM (4 resident waves); beyond that the grid-stride loop takes over
+    // at most 8 blocks per SM (two waves of the 4 resident ones); beyond that the grid-stride loop takes over
     const int64_t cap = int64_t(sms) * 8;
     const int blocks = int(want < cap ? (want > 0 ? want : 1) : cap);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (vec) compress_reduce_kernel<4, 8><<<blocks, kCompressThreads, 0, s>>>(a);
+    if (vec) compress_reduce_kernel<4, 4><<<blocks, kCompressThreads, 0, s>>>(a);
     else compress_reduce_kernel<4, 1><<<blocks, kCompressThreads, 0, s>>>(a);
     return int(cudaGetLastError());
 }
