@@ -545,23 +545,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     // the other block of the pair sees this block's shared memory at (address + peer_delta)
     const uint32_t peer_delta = PAIR ? ptx::mapa(smem_base, uint32_t(half ^ 1)) - smem_base : 0u;
 
-    // ── this block's tile range ──
-    int n_tok, kv_len_n;
+    // The per-row lengths are requested here and used only after the set-up below: the Q load and the
+    // barrier initialisation do not wait for them.
+    int raw_len0 = 0, raw_len1 = 0;
     if constexpr (SRC == kSrcCsa) {
-        n_tok = (a.topk_len != nullptr) ? min(max(__ldg(a.topk_len + n), 0), a.topk) : a.topk;
-        kv_len_n = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
+        raw_len0 = (a.topk_len != nullptr) ? __ldg(a.topk_len + n) : a.topk;
+        raw_len1 = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
     } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
-        kv_len_n = max(__ldg(a.kv_len + n), 0);
-        n_tok = kv_len_n + max(__ldg(a.win_len + n), 0);
-    } else {
-        kv_len_n = a.ref_m_cur;
-        n_tok = a.ref_m_cur + a.ref_swa_len;
+        raw_len0 = __ldg(a.kv_len + n);
+        raw_len1 = __ldg(a.win_len + n);
     }
-    const int tiles_total = (n_tok + kTileN - 1) / kTileN;
-    const int tiles_per_split = (tiles_total + a.num_splits - 1) / a.num_splits;
-    const int tile0 = min(split * tiles_per_split, tiles_total);
-    const int tile1 = min(tile0 + tiles_per_split, tiles_total);
-    const int ntiles = tile1 - tile0;
+    if (tid == 32) {
+        // first link of the loaders' chains of dependent loads (index list -> block table -> entries): into L2 now
+        if constexpr (SRC == kSrcCsa) {
+            const int32_t* idx = a.indices + int64_t(n) * a.topk;
+            const int lines = min((a.topk * 4 + 127) / 128, 8);
+            for (int l = 0; l < lines; ++l) ptx::prefetch_l2(reinterpret_cast<const uint8_t*>(idx) + 128 * l);
+        }
+        if constexpr (SRC == kSrcCsa || SRC == kSrcHca || SRC == kSrcRefPaged)
+            ptx::prefetch_l2(a.block_table + int64_t(b) * a.max_pages);
+    }
 
     const uint32_t v_off = uint32_t(half ? 4 : 0) * kKvChunkBytes;   // this block's value columns inside a stage
 
@@ -589,7 +592,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         ptx::mbar_init(bar_q_full, 1);
         ptx::mbar_init(bar_q_ready, (PAIR ? 2 : 1) * (kNumSoftmaxWarps + kNumLoaderWarps));
         ptx::fence_mbar_init();
-        if (ntiles > 0) {
+        {
+            // (issued whether or not this block has tiles: a block without tiles waits for it before it leaves)
             // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
             // the swizzled operand layout: chunks >= kQTmemChunks at their final place, the others
             // in the staging area.  Rows past the end of Q read as zero; rows of a following
@@ -605,6 +609,24 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
         trace_mark(a, 3, 10);
     }
+
+    // ── this block's tile range ──
+    int n_tok, kv_len_n;
+    if constexpr (SRC == kSrcCsa) {
+        n_tok = min(max(raw_len0, 0), a.topk);
+        kv_len_n = raw_len1;
+    } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
+        kv_len_n = max(raw_len0, 0);
+        n_tok = kv_len_n + max(raw_len1, 0);
+    } else {
+        kv_len_n = a.ref_m_cur;
+        n_tok = a.ref_m_cur + a.ref_swa_len;
+    }
+    const int tiles_total = (n_tok + kTileN - 1) / kTileN;
+    const int tiles_per_split = (tiles_total + a.num_splits - 1) / a.num_splits;
+    const int tile0 = min(split * tiles_per_split, tiles_total);
+    const int tile1 = min(tile0 + tiles_per_split, tiles_total);
+    const int ntiles = tile1 - tile0;
 
     // Block-wide rendezvous.  Every role runs the same number of them (one before the
     // main loops, one at the exit), each from its own branch.
@@ -1172,7 +1194,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         }
     }
     if (ntiles <= 0) {
-        // Nothing to attend to in this split: zero output, LSE = -inf.
+        // Nothing to attend to in this split: zero output, LSE = -inf.  The Q tile is on its way into
+        // shared memory all the same and must have landed before the block leaves.
+        if (tid == 0 && !ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs)) report_timeout(a.status, kStatusWaitQ, 3, tile0);
         const bool final_out = a.num_splits == 1;
         for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumThreads) {
             const int r = i / (kDvHalf / 8), v = i % (kDvHalf / 8);
