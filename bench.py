@@ -265,16 +265,17 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
     """Same metric through the public API with HOST buffers: every step copies its inputs
     (q and the per-step index / length tensors) from pinned host memory, runs the decode,
     and reads the result (out, lse) back to pinned host memory.  The three stages run on
-    their own streams (copy-in on two, compute, copy-out) chained by events, so that the copies of
+    their own streams (copy-in, compute, copy-out) chained by events, so that the copies of
     neighbouring steps overlap the compute, as a serving engine would run them; step i
     works on instance i mod R (its own KV pool, staging and output buffers).  Returns
     (total ms of the K steps, h2d bytes per step, d2h bytes per step)."""
     import torch
     R = len(insts)
     dev = insts[0][0].q.device
-    # the query upload is split over two copy-in streams: one stream alone reaches about half of
-    # the host link's bandwidth on this machine (29 against 53 GB/s measured for 9.4 MB)
-    s_in, s_in2, s_c, s_out = (torch.cuda.Stream(dev) for _ in range(4))
+    # One copy-in stream: back-to-back uploads on one stream reach the host link's rate (52 GB/s measured
+    # for 9.4 MB pieces), and while results are read back at the same time a split upload was slower
+    # (270 against 250 us per step; copies alone: 241 against 211 us per step for both directions).
+    s_in, s_c, s_out = (torch.cuda.Stream(dev) for _ in range(3))
     main = torch.cuda.current_stream(dev)
     slots = []
     for w, fn, _ in insts:
@@ -289,10 +290,7 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
         out, lse = fn()
         ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
         hl = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
-        hqf, dqf = hq.view(-1), dq.view(-1)
-        cut = (hqf.numel() // 2 + 127) // 128 * 128
-        slots.append(dict(fn=fn, hq=hq, dq=dq, hq_a=hqf[:cut], dq_a=dqf[:cut], hq_b=hqf[cut:], dq_b=dqf[cut:],
-                          h1=h1, d1=d1, h2=h2, d2=d2, ho=ho, hl=hl, ev_in=torch.cuda.Event(), ev_in2=torch.cuda.Event(),
+        slots.append(dict(fn=fn, hq=hq, dq=dq, h1=h1, d1=d1, h2=h2, d2=d2, ho=ho, hl=hl, ev_in=torch.cuda.Event(),
                           ev_c=None, ev_o=None))
     z = slots[0]
     h2d = z["hq"].numel() * z["hq"].element_size() + z["h1"].numel() * z["h1"].element_size() + \
@@ -306,19 +304,13 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
             with torch.cuda.stream(s_in):
                 if k["ev_c"] is not None:
                     s_in.wait_event(k["ev_c"])          # this instance's staging buffers are free again
-                k["dq_a"].copy_(k["hq_a"], non_blocking=True)
+                k["dq"].copy_(k["hq"], non_blocking=True)
                 k["d1"].copy_(k["h1"], non_blocking=True)
                 if k["h2"] is not None:
                     k["d2"].copy_(k["h2"], non_blocking=True)
                 k["ev_in"].record(s_in)
-            with torch.cuda.stream(s_in2):
-                if k["ev_c"] is not None:
-                    s_in2.wait_event(k["ev_c"])
-                k["dq_b"].copy_(k["hq_b"], non_blocking=True)
-                k["ev_in2"].record(s_in2)
             with torch.cuda.stream(s_c):
                 s_c.wait_event(k["ev_in"])
-                s_c.wait_event(k["ev_in2"])
                 if k["ev_o"] is not None:
                     s_c.wait_event(k["ev_o"])           # its previous result has been read back
                 o, l = k["fn"](k["dq"], k["d1"], k["d2"]) if kind == "hca" else k["fn"](k["dq"], k["d1"])
@@ -333,14 +325,14 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
 
     run(max(warmup, R))
     torch.cuda.synchronize()
-    side = (s_in, s_in2, s_c, s_out)
+    side = (s_in, s_c, s_out)
 
     def fresh_events():
         for k in slots:
             k["ev_c"] = k["ev_o"] = None
-            k["ev_in"], k["ev_in2"] = torch.cuda.Event(), torch.cuda.Event()
+            k["ev_in"] = torch.cuda.Event()
 
-    # The K steps (copies, launches and their event edges over the four streams) are captured into
+    # The K steps (copies, launches and their event edges over the three streams) are captured into
     # one CUDA graph: enqueueing them from Python takes longer per step than the step itself.
     graph = None
     try:
@@ -678,7 +670,7 @@ def run_ours(args):
                          f"with a {L2_FLUSH_BYTES >> 20} MiB write before each launch",
                    "kv_bytes_per_gpu_step": head["kv_bytes"], "parallelism": f"dp{world} over requests, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"],
-                "ms_per_step": e2e_ms, "note": "every step copies q and its length/index tensors from pinned host memory and reads out+lse back to pinned host memory; copy-in (two streams), compute and copy-out run on streams chained by events, K steps timed as a whole; the KV cache is device-resident state"},
+                "ms_per_step": e2e_ms, "note": "every step copies q and its length/index tensors from pinned host memory and reads out+lse back to pinned host memory; copy-in, compute and copy-out run on their own streams chained by events, K steps timed as a whole; the KV cache is device-resident state"},
         "gpu_launches": head["launches"] * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "traffic": NCU_DRAM_TRAFFIC.get(args.workload), "traffic_source": NCU_TRAFFIC_SOURCE if args.workload in NCU_DRAM_TRAFFIC else None,
