@@ -132,9 +132,25 @@ cudaError_t launch_simt(const DecodeArgs& a, int rows, int max_tok, cudaStream_t
     return cudaGetLastError();
 }
 
-cudaError_t launch_combine(const CombineArgs& c, cudaStream_t stream) {
+// after_decode: the launch directly follows this library's decode launch on the same stream; the merge is then
+// launched as its programmatic dependent, so that its blocks are resident (and waiting) when the last decode
+// blocks are in their epilogue.
+cudaError_t launch_combine(const CombineArgs& c, cudaStream_t stream, bool after_decode = false) {
     const int64_t units = int64_t(c.N) * c.H;
     const int blocks = int((units + kCombineWarps - 1) / kCombineWarps);
+    if (after_decode && !(g_dbg & 64)) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(kCombineWarps * 32);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, combine_kernel, c);
+    }
     combine_kernel<<<blocks, kCombineWarps * 32, 0, stream>>>(c);
     return cudaGetLastError();
 }
@@ -246,7 +262,7 @@ int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
     if (a.num_splits > 1) {
         CombineArgs c = contiguous_combine(rows, a.H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
                                            !a.partial_f32);
-        e = launch_combine(c, stream);
+        e = launch_combine(c, stream, true);
     }
     return int(e);
 }
@@ -431,7 +447,7 @@ extern "C" int hca_decode_fwd(const void* Q,
     if (e != cudaSuccess) return int(e);
     if (splits > 1) {
         CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink, !a.partial_f32);
-        e = launch_combine(cb, s);
+        e = launch_combine(cb, s, true);
     }
     return int(e);
 }
@@ -572,7 +588,7 @@ extern "C" int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, vo
     if (a.num_splits > 1) {
         CombineArgs cb = contiguous_combine(p->B, p->H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
                                             !a.partial_f32);
-        e = launch_combine(cb, s);
+        e = launch_combine(cb, s, true);
     }
     return int(e);
 }

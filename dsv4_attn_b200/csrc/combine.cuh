@@ -42,6 +42,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineArgs a) {
+    // When launched as a programmatic dependent of the decode kernel (same call, same stream) the blocks may
+    // be resident before that kernel has finished: nothing is read before it has completed and its
+    // writes are visible.  Returns at once in an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t unit = int64_t(blockIdx.x) * kCombineWarps + warp;   // (row, head) flattened
     if (unit >= int64_t(a.N) * a.H) return;

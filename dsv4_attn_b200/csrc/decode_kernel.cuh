@@ -1112,6 +1112,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             if (ok) {
                 ptx::tc_fence_after_sync();
                 if (tid == 0) trace_mark(a, 3, 2);
+                // A merge kernel launched as a programmatic dependent may be made resident once every block of
+                // this grid is here (or gone): by then no block of this grid is waiting for an SM any more.
+                if (tid == 0 && a.num_splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
                 const int h = hg * kHeadsPerCta + r;
                 const bool write = h < a.H;
                 const bool final_out = a.num_splits == 1;

@@ -451,7 +451,8 @@ void dsv4_debug_set_trace(void* device_buffer);
  * distributed shared memory) instead of the default kernel; bit5 (packed layout only): the two
  * blocks of a row and head group run as a cluster pair in which each fetches and dequantises half
  * of every tile and forwards it to the other (results bit-identical to the default kernel).
- * No counterpart in the reference. */
+ * bit6: launch the split-KV merge as an ordinary kernel instead of as a programmatic dependent of
+ * the decode kernel.  No counterpart in the reference. */
 void dsv4_debug_set_flags(int flags);
 
 /* Library identification: (major << 16) | minor. */
