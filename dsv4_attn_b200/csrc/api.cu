@@ -686,7 +686,21 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     static bool done_topk[kMaxDevices] = {}, done_pair[kMaxDevices] = {};
     e = pair ? ensure_smem(topk_select_pair_kernel, 180 * 1024, done_pair) : ensure_smem(topk_select_kernel, 180 * 1024, done_topk);
     if (e != cudaSuccess) return int(e);
-    if (pair) topk_select_pair_kernel<<<t.rows * 2, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
-    else topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
-    return int(cudaGetLastError());
+    if (g_dbg & 64) {
+        if (pair) topk_select_pair_kernel<<<t.rows * 2, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
+        else topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
+        return int(cudaGetLastError());
+    }
+    // as a programmatic dependent of the scoring kernel: resident (and waiting) when its last blocks finish
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pair ? t.rows * 2 : t.rows);
+    cfg.blockDim = dim3(kTopkThreads);
+    cfg.dynamicSmemBytes = t.row_in_smem ? row_bytes : 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return int(pair ? cudaLaunchKernelEx(&cfg, topk_select_pair_kernel, t) : cudaLaunchKernelEx(&cfg, topk_select_kernel, t));
 }

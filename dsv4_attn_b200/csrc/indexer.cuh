@@ -233,6 +233,8 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
     // common exit: every role arrives; the MMA warp frees tensor memory after all accumulator reads
     ptx::tc_fence_before_sync();
     __syncthreads();
+    // the top-k kernel may be made resident as soon as every block of this grid is here or gone
+    if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem, kIdxTmemCols);
@@ -502,11 +504,13 @@ __device__ __forceinline__ void topk_select_body(const TopkArgs& a, float* topk_
 
 __global__ void __launch_bounds__(kTopkThreads) topk_select_kernel(const TopkArgs a) {
     extern __shared__ float topk_row[];
+    asm volatile("griddepcontrol.wait;" ::: "memory");     // launched as a programmatic dependent of the scoring kernel
     topk_select_body<1>(a, topk_row);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTopkThreads) topk_select_pair_kernel(const TopkArgs a) {
     extern __shared__ float topk_row[];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     topk_select_body<2>(a, topk_row);
 }
 
