@@ -10,7 +10,7 @@ from __future__ import annotations
 import importlib
 
 _API = ("Dsv4Error", "alloc_workspace", "combine", "csa_sparse_decode", "csa_sparse_decode_noalloc", "csa_compress_reduce_fwd", "hca_compress_fwd", "kv_quantize_insert", "hca_packed_decode", "rope_norm", "indexer_topk", "hca_decode_fwd", "hca_dense_decode",
-        "new_status", "plan_splits")
+        "new_status", "plan_splits", "plan_csa", "plan_hca", "Plan", "check_fp16_operand_range")
 __all__ = ["LIB", "library_path", "layout", "synth", *_API]
 
 

@@ -28,7 +28,7 @@ class CsaSparseDecodeParams(C.Structure):
         ("q", C.c_void_p), ("kv_pool", C.c_void_p), ("block_table", C.c_void_p),
         ("indices", C.c_void_p), ("kv_len", C.c_void_p), ("topk_len", C.c_void_p), ("attn_sink", C.c_void_p),
         ("out", C.c_void_p), ("lse", C.c_void_p), ("partial_o", C.c_void_p),
-        ("partial_lse", C.c_void_p), ("status", C.c_void_p),
+        ("partial_lse", C.c_void_p), ("status", C.c_void_p), ("sched", C.c_void_p),
     ]
 
 
@@ -40,7 +40,16 @@ class HcaDenseDecodeParams(C.Structure):
         ("q", C.c_void_p), ("kv_pool", C.c_void_p), ("block_table", C.c_void_p),
         ("kv_len", C.c_void_p), ("win_pool", C.c_void_p), ("win_len", C.c_void_p),
         ("attn_sink", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
-        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("status", C.c_void_p),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("status", C.c_void_p), ("sched", C.c_void_p),
+    ]
+
+
+class PlanParams(C.Structure):
+    _fields_ = [
+        ("kind", C.c_int32), ("B", C.c_int32), ("s_q", C.c_int32), ("H", C.c_int32), ("topk", C.c_int32),
+        ("num_splits", C.c_int32), ("num_sms", C.c_int32), ("reserved0", C.c_int32),
+        ("topk_len", C.c_void_p), ("kv_len", C.c_void_p), ("win_len", C.c_void_p),
+        ("sched", C.c_void_p), ("sched_bytes", C.c_int64),
     ]
 
 
@@ -55,7 +64,7 @@ class CombineParams(C.Structure):
     ]
 
 
-EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_trace", "dsv4_debug_set_flags", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
+EXPORTS = ("dsv4_attn_version", "dsv4_debug_set_wait", "dsv4_debug_set_flags", "dsv4_attn_plan", "dsv4_attn_plan_host", "dsv4_attn_sched_bytes", "dsv4_csa_sparse_decode_fwd", "dsv4_csa_sparse_decode_simt", "dsv4_csa_sparse_decode_fwd_noalloc",
            "dsv4_noalloc_scratch_bytes", "dsv4_attn_last_error", "dsv4_csa_compress_reduce_fwd",
            "dsv4_hca_dense_decode_fwd", "dsv4_hca_dense_decode_simt", "dsv4_attn_combine", "dsv4_attn_plan_splits",
            "dsv4_attn_workspace_bytes", "hca_decode_fwd", "dsv4_hca_compress_fwd", "dsv4_kv_quantize_insert",
@@ -147,14 +156,19 @@ def _load() -> C.CDLL:
                      ("dsv4_rope_norm_fwd", RopeNormParams),
                      ("dsv4_hca_packed_decode_fwd", HcaPackedDecodeParams),
                      ("dsv4_kv_quantize_insert", KvQuantizeInsertParams),
+                     ("dsv4_attn_plan", PlanParams),
                      ("dsv4_attn_combine", CombineParams)):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [P(st), C.c_void_p]
     lib.dsv4_debug_set_flags.restype = None
     lib.dsv4_debug_set_flags.argtypes = [C.c_int]
-    lib.dsv4_debug_set_trace.restype = None
-    lib.dsv4_debug_set_trace.argtypes = [C.c_void_p]
+    lib.dsv4_debug_set_wait.restype = None
+    lib.dsv4_debug_set_wait.argtypes = [C.c_uint64, C.c_int]
+    lib.dsv4_attn_plan_host.restype = C.c_int
+    lib.dsv4_attn_plan_host.argtypes = [P(PlanParams)]
+    lib.dsv4_attn_sched_bytes.restype = C.c_int64
+    lib.dsv4_attn_sched_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, P(C.c_int64), P(C.c_int64)]
     lib.dsv4_noalloc_scratch_bytes.restype = C.c_int64
     lib.dsv4_noalloc_scratch_bytes.argtypes = []
     lib.dsv4_attn_last_error.restype = C.c_char_p

@@ -71,7 +71,70 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros(4, dtype=torch.int32, device=device)
 
 
-def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace, max_len, need_workspace=True):
+class Plan:
+    """A split-KV schedule for one batch (see dsv4_attn_plan in include/dsv4_attn.h): the device
+    buffer the planner kernel filled, plus the partial-output areas the decode call needs with it.
+    A plan depends only on (kind, B, s_q, H) and the length tensors it was made from; it can be
+    reused by every layer of a decode step that shares them, and re-made in place with `remake()`
+    when the lengths change (same shapes: nothing is allocated)."""
+
+    def __init__(self, kind, B, s_q, H, topk, num_splits, num_sms, lengths, device):
+        self.kind, self.B, self.s_q, self.H, self.topk = kind, B, s_q, H, topk
+        self.num_splits, self.num_sms = num_splits, num_sms
+        po, pl = C.c_int64(0), C.c_int64(0)
+        nbytes = _lib.LIB.dsv4_attn_sched_bytes(B * s_q, H, num_splits, num_sms, C.byref(po), C.byref(pl))
+        _check(nbytes > 0, "dsv4_attn_sched_bytes rejected the shape")
+        self.sched = torch.empty(nbytes // 4, dtype=torch.int32, device=device)
+        # one BF16 row of 512 per (slot, head row); held as float32 storage like the split workspace
+        self.partial_o = torch.empty(max(po.value // 4, 4), dtype=torch.float32, device=device)
+        self.partial_lse = torch.empty(max(pl.value // 4, 4), dtype=torch.float32, device=device)
+        self.lengths = lengths
+        self.remake()
+
+    def remake(self):
+        topk_len, kv_len, win_len = self.lengths
+        p = _lib.PlanParams(kind=self.kind, B=self.B, s_q=self.s_q, H=self.H, topk=self.topk, num_splits=self.num_splits,
+                            num_sms=self.num_sms, topk_len=_ptr(topk_len), kv_len=_ptr(kv_len), win_len=_ptr(win_len),
+                            sched=_ptr(self.sched), sched_bytes=self.sched.numel() * 4)
+        rc = _lib.LIB.dsv4_attn_plan(C.byref(p), _stream(self.sched.device))
+        if rc != 0:
+            raise Dsv4Error(f"dsv4_attn_plan failed: cudaError={rc} {_lib.LIB.dsv4_attn_last_error().decode()}")
+        return self
+
+    def info(self):
+        """(items, partial slots, capacity exceeded, cost share per block pair): reads the device buffer back."""
+        return tuple(self.sched[:4].cpu().tolist())
+
+
+def plan_csa(B, s_q, H, topk, *, topk_len=None, kv_len=None, num_splits=0, num_sms=0, device="cuda") -> Plan:
+    """Schedule for a CSA sparse decode batch.  num_splits = 0: the planner balances the SMs;
+    >= 1: exactly that many pieces per (row, 128 heads)."""
+    for name, t in (("topk_len", topk_len), ("kv_len", kv_len)):
+        if t is not None:
+            _cuda_contig(t, name, torch.int32, 2)
+            _check(tuple(t.shape) == (B, s_q), f"{name} must be [B, s_q]")
+    return Plan(0, B, s_q, H, topk, num_splits, num_sms, (topk_len, kv_len, None), device)
+
+
+def plan_hca(B, s_q, H, kv_len, win_len, *, num_splits=0, num_sms=0) -> Plan:
+    """Schedule for an HCA dense decode batch (lengths int32 [B, s_q] on the device)."""
+    _cuda_contig(kv_len, "kv_len", torch.int32, 2)
+    _cuda_contig(win_len, "win_len", torch.int32, 2)
+    _check(tuple(kv_len.shape) == (B, s_q) and tuple(win_len.shape) == (B, s_q), "kv_len/win_len must be [B, s_q]")
+    return Plan(1, B, s_q, H, 0, num_splits, num_sms, (None, kv_len, win_len), kv_len.device)
+
+
+def check_fp16_operand_range(q: torch.Tensor, kv_pool: torch.Tensor, win_pool: Optional[torch.Tensor] = None) -> None:
+    """Host-side check of the preconditions of the FP16 operand route (|q| < 65504, block scales <= 146).
+    Reads the tensors back: for callers that cannot vouch for their inputs, not for the hot path."""
+    _check(bool(q.abs().max() < 65504), "|q| must stay below 65504")
+    for name, pool in (("kv_pool", kv_pool), ("win_pool", win_pool)):
+        if pool is not None and pool.numel() > 0:
+            sc = pool.reshape(-1, ENTRY_BYTES)[:, 512:528].contiguous().view(torch.float32)
+            _check(bool(sc.abs().max() <= 146.0), f"{name}: a block scale exceeds 146 (it would be clamped)")
+
+
+def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace, max_len, need_workspace=True, plan=None):
     _cuda_contig(q, "q", torch.bfloat16, 4)
     B, s_q, H, dq = q.shape
     _check(dq == D_QK, f"q last dim must be {D_QK}")
@@ -84,6 +147,10 @@ def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace,
         _cuda_contig(attn_sink, "attn_sink", torch.float32, 1)
         _check(attn_sink.shape[0] == H, "attn_sink must be [H]")
     rows = B * s_q
+    if plan is not None:
+        _check((plan.B, plan.s_q, plan.H) == (B, s_q, H), "plan was made for another batch shape")
+        num_splits = 1
+        need_workspace = False
     if num_splits is None:
         num_splits = plan_splits(rows, H, max_len)
     _check(1 <= num_splits <= MAX_SPLITS, f"num_splits must be in [1, {MAX_SPLITS}]")
@@ -107,11 +174,14 @@ def _common(q, kv_pool, block_table, attn_sink, out, lse, num_splits, workspace,
             _cuda_contig(pl, "partial_lse", torch.float32)
             _check(po.numel() >= num_splits * rows * H * D_LATENT and pl.numel() >= num_splits * rows * H,
                    "workspace too small for num_splits")
+    if plan is not None:
+        po, pl = plan.partial_o, plan.partial_lse
     return B, s_q, H, num_splits, out, lse, po, pl
 
 
 def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None, topk_len=None, attn_sink=None,
-                      num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma"):
+                      num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma", plan=None,
+                      check_fp16_range=False):
     """CSA sparse decode.  q bf16 [B, s_q, H, 576]; kv_pool uint8 [P, 64, 656];
     block_table int32 [B, max_pages]; indices int32 [B, s_q, topk] (-1 = pad);
     kv_len optional int32 [B, s_q]; topk_len optional int32 [B, s_q] (only the
@@ -120,10 +190,13 @@ def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None
     _cuda_contig(indices, "indices", torch.int32, 3)
     topk = indices.shape[-1]
     if impl == "simt":
-        num_splits = 1
+        num_splits, plan = 1, None
     B, s_q, H, num_splits, out, lse, po, pl = _common(q, kv_pool, block_table, attn_sink, out, lse,
-                                                      num_splits, workspace, topk)
+                                                      num_splits, workspace, topk, plan=plan)
     _check(tuple(indices.shape[:2]) == (B, s_q), "indices must be [B, s_q, topk]")
+    _check(plan is None or (plan.kind == 0 and plan.topk == topk), "plan was made for another kind of batch")
+    if check_fp16_range:
+        check_fp16_operand_range(q, kv_pool)
     if kv_len is not None:
         _cuda_contig(kv_len, "kv_len", torch.int32, 2)
         _check(tuple(kv_len.shape) == (B, s_q), "kv_len must be [B, s_q]")
@@ -135,7 +208,7 @@ def csa_sparse_decode(q, kv_pool, block_table, indices, sm_scale, *, kv_len=None
         sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
         q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), indices=_ptr(indices),
         kv_len=_ptr(kv_len), topk_len=_ptr(topk_len), attn_sink=_ptr(attn_sink), out=_ptr(out), lse=_ptr(lse),
-        partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
+        partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status), sched=None if plan is None else _ptr(plan.sched))
     fn = _lib.LIB.dsv4_csa_sparse_decode_fwd if impl == "mma" else _lib.LIB.dsv4_csa_sparse_decode_simt
     _rc(fn(C.byref(p), _stream(q.device)), "dsv4_csa_sparse_decode")
     return out, lse
@@ -175,7 +248,7 @@ def csa_sparse_decode_noalloc(q, kv_pool, block_table, indices, sm_scale, *, out
 
 def hca_dense_decode(q, kv_pool, block_table, kv_len, win_pool, win_len, sm_scale, *, attn_sink=None,
                      num_splits=None, out=None, lse=None, workspace=None, status=None, impl="mma",
-                     max_len=None):
+                     max_len=None, plan=None, check_fp16_range=False):
     """HCA dense decode.  kv_len / win_len int32 [B, s_q]; win_pool uint8
     [B, W, 656].  `max_len` (longest kv_len + win_len) only steers the split
     planner; when omitted the block-table capacity is used so that no device
@@ -188,9 +261,12 @@ def hca_dense_decode(q, kv_pool, block_table, kv_len, win_pool, win_len, sm_scal
     if max_len is None:
         max_len = block_table.shape[1] * PAGE_ENTRIES + W
     if impl == "simt":
-        num_splits = 1
+        num_splits, plan = 1, None
     B, s_q, H, num_splits, out, lse, po, pl = _common(q, kv_pool, block_table, attn_sink, out, lse,
-                                                      num_splits, workspace, max_len)
+                                                      num_splits, workspace, max_len, plan=plan)
+    _check(plan is None or plan.kind == 1, "plan was made for another kind of batch")
+    if check_fp16_range:
+        check_fp16_operand_range(q, kv_pool, win_pool)
     _check(tuple(kv_len.shape) == (B, s_q) and tuple(win_len.shape) == (B, s_q), "kv_len/win_len must be [B, s_q]")
     _check(win_pool.shape[0] == B, "win_pool must be [B, W, 656]")
     p = _lib.HcaDenseDecodeParams(
@@ -198,7 +274,8 @@ def hca_dense_decode(q, kv_pool, block_table, kv_len, win_pool, win_len, sm_scal
         sm_scale=float(sm_scale), num_pages=kv_pool.shape[0],
         q=_ptr(q), kv_pool=_ptr(kv_pool), block_table=_ptr(block_table), kv_len=_ptr(kv_len),
         win_pool=_ptr(win_pool), win_len=_ptr(win_len), attn_sink=_ptr(attn_sink),
-        out=_ptr(out), lse=_ptr(lse), partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status))
+        out=_ptr(out), lse=_ptr(lse), partial_o=_ptr(po), partial_lse=_ptr(pl), status=_ptr(status),
+        sched=None if plan is None else _ptr(plan.sched))
     fn = _lib.LIB.dsv4_hca_dense_decode_fwd if impl == "mma" else _lib.LIB.dsv4_hca_dense_decode_simt
     _rc(fn(C.byref(p), _stream(q.device)), "dsv4_hca_dense_decode")
     return out, lse

@@ -1,12 +1,14 @@
 // C ABI of the library: argument validation, parameter filling, launches.
-// No allocation, no synchronisation, no global mutable state apart from
-// per-device kernel attributes that are set once.
+// No allocation and no synchronisation.  Process-wide state is limited to: per-device flags that a
+// kernel's shared-memory attribute has been set, the per-device address of the built-in scratch array of
+// the entry point that allocates nothing (both written once, atomically), and the test switches of
+// dsv4_debug_set_flags / dsv4_debug_set_wait, which are read once per call.
 #include "../../include/dsv4_attn.h"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cmath>
-#include <mutex>
+#include <atomic>
 
 #include "combine.cuh"
 #include "compress_reduce.cuh"
@@ -14,7 +16,7 @@
 #include "rope_norm.cuh"
 #include "indexer.cuh"
 #include "decode_kernel.cuh"
-#include "decode_pair.cuh"
+#include "sched.cuh"
 #include "decode_simt.cuh"
 
 namespace dsv4 {
@@ -22,10 +24,15 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 
-// Profiling aid (see dsv4_debug_set_trace): device buffer that block (0,0,0) of
-// the next decode launches writes phase timestamps to.  Null in normal use.
-unsigned long long* g_trace = nullptr;
-int g_dbg = 0;
+// Test switches (dsv4_debug_set_flags, dsv4_debug_set_wait); product behaviour when left alone.
+std::atomic<int> g_dbg{0};
+std::atomic<unsigned long long> g_wait_ns{kDefaultWaitNs};
+std::atomic<int> g_drop_tile{-1};
+#ifdef DSV4_TRACE
+std::atomic<unsigned long long*> g_trace{nullptr};
+#endif
+
+thread_local const char* t_last_error = "";
 
 // cuTensorMapEncodeTiled, looked up through the runtime so that the library does
 // not link against libcuda.
@@ -61,68 +68,87 @@ cudaError_t make_q_map(CUtensorMap* map, const void* q, int64_t rows, int cols) 
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-// Opt in to the large dynamic shared memory once per (kernel, device).
+// Opt in to the large dynamic shared memory once per (kernel, device).  The flags are written once,
+// atomically; two threads racing on the first call both set the attribute, which is harmless.
 template <typename Kernel>
-cudaError_t ensure_smem(Kernel kernel, int bytes, bool* done_per_device) {
+cudaError_t ensure_smem(Kernel kernel, int bytes, std::atomic<bool>* done_per_device) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!done_per_device[dev]) {
+    if (!done_per_device[dev].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return e;
-        done_per_device[dev] = true;
+        done_per_device[dev].store(true, std::memory_order_release);
     }
     return cudaSuccess;
 }
 
+int device_sms() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
+
+// Layout of a schedule buffer (int32 words); a function of the batch shape only, so that the planner and
+// the decode entry points agree on it without reading anything back.
+struct SchedLayout {
+    int64_t info, pair_begin, unit_nsplits, unit_slot, unit_prefix, items, words;
+    int item_cap;
+};
+constexpr int kSchedInfoWords = 16;
+SchedLayout sched_layout(int n_units, int item_cap) {
+    SchedLayout l{};
+    l.info = 0;
+    l.pair_begin = kSchedInfoWords;
+    l.unit_nsplits = l.pair_begin + ((kPlanMaxPairs + 1 + 3) / 4) * 4;
+    l.unit_slot = l.unit_nsplits + ((n_units + 3) / 4) * 4;
+    l.unit_prefix = l.unit_slot + ((n_units + 3) / 4) * 4;
+    l.items = l.unit_prefix + 2 * int64_t((n_units + 1) / 2 * 2);
+    l.item_cap = item_cap;
+    l.words = l.items + int64_t(item_cap) * kItemWords;
+    return l;
+}
+int sched_item_cap(int n_units, int num_splits, int num_pairs) {
+    return n_units * (num_splits > 1 ? num_splits : 1) + num_pairs;
+}
+int64_t sched_slot_cap(int n_units, int num_splits, int num_pairs) {
+    if (num_splits == 1) return 0;
+    return num_splits > 1 ? int64_t(n_units) * num_splits : 2 * int64_t(num_pairs);
+}
+
 template <int NCHUNK, int SRC>
-cudaError_t launch_mma(DecodeArgs& a, int rows, cudaStream_t stream) {
+cudaError_t launch_mma(DecodeArgs& a, int rows, const void* sched, cudaStream_t stream) {
     cudaError_t e = make_q_map(&a.q_map, a.q, int64_t(rows) * a.H, NCHUNK * 64);
     if (e != cudaSuccess) return e;
+    a.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+    a.dbg_drop_tile = g_drop_tile.load(std::memory_order_relaxed);
+#ifdef DSV4_TRACE
+    a.trace = g_trace.load();
+#endif
     const int head_groups = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
     dim3 grid(2 * head_groups, rows, a.num_splits);
-    if ((g_dbg & 32) && !is_ref_layout(SRC)) {
-        if constexpr (!is_ref_layout(SRC)) {
-            // cluster pairs that share the fetch and dequantisation of every tile
-            static bool done[kMaxDevices] = {};
-            constexpr int smem = SmemLayout<NCHUNK>::kTotal;
-            e = ensure_smem(decode_mma_kernel<NCHUNK, SRC, true>, smem, done);
-            if (e != cudaSuccess) return e;
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = grid;
-            cfg.blockDim = dim3(kNumThreads);
-            cfg.dynamicSmemBytes = smem;
-            cfg.stream = stream;
-            cudaLaunchAttribute attr{};
-            attr.id = cudaLaunchAttributeClusterDimension;
-            attr.val.clusterDim.x = 2;  attr.val.clusterDim.y = 1;  attr.val.clusterDim.z = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
-            return cudaLaunchKernelEx(&cfg, decode_mma_kernel<NCHUNK, SRC, true>, a);
-        }
-    } else if (!(g_dbg & 16) || SRC == kSrcRefPaged) {
-        // product path: each block computes the whole QK product for its half of the value columns
-        static bool done[kMaxDevices] = {};
-        constexpr int smem = SmemLayout<NCHUNK>::kTotal;
-        e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
-        if (e != cudaSuccess) return e;
-        decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
-    } else if constexpr (SRC != kSrcRefPaged) {
-        // evaluated alternative, kept selectable for measurements: cluster pairs that split the
-        // query/key columns and exchange halves of S through distributed shared memory
-        static bool done[kMaxDevices] = {};
-        a.partial_f32 = 1;                     // that kernel writes its split partials as FP32
-        e = ensure_smem(pair::decode_pair_kernel<NCHUNK, SRC>, pair::kSmemTotal, done);
-        if (e != cudaSuccess) return e;
-        pair::decode_pair_kernel<NCHUNK, SRC><<<grid, kNumThreads, pair::kSmemTotal, stream>>>(a);
+    if (sched != nullptr) {
+        // resident blocks, one pair per two SMs, each walking its slice of the plan
+        const SchedLayout l = sched_layout(rows * head_groups, 0);
+        const int32_t* base = static_cast<const int32_t*>(sched);
+        a.sched_pair_begin = base + l.pair_begin;
+        a.sched_items = base + l.items;
+        int pairs = device_sms() / 2;
+        if (pairs > kPlanMaxPairs) pairs = kPlanMaxPairs;
+        grid = dim3(2 * (pairs > 0 ? pairs : 1), 1, 1);
     }
+    static std::atomic<bool> done[kMaxDevices];
+    constexpr int smem = SmemLayout<NCHUNK>::kTotal;
+    e = ensure_smem(decode_mma_kernel<NCHUNK, SRC>, smem, done);
+    if (e != cudaSuccess) return e;
+    decode_mma_kernel<NCHUNK, SRC><<<grid, kNumThreads, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int SRC>
 cudaError_t launch_simt(const DecodeArgs& a, int rows, int max_tok, cudaStream_t stream) {
-    static bool done[kMaxDevices] = {};
+    static std::atomic<bool> done[kMaxDevices];
     const int smem = (576 + kSimtThreads + max_tok) * int(sizeof(float));
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     cudaError_t e = ensure_smem(decode_simt_kernel<SRC>, 200 * 1024, done);
@@ -138,7 +164,7 @@ cudaError_t launch_simt(const DecodeArgs& a, int rows, int max_tok, cudaStream_t
 cudaError_t launch_combine(const CombineArgs& c, cudaStream_t stream, bool after_decode = false) {
     const int64_t units = int64_t(c.N) * c.H;
     const int blocks = int((units + kCombineWarps - 1) / kCombineWarps);
-    if (after_decode && !(g_dbg & 64)) {
+    if (after_decode && !(g_dbg.load(std::memory_order_relaxed) & 64)) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(blocks);
         cfg.blockDim = dim3(kCombineWarps * 32);
@@ -182,14 +208,15 @@ bool common_ok(int B, int s_q, int H, int num_splits, float sm_scale, const void
 
 bool fill_csa(const Dsv4CsaSparseDecodeParams* p, DecodeArgs& a) {
     if (p == nullptr) return false;
-    if (!common_ok(p->B, p->s_q, p->H, p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
+    if (!common_ok(p->B, p->s_q, p->H, p->sched != nullptr ? 2 : p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
         return false;
-    if (p->topk <= 0 || p->max_pages <= 0) return false;
+    if (p->topk <= 0 || p->max_pages <= 0 || p->num_pages <= 0 || !aligned(p->sched, 16)) return false;
     if (p->kv_pool == nullptr || p->block_table == nullptr || p->indices == nullptr) return false;
     if (!aligned(p->kv_pool, 16)) return false;
     a = DecodeArgs{};
     a.B = p->B;  a.s_q = p->s_q;  a.H = p->H;  a.topk = p->topk;  a.max_pages = p->max_pages;
-    a.num_splits = p->num_splits;
+    a.num_pages = p->num_pages;
+    a.num_splits = p->sched != nullptr ? 1 : p->num_splits;
     a.scale_log2 = p->sm_scale * 1.4426950408889634f;
     a.q = static_cast<const __nv_bfloat16*>(p->q);
     a.kv_pool = static_cast<const uint8_t*>(p->kv_pool);
@@ -197,22 +224,22 @@ bool fill_csa(const Dsv4CsaSparseDecodeParams* p, DecodeArgs& a) {
     a.attn_sink = p->attn_sink;
     a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
-    a.trace = g_trace;  a.dbg = g_dbg;
     return true;
 }
 
 bool fill_hca(const Dsv4HcaDenseDecodeParams* p, DecodeArgs& a) {
     if (p == nullptr) return false;
-    if (!common_ok(p->B, p->s_q, p->H, p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
+    if (!common_ok(p->B, p->s_q, p->H, p->sched != nullptr ? 2 : p->num_splits, p->sm_scale, p->q, p->out, p->partial_o, p->partial_lse))
         return false;
-    if (p->max_pages <= 0 || p->win_cap < 0) return false;
+    if (p->max_pages <= 0 || p->win_cap < 0 || p->num_pages <= 0 || !aligned(p->sched, 16)) return false;
     if (p->kv_pool == nullptr || p->block_table == nullptr || p->kv_len == nullptr || p->win_len == nullptr)
         return false;
     if (p->win_cap > 0 && p->win_pool == nullptr) return false;
     if (!aligned(p->kv_pool, 16) || !aligned(p->win_pool, 16)) return false;
     a = DecodeArgs{};
     a.B = p->B;  a.s_q = p->s_q;  a.H = p->H;  a.max_pages = p->max_pages;  a.win_cap = p->win_cap;
-    a.num_splits = p->num_splits;
+    a.num_pages = p->num_pages;
+    a.num_splits = p->sched != nullptr ? 1 : p->num_splits;
     a.scale_log2 = p->sm_scale * 1.4426950408889634f;
     a.q = static_cast<const __nv_bfloat16*>(p->q);
     a.kv_pool = static_cast<const uint8_t*>(p->kv_pool);
@@ -221,7 +248,6 @@ bool fill_hca(const Dsv4HcaDenseDecodeParams* p, DecodeArgs& a) {
     a.attn_sink = p->attn_sink;
     a.out = static_cast<__nv_bfloat16*>(p->out);  a.lse = p->lse;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;  a.status = p->status;
-    a.trace = g_trace;  a.dbg = g_dbg;
     return true;
 }
 
@@ -236,35 +262,50 @@ __device__ __align__(256) float g_noalloc_scratch[kNoAllocPartialFloats + kNoAll
 // array's name is only a handle for the runtime, not an address a kernel could
 // use, so the address is asked for once per device and kept.
 cudaError_t noalloc_scratch(float** ptr) {
-    static float* per_device[kMaxDevices] = {};
+    static std::atomic<float*> per_device[kMaxDevices];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (per_device[dev] == nullptr) {
+    float* known = per_device[dev].load(std::memory_order_acquire);
+    if (known == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess) return e;
-        per_device[dev] = static_cast<float*>(p);
+        known = static_cast<float*>(p);
+        per_device[dev].store(known, std::memory_order_release);     // racing threads store the same address
     }
-    *ptr = per_device[dev];
+    *ptr = known;
     return cudaSuccess;
 }
 
-thread_local const char* t_last_error = "";
+// Records why a launch failed for dsv4_attn_last_error().
+int launch_failed(cudaError_t e) {
+    t_last_error = cudaGetErrorString(e);
+    return int(e);
+}
 
-// Decode (+ merge when split) for the packed-entry sources.
+// Decode (+ merge when split) for the packed-entry sources.  With a plan, the resident blocks walk it and the
+// merge adds up the units the plan cut.
 template <int SRC>
-int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
+int decode_fwd(DecodeArgs& a, const void* sched, cudaStream_t stream) {
     const int rows = a.B * a.s_q;
-    cudaError_t e = launch_mma<9, SRC>(a, rows, stream);
-    if (e != cudaSuccess) return int(e);
-    if (a.num_splits > 1) {
+    cudaError_t e = launch_mma<9, SRC>(a, rows, sched, stream);
+    if (e != cudaSuccess) return launch_failed(e);
+    if (sched != nullptr) {
+        const int hgs = (a.H + kHeadsPerCta - 1) / kHeadsPerCta;
+        const SchedLayout l = sched_layout(rows * hgs, 0);
+        CombineArgs c = contiguous_combine(rows, a.H, 1, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink, true);
+        c.unit_nsplits = static_cast<const int32_t*>(sched) + l.unit_nsplits;
+        c.unit_slot = static_cast<const int32_t*>(sched) + l.unit_slot;
+        c.hgs = hgs;
+        e = launch_combine(c, stream, true);
+    } else if (a.num_splits > 1) {
         CombineArgs c = contiguous_combine(rows, a.H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
-                                           !a.partial_f32);
+                                           true);
         e = launch_combine(c, stream, true);
     }
-    return int(e);
+    return e == cudaSuccess ? 0 : launch_failed(e);
 }
 
 }  // namespace
@@ -272,18 +313,107 @@ int decode_fwd(DecodeArgs& a, cudaStream_t stream) {
 
 using namespace dsv4;
 
-extern "C" int dsv4_attn_version(void) { return (0 << 16) | 1; }
+extern "C" int dsv4_attn_version(void) { return (0 << 16) | 2; }
 
-extern "C" void dsv4_debug_set_flags(int flags) { g_dbg = flags; }
+extern "C" void dsv4_debug_set_flags(int flags) { g_dbg.store(flags); }
 
-extern "C" void dsv4_debug_set_trace(void* device_buffer) {
-    g_trace = static_cast<unsigned long long*>(device_buffer);
+extern "C" void dsv4_debug_set_wait(unsigned long long wait_ns, int drop_tile) {
+    g_wait_ns.store(wait_ns != 0 ? wait_ns : kDefaultWaitNs);
+    g_drop_tile.store(drop_tile);
+}
+
+#ifdef DSV4_TRACE
+extern "C" void dsv4_debug_set_trace(void* device_buffer) { g_trace.store(static_cast<unsigned long long*>(device_buffer)); }
+#endif
+
+extern "C" int64_t dsv4_attn_sched_bytes(int rows, int H, int num_splits, int num_sms, int64_t* partial_o_bytes,
+                                         int64_t* partial_lse_bytes) {
+    if (partial_o_bytes) *partial_o_bytes = 0;
+    if (partial_lse_bytes) *partial_lse_bytes = 0;
+    if (rows <= 0 || H <= 0 || num_splits < 0 || num_splits > DSV4_MAX_SPLITS) return 0;
+    if (num_sms <= 0) num_sms = device_sms();
+    int pairs = num_sms / 2;
+    if (pairs < 1) pairs = 1;
+    if (pairs > kPlanMaxPairs) pairs = kPlanMaxPairs;
+    const int hgs = (H + kHeadsPerCta - 1) / kHeadsPerCta;
+    if (int64_t(rows) * hgs > 0x3FFFFFFF / DSV4_MAX_SPLITS) return 0;
+    const int n_units = rows * hgs;
+    const SchedLayout l = sched_layout(n_units, sched_item_cap(n_units, num_splits, pairs));
+    const int64_t slots = sched_slot_cap(n_units, num_splits, pairs);
+    if (partial_o_bytes) *partial_o_bytes = slots * 128 * 512 * 2;       // BF16 rows
+    if (partial_lse_bytes) *partial_lse_bytes = slots * 128 * 4;
+    return l.words * 4;
+}
+
+namespace {
+// Validates a plan request and fills the planner's arguments; `base` is where the schedule goes.
+int fill_plan(const Dsv4PlanParams* p, int32_t* base, PlanArgs& a) {
+    t_last_error = "invalid argument";
+    if (p == nullptr || p->B <= 0 || p->s_q <= 0 || p->H <= 0 || base == nullptr || !aligned(base, 16)) return int(cudaErrorInvalidValue);
+    if (p->num_splits < 0 || p->num_splits > DSV4_MAX_SPLITS || int64_t(p->B) * p->s_q > 65535) return int(cudaErrorInvalidValue);
+    const int sms = device_sms();
+    int num_sms = p->num_sms > 0 ? p->num_sms : sms;
+    if (num_sms > sms && p->num_sms <= 0) num_sms = sms;
+    int pairs = num_sms / 2;
+    if (pairs < 1) pairs = 1;
+    if (pairs > kPlanMaxPairs) pairs = kPlanMaxPairs;
+    a = PlanArgs{};
+    if (p->kind == DSV4_PLAN_CSA) {
+        if (p->topk <= 0) return int(cudaErrorInvalidValue);
+        a.kind = kSrcCsa;
+    } else if (p->kind == DSV4_PLAN_HCA) {
+        if (p->kv_len == nullptr || p->win_len == nullptr) return int(cudaErrorInvalidValue);
+        a.kind = kSrcHca;
+    } else {
+        return int(cudaErrorInvalidValue);
+    }
+    a.rows = p->B * p->s_q;
+    a.hgs = (p->H + kHeadsPerCta - 1) / kHeadsPerCta;
+    const int n_units = a.rows * a.hgs;
+    const SchedLayout l = sched_layout(n_units, sched_item_cap(n_units, p->num_splits, pairs));
+    if (p->sched_bytes < l.words * 4) {
+        t_last_error = "schedule buffer smaller than dsv4_attn_sched_bytes() for this shape";
+        return int(cudaErrorInvalidValue);
+    }
+    a.topk = p->topk;  a.topk_len = p->topk_len;  a.kv_len = p->kv_len;  a.win_len = p->win_len;
+    a.num_pairs = pairs;
+    a.fixed_splits = p->num_splits;
+    a.item_cap = l.item_cap;
+    const int64_t slots = sched_slot_cap(n_units, p->num_splits, pairs);
+    a.slot_cap = int(slots < 0x7FFFFFFF ? slots : 0x7FFFFFFF);
+    a.info = base + l.info;
+    a.pair_begin = base + l.pair_begin;
+    a.unit_nsplits = base + l.unit_nsplits;
+    a.unit_slot = base + l.unit_slot;
+    a.unit_prefix = reinterpret_cast<long long*>(base + l.unit_prefix);
+    a.items = base + l.items;
+    t_last_error = "";
+    return 0;
+}
+}  // namespace
+
+extern "C" int dsv4_attn_plan(const Dsv4PlanParams* p, void* stream) {
+    PlanArgs a;
+    if (p != nullptr && p->num_sms > device_sms()) { t_last_error = "num_sms exceeds the device";  return int(cudaErrorInvalidValue); }
+    const int rc = fill_plan(p, p ? static_cast<int32_t*>(p->sched) : nullptr, a);
+    if (rc != 0) return rc;
+    plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : launch_failed(e);
+}
+
+extern "C" int dsv4_attn_plan_host(const Dsv4PlanParams* p) {
+    PlanArgs a;
+    const int rc = fill_plan(p, p ? static_cast<int32_t*>(p->sched) : nullptr, a);
+    if (rc != 0) return rc;
+    plan_host(a);
+    return 0;
 }
 
 extern "C" int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream) {
     DecodeArgs a;
     if (!fill_csa(p, a)) return int(cudaErrorInvalidValue);
-    return decode_fwd<kSrcCsa>(a, static_cast<cudaStream_t>(stream));
+    return decode_fwd<kSrcCsa>(a, p->sched, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" const char* dsv4_attn_last_error(void) { return t_last_error; }
@@ -298,6 +428,7 @@ extern "C" int dsv4_csa_sparse_decode_fwd_noalloc(const Dsv4CsaSparseDecodeParam
     if (p == nullptr) { t_last_error = "null parameter block";  return int(cudaErrorInvalidValue); }
     // the caller's workspace pointers are not used here; validate the rest as usual
     Dsv4CsaSparseDecodeParams q = *p;
+    q.sched = nullptr;                        // this entry point always takes the caller's split count
     static float dummy;                       // stands in for the workspace during host-side validation only
     if (q.num_splits > 1) { q.partial_o = reinterpret_cast<float*>(uintptr_t(256));  q.partial_lse = &dummy; }
     if (!fill_csa(&q, a)) { t_last_error = "invalid argument";  return int(cudaErrorInvalidValue); }
@@ -319,13 +450,13 @@ extern "C" int dsv4_csa_sparse_decode_fwd_noalloc(const Dsv4CsaSparseDecodeParam
         a.partial_o = nullptr;
         a.partial_lse = nullptr;
     }
-    return decode_fwd<kSrcCsa>(a, static_cast<cudaStream_t>(stream));
+    return decode_fwd<kSrcCsa>(a, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dsv4_hca_dense_decode_fwd(const Dsv4HcaDenseDecodeParams* p, void* stream) {
     DecodeArgs a;
     if (!fill_hca(p, a)) return int(cudaErrorInvalidValue);
-    return decode_fwd<kSrcHca>(a, static_cast<cudaStream_t>(stream));
+    return decode_fwd<kSrcHca>(a, p->sched, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dsv4_csa_sparse_decode_simt(const Dsv4CsaSparseDecodeParams* p, void* stream) {
@@ -432,7 +563,6 @@ extern "C" int hca_decode_fwd(const void* Q,
     a.ref_ks = static_cast<const uint8_t*>(Kswa);  a.ref_ks_s = static_cast<const uint8_t*>(Kswa_s);
     a.ref_ks_rope = static_cast<const __nv_bfloat16*>(Kswa_rope);
     a.ref_m_cur = M_cur;  a.ref_swa_len = swa_len;
-    a.trace = g_trace;  a.dbg = g_dbg;
     // The caller sizes the workspaces for (M_cur + swa_len) / 128 splits; never use more.
     const int caller_splits = (M_cur + swa_len) / 128;
     int splits = dsv4_attn_plan_splits(B, n_h, M_cur + swa_len, 0);
@@ -443,10 +573,10 @@ extern "C" int hca_decode_fwd(const void* Q,
     a.partial_o = static_cast<float*>(partial_O);
     a.partial_lse = static_cast<float*>(partial_lse);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e = launch_mma<8, kSrcRef>(a, B, s);
+    cudaError_t e = launch_mma<8, kSrcRef>(a, B, nullptr, s);
     if (e != cudaSuccess) return int(e);
     if (splits > 1) {
-        CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink, !a.partial_f32);
+        CombineArgs cb = contiguous_combine(B, n_h, splits, a.partial_o, a.partial_lse, O, nullptr, a.attn_sink, true);
         e = launch_combine(cb, s, true);
     }
     return int(e);
@@ -581,13 +711,12 @@ extern "C" int dsv4_hca_packed_decode_fwd(const Dsv4HcaPackedDecodeParams* p, vo
     a.num_splits = p->num_splits;
     a.partial_o = p->partial_o;  a.partial_lse = p->partial_lse;
     a.status = p->status;
-    a.trace = g_trace;  a.dbg = g_dbg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e = launch_mma<8, kSrcRefPaged>(a, p->B, s);
+    cudaError_t e = launch_mma<8, kSrcRefPaged>(a, p->B, nullptr, s);
     if (e != cudaSuccess) return int(e);
     if (a.num_splits > 1) {
         CombineArgs cb = contiguous_combine(p->B, p->H, a.num_splits, a.partial_o, a.partial_lse, a.out, a.lse, a.attn_sink,
-                                            !a.partial_f32);
+                                            true);
         e = launch_combine(cb, s, true);
     }
     return int(e);
@@ -668,7 +797,7 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     a.B = p->B;  a.s_q = p->s_q;  a.max_pages = p->max_pages;  a.num_pages = p->num_pages;
     a.q_weight = p->q_weight;  a.block_table = p->block_table;  a.n_vis = p->n_vis;
     a.scores = p->scores;  a.score_stride = p->score_stride;  a.status = p->status;
-    static bool done[kMaxDevices] = {};
+    static std::atomic<bool> done[kMaxDevices];
     e = ensure_smem(indexer_logits_kernel, kIdxSmemBytes, done);
     if (e != cudaSuccess) return int(e);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -683,10 +812,10 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     const bool pair = t.rows * 2 <= sms;
     const int row_bytes = (pair ? (t.n_cap + 1) / 2 : t.n_cap) * int(sizeof(float));
     t.row_in_smem = row_bytes <= 180 * 1024 ? 1 : 0;
-    static bool done_topk[kMaxDevices] = {}, done_pair[kMaxDevices] = {};
+    static std::atomic<bool> done_topk[kMaxDevices], done_pair[kMaxDevices];
     e = pair ? ensure_smem(topk_select_pair_kernel, 180 * 1024, done_pair) : ensure_smem(topk_select_kernel, 180 * 1024, done_topk);
     if (e != cudaSuccess) return int(e);
-    if (g_dbg & 64) {
+    if (g_dbg.load(std::memory_order_relaxed) & 64) {
         if (pair) topk_select_pair_kernel<<<t.rows * 2, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
         else topk_select_kernel<<<t.rows, kTopkThreads, t.row_in_smem ? row_bytes : 0, s>>>(t);
         return int(cudaGetLastError());

@@ -1,7 +1,7 @@
 // LSE-weighted merge of split-KV partial outputs.  One warp per (row, head):
 // the per-split log2 LSEs are reduced with warp shuffles, each lane then owns
-// 2 x 8 consecutive value columns, reads partials with 128-bit loads and
-// writes BF16 with 128-bit stores.
+// 2 x 8 consecutive value columns, reads partials with 128-bit loads (four splits
+// in flight per lane) and writes BF16 with 128-bit stores.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -25,6 +25,12 @@ struct CombineArgs {
     int64_t stride_out_n, stride_out_h;
     int64_t stride_lse_n;
     int partial_bf16;          // partial_o holds BF16 (strides then count BF16 elements): the library's own split path
+    // Scheduled decode (sched.cuh): the pieces of unit (row, head group) lie in partial slots
+    // unit_slot[u] .. + unit_nsplits[u] - 1, a slot being 128 head rows of 512 BF16 (and 128 LSEs); a unit
+    // with one piece was written out by the decode kernel itself and is skipped here.
+    const int32_t* unit_nsplits;
+    const int32_t* unit_slot;
+    int hgs;
 };
 
 constexpr int kCombineWarps = 8;
@@ -50,16 +56,32 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     const int64_t unit = int64_t(blockIdx.x) * kCombineWarps + warp;   // (row, head) flattened
     if (unit >= int64_t(a.N) * a.H) return;
     const int n = int(unit / a.H), h = int(unit % a.H);
-    const int S = a.num_splits;
+    int S = a.num_splits;
+    const float* pl;
+    int64_t pl_stride, po_off, po_stride;      // po_*: element offsets into partial_o (FP32 or BF16 elements)
+    if (a.unit_nsplits != nullptr) {
+        const int u = n * a.hgs + (h >> 7);
+        S = __ldg(a.unit_nsplits + u);
+        if (S <= 1) return;
+        const int64_t row = int64_t(__ldg(a.unit_slot + u)) * 128 + (h & 127);
+        pl = a.partial_lse + row;
+        pl_stride = 128;
+        po_off = row * 512 + lane * 8;
+        po_stride = 128 * 512;
+    } else {
+        pl = a.partial_lse + int64_t(n) * a.stride_pl_n + h;
+        pl_stride = a.stride_pl_split;
+        po_off = int64_t(n) * a.stride_po_n + int64_t(h) * a.stride_po_h + lane * 8;
+        po_stride = a.stride_po_split;
+    }
 
-    const float* pl = a.partial_lse + int64_t(n) * a.stride_pl_n + h;
     // pass 1: maximum and sum over splits, 32 splits per step
     float mx = -CUDART_INF_F;
-    for (int s = lane; s < S; s += 32) mx = fmaxf(mx, __ldg(pl + int64_t(s) * a.stride_pl_split));
+    for (int s = lane; s < S; s += 32) mx = fmaxf(mx, __ldg(pl + int64_t(s) * pl_stride));
     mx = warp_max(mx);
     float sum = 0.f;
     if (mx != -CUDART_INF_F)
-        for (int s = lane; s < S; s += 32) sum += exp2f(__ldg(pl + int64_t(s) * a.stride_pl_split) - mx);
+        for (int s = lane; s < S; s += 32) sum += exp2f(__ldg(pl + int64_t(s) * pl_stride) - mx);
     sum = warp_sum(sum);
     const bool has = sum != 0.f;
     const float glse = has ? log2f(sum) + mx : -CUDART_INF_F;
@@ -77,42 +99,63 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
 
-    const float* po = a.partial_o + int64_t(n) * a.stride_po_n + int64_t(h) * a.stride_po_h + lane * 8;
     for (int s0 = 0; s0 < S; s0 += 32) {
         // each lane computes the weight of one split of this group; broadcast by shuffle
         float w_mine = 0.f;
         if (s0 + lane < S) {
-            const float l = __ldg(pl + int64_t(s0 + lane) * a.stride_pl_split);
+            const float l = __ldg(pl + int64_t(s0 + lane) * pl_stride);
             w_mine = (l == -CUDART_INF_F || denom == -CUDART_INF_F) ? 0.f : exp2f(l - denom);
         }
         const int cnt = min(32, S - s0);
-        for (int k = 0; k < cnt; ++k) {
-            const float w = __shfl_sync(0xFFFFFFFFu, w_mine, k);
-            if (w == 0.f) continue;     // empty split: its partial may hold anything
-            const float* src = po + int64_t(s0 + k) * a.stride_po_split;
-            if (a.partial_bf16) {
-                const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(a.partial_o) + int64_t(n) * a.stride_po_n +
-                                          int64_t(h) * a.stride_po_h + lane * 8 + int64_t(s0 + k) * a.stride_po_split;
+        // four splits at a time: their loads are all issued before the first is used
+        for (int k0 = 0; k0 < cnt; k0 += 4) {
+            float w[4];
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(sb + i * 256));
-                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[i][2 * j] = fmaf(w, __uint_as_float(u[j] << 16), acc[i][2 * j]);
-                        acc[i][2 * j + 1] = fmaf(w, __uint_as_float(u[j] & 0xFFFF0000u), acc[i][2 * j + 1]);
-                    }
-                }
-                continue;
+            for (int j = 0; j < 4; ++j) {
+                const float x = __shfl_sync(0xFFFFFFFFu, w_mine, (k0 + j) & 31);
+                w[j] = (k0 + j < cnt) ? x : 0.f;      // an empty split has weight 0: its partial may hold anything and is not read
             }
+            if (a.partial_bf16) {
+                const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(a.partial_o) + po_off + int64_t(s0 + k0) * po_stride;
+                uint4 v[4][2];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const float4 v0 = __ldg(reinterpret_cast<const float4*>(src + i * 256));
-                const float4 v1 = __ldg(reinterpret_cast<const float4*>(src + i * 256 + 4));
-                acc[i][0] = fmaf(w, v0.x, acc[i][0]);  acc[i][1] = fmaf(w, v0.y, acc[i][1]);
-                acc[i][2] = fmaf(w, v0.z, acc[i][2]);  acc[i][3] = fmaf(w, v0.w, acc[i][3]);
-                acc[i][4] = fmaf(w, v1.x, acc[i][4]);  acc[i][5] = fmaf(w, v1.y, acc[i][5]);
-                acc[i][6] = fmaf(w, v1.z, acc[i][6]);  acc[i][7] = fmaf(w, v1.w, acc[i][7]);
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+                        v[j][i] = (w[j] != 0.f) ? __ldg(reinterpret_cast<const uint4*>(sb + int64_t(j) * po_stride + i * 256))
+                                                : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const uint32_t u[4] = {v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            acc[i][2 * q] = fmaf(w[j], __uint_as_float(u[q] << 16), acc[i][2 * q]);
+                            acc[i][2 * q + 1] = fmaf(w[j], __uint_as_float(u[q] & 0xFFFF0000u), acc[i][2 * q + 1]);
+                        }
+                    }
+            } else {
+                const float* src = a.partial_o + po_off + int64_t(s0 + k0) * po_stride;
+                float4 v[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float4* q = reinterpret_cast<const float4*>(src + int64_t(j) * po_stride + i * 256);
+                        v[j][2 * i] = (w[j] != 0.f) ? __ldg(q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v[j][2 * i + 1] = (w[j] != 0.f) ? __ldg(q + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float4 v0 = v[j][2 * i], v1 = v[j][2 * i + 1];
+                        acc[i][0] = fmaf(w[j], v0.x, acc[i][0]);  acc[i][1] = fmaf(w[j], v0.y, acc[i][1]);
+                        acc[i][2] = fmaf(w[j], v0.z, acc[i][2]);  acc[i][3] = fmaf(w[j], v0.w, acc[i][3]);
+                        acc[i][4] = fmaf(w[j], v1.x, acc[i][4]);  acc[i][5] = fmaf(w[j], v1.y, acc[i][5]);
+                        acc[i][6] = fmaf(w[j], v1.z, acc[i][6]);  acc[i][7] = fmaf(w[j], v1.w, acc[i][7]);
+                    }
             }
         }
     }

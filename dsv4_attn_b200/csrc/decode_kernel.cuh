@@ -1,17 +1,25 @@
 // Decode attention over an FP8 latent KV cache on sm_100a tensor cores.
 //
-// One thread block handles (request-token row n, group of 128 heads, one half
-// of the 512 value columns, one KV split).  Per 64-entry tile:
+// A thread block works through a list of work items.  An item is (query-token
+// row n, group of 128 heads, a range of 64-entry tiles of that row); the block
+// computes it for one half of the 512 value columns (the block with the other
+// half runs the same list on the neighbouring SM).  The list is either the single
+// item the block's grid position names (one launch = rows x head groups x splits
+// blocks) or this block pair's slice of a schedule a planner kernel wrote (sched.cuh):
+// the block then stays resident, keeps its tensor memory and barriers, and overlaps
+// the set-up of the next item with the tail of the current one.
+// Per 64-entry tile:
 //   loader warps   gather the entries (index list -> block table -> 656-byte
 //                  rows, or the dense / reference-layout equivalents) into
-//                  registers, dequantise FP8 * scale -> BF16 and write the tile
-//                  into shared memory in the 128-byte-swizzled operand layout;
-//   MMA thread     S[128 heads x 64] = Q . K^T   (tcgen05.mma, BF16, K = 576
-//                  or 512) into tensor memory, later O[128 x 256] += P . V with
-//                  V read from the same tile as an MN-major operand;
+//                  registers, dequantise FP8 * scale -> FP16 (BF16 for the reference
+//                  layouts) and write the tile into shared memory in the
+//                  128-byte-swizzled operand layout;
+//   MMA threads    S[128 heads x 64] = Q . K^T   (tcgen05.mma, K = 576 or 512) into
+//                  tensor memory, later O[128 x 256] += P . V with V read from the
+//                  same tile as an MN-major operand;
 //   softmax warps  read S from tensor memory (one head per thread), run the
 //                  online softmax with a lazily updated reference maximum,
-//                  write P (BF16) to shared memory, rescale O in tensor memory
+//                  write P to tensor memory, rescale O in tensor memory
 //                  when the maximum moved, and finally normalise and store.
 // All waits are bounded; a wait that gives up records where in `status` and the
 // block leaves through the common exit, freeing its tensor memory.
@@ -32,13 +40,15 @@ namespace dsv4 {
 constexpr int kTileN = 64;             // cache entries per tile (MMA N of S, K of PV)
 constexpr int kHeadsPerCta = 128;      // MMA M
 constexpr int kDvHalf = 256;           // value columns per block (MMA N of PV)
-constexpr int kQChunkBytes = 128 * 128;   // 128 heads x 64 bf16
-constexpr int kKvChunkBytes = kTileN * 128;  // 64 entries x 64 bf16
+constexpr int kQChunkBytes = 128 * 128;   // 128 heads x 64 16-bit values
+constexpr int kKvChunkBytes = kTileN * 128;  // 64 entries x 64 16-bit values
 // Warp roles, four warpgroups of four warps.  Warps 0-3: softmax + epilogue.
-// Warps 4-11: loaders.  Warp 12: issue of the S = Q.K^T MMAs and tensor-memory allocation;
-// warp 13: issue of the O += P.V MMAs (its own thread, so that a ready P never waits for the
-// other thread to finish issuing a group: an issuing thread is held while the tensor pipe's
-// short queue is full); warps 14-15 only take part in the block-wide barriers.  All 16 warps start with 128
+// Warps 4-11: loaders (and the Q set-up).  Warp 12: issue of the S = Q.K^T MMAs, the Q load and the
+// tensor-memory allocation; warp 13: issue of the O += P.V MMAs (its own thread, so that a ready P never
+// waits for the other thread to finish issuing a group: an issuing thread is held while the tensor pipe's
+// short queue is full); warp 14: walks the block's items and resolves, several tiles ahead, where every
+// entry lives (index list -> block table -> record number), so that the loaders start from record numbers
+// in shared memory; warp 15 only takes part in the block-wide barriers.  All 16 warps start with 128
 // registers (the whole register file); the last warpgroup gives most of its
 // share back and the loaders take it, so that they can hold two tiles of cache
 // entries in flight.  setmaxnreg.inc waits for registers without a time limit,
@@ -48,18 +58,21 @@ constexpr int kNumLoaderWarps = 8;
 constexpr int kFirstLoaderWarp = 4;
 constexpr int kMmaWarp = 12;
 constexpr int kNumWarps = 16;
-constexpr int kStageThreads = (kNumSoftmaxWarps + kNumLoaderWarps) * 32;   // threads that stage Q
+constexpr int kLoaderThreads = kNumLoaderWarps * 32;
 constexpr int kLoaderRegs = 160;       // 8 x 32 x (160-128) = 8192 registers taken ...
 constexpr int kIdleRegs = 64;          // ... from 4 x 32 x (128-64) = 8192 released
 constexpr int kNumThreads = kNumWarps * 32;  // 512
 constexpr int kNumKvGroups = 2;        // hand-overs per tile from the loaders to the MMA thread
 constexpr int kQTmemChunks = 4;        // Q chunks (64 columns each) held in tensor memory as the A operand
 constexpr int kTmemCols = 512;
-constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P (BF16) overwrites the first 32 of its S
+constexpr int kTmemS = 0;              // two S accumulators of 64 columns; P overwrites the first 32 of its S
 constexpr int kTmemO = 128;            // O accumulator: 256 columns
-constexpr int kTmemQ = 384;            // Q chunks 0..3 as packed BF16: 4 x 32 columns
-constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr int kTmemQ = 384;            // Q chunks 0..3 as packed 16-bit values: 4 x 32 columns
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // 2 s
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; O is rescaled only when the max grows by more
+constexpr int kItemWords = 8;          // int32 words per work item of a schedule
+constexpr int kResolveWarp = 14;       // resolves the entries of the tiles ahead of the loaders
+constexpr int kRing = 6;               // tiles the resolver may be ahead of the loaders' fetches
 
 enum SourceKind : int {
     kSrcCsa = 0,   // index list + block table, packed 656-byte entries
@@ -90,6 +103,9 @@ enum StatusCode : int {
     kStatusWaitPFull = 4,
     kStatusWaitOFull = 5,
     kStatusWaitQ = 6,
+    kStatusBadIndex = 7,       // an index, length or block-table value pointed outside the cache: entry left out, not read
+    kStatusWaitEpilogue = 8,
+    kStatusWaitResolver = 9,
 };
 
 struct DecodeArgs {
@@ -101,6 +117,7 @@ struct DecodeArgs {
     int win_cap;         // HCA
     int num_splits;
     float scale_log2;    // sm_scale * log2(e)
+    long long num_pages; // pages in kv_pool: block-table values outside [0, num_pages) are not followed
     const __nv_bfloat16* q;
     const uint8_t* kv_pool;
     const int32_t* block_table;
@@ -112,12 +129,18 @@ struct DecodeArgs {
     const float* attn_sink;
     __nv_bfloat16* out;
     float* lse;
-    float* partial_o;
+    float* partial_o;            // split partials, stored as BF16 (the area is sized for FP32)
     float* partial_lse;
     int32_t* status;
-    int partial_f32;             // split partials as FP32 (default: BF16 in the same workspace)
-    int dbg;                     // profiling aid: bit1 no L2 prefetch
-    unsigned long long* trace;   // optional profiling aid: block (0,0,0) records phase times here
+    // schedule (sched.cuh): null = one item per block, named by the grid position
+    const int32_t* sched_pair_begin;   // [pairs + 1]: first item of every block pair
+    const int32_t* sched_items;        // [items][kItemWords]
+#ifdef DSV4_TRACE
+    unsigned long long* trace;         // development builds only: block 0 stores %globaltimer values here, 1024 slots per role
+#endif
+    unsigned long long wait_ns;        // limit of every bounded wait
+    int dbg_drop_tile;                 // test aid (-1 = off): the loaders withhold the hand-over of the block's tile with this
+                                       // running number, so that a bounded wait runs out and the error path can be checked
     // reference layout planes (kSrcRef)
     const uint8_t* ref_kc;  const uint8_t* ref_kc_s;  const __nv_bfloat16* ref_kc_rope;
     const uint8_t* ref_ks;  const uint8_t* ref_ks_s;  const __nv_bfloat16* ref_ks_rope;
@@ -132,6 +155,15 @@ struct DecodeArgs {
     int64_t pg_num_pages, pg_swa_num_pages;
 };
 
+// One unit of work of a block: tiles [tile0, tile0 + ntiles) of row n for head group hg.
+struct Item {
+    int n, b, hg;
+    int tile0, ntiles;
+    int n_tok;        // entries of the row that take part (index-list slots in use, or kv_len + win_len)
+    int kv_len_n;     // CSA: causal bound on index values; HCA: entries read through the block table
+    int slot;         // < 0: the item is the whole row, write out / lse; else the partial slot to write
+};
+
 template <int NCHUNK>
 struct SmemLayout {
     static constexpr int kQSmemChunks = NCHUNK - kQTmemChunks;      // Q chunks kept in shared memory
@@ -140,32 +172,46 @@ struct SmemLayout {
     static constexpr int kQOff = 0;
     static constexpr int kKvOff = kQBytes;                          // two stages
     static constexpr int kMiscOff = kKvOff + 2 * kKvStageBytes;
-    static constexpr int kMiscBytes = 512;
+    static constexpr int kMiscBytes = 2048;
     static constexpr int kTotal = kMiscOff + kMiscBytes + 1024;     // + slack to align the base to 1024
-    // the Q chunks bound for tensor memory are staged (as swizzled 16 KB chunks) in KV stage 1,
-    // which the loaders do not touch before the copy to tensor memory has finished
-    static constexpr int kQStageOff = kKvOff + kKvStageBytes;
     static_assert(kQTmemChunks * kQChunkBytes <= kKvStageBytes, "Q staging must fit in one KV stage");
+    // epilogue staging inside one KV stage: per warp 32 rows of kEpiCols BF16 + 16 bytes; all 256 value columns at
+    // once where the stage is large enough, else 128 at a time
+    static constexpr int kEpiPasses = (kNumSoftmaxWarps * 32 * (kDvHalf * 2 + 16) <= kKvStageBytes) ? 1 : 2;
+    static constexpr int kEpiCols = kDvHalf / kEpiPasses;
+    static constexpr int kEpiPitch = kEpiCols * 2 + 16;
+    static constexpr int kEpiWarpBytes = 32 * kEpiPitch;
+    static_assert(kNumSoftmaxWarps * kEpiWarpBytes <= kKvStageBytes, "epilogue staging must fit in one KV stage");
+};
+
+// What the resolver hands the loaders for one tile.
+struct TileSlot {
+    uint32_t id[kTileN];      // per entry: bit 31 = takes part, bit 30 = second pool (window), low bits = record number
+    uint64_t mask;            // bit t = entry t takes part
+    uint32_t meta;            // row | head group << 16 | first tile of its item << 24 | last << 25 | bit 31: a tile at all
+    uint32_t pad;
 };
 
 struct SmemMisc {
-    uint64_t bar_kv_full[2][10];   // [stage][chunk]: chunk written by all loader warps
+    TileSlot ring[kRing];
+    uint64_t bar_res_full[kRing];    // slot written by the resolver
+    uint64_t bar_res_empty[kRing];   // slot read by all loader warps
+    uint64_t bar_kv_full[2][kNumKvGroups];   // [stage][group]: group written by all loader warps
     uint64_t bar_kv_free[2];
     uint64_t bar_s_full[2];
     uint64_t bar_p_full[2];
-    uint64_t bar_o_full;
-    uint64_t bar_q_full;      // Q tile landed in shared memory (TMA transaction count)
-    uint64_t bar_q_ready;     // Q chunks copied to tensor memory, staging area released
+    uint64_t bar_o_full;      // per item: all P.V of the item have completed
+    uint64_t bar_q_full;      // per item: Q chunks of the item landed in shared memory (TMA transaction count)
+    uint64_t bar_q_ready;     // per item: Q in tensor memory, shared-memory chunks converted
+    uint64_t bar_tmem;        // tensor memory allocated, its address in tmem_base
+    uint64_t bar_q_copied;    // per item: every loader warp has copied its share of Q out of the staging area
     uint64_t valid_mask[2];   // per stage: bit t = entry t of the tile takes part in the softmax
     uint32_t tmem_base;
     uint32_t pad;
-    // cluster-pair kernel: per stage, byte i = 4-bit mask of tile rows 4 i .. 4 i + 3 (written by the
-    // loader warp that owns them, in either block of the pair)
-    alignas(16) uint8_t valid_bytes[2][16];
-    uint64_t bar_loc[2][4];   // [stage][span]: this block's loader warps have written their half of chunks 2 span, 2 span + 1 (span 3: and the RoPE tail)
+    volatile uint32_t epi_done[kNumSoftmaxWarps];   // items whose epilogue this softmax warp has finished (staging area free again)
 };
 
-__device__ __forceinline__ void report_timeout(int32_t* status, int code, int role, int tile) {
+__device__ __forceinline__ void report_status(int32_t* status, int code, int role, int tile) {
     if (status != nullptr) {
         if (atomicCAS(status, 0, code) == 0) {
             status[1] = int(blockIdx.x) | (int(blockIdx.y) << 8) | (int(blockIdx.z) << 20);
@@ -175,18 +221,16 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int code, int ro
     }
 }
 
-// Profiling aid: block (0,0,0) stores %globaltimer values, 1024 slots per role
-// (0 softmax, 1 MMA, 2 loader, 3 block phases).
+// Development builds (-DDSV4_TRACE): block 0 records when its roles pass their pipeline points
+// (role 0 softmax, 1 Q.K^T issue, 2 loader warp 0, 3 P.V issue).  Compiled out of the product.
+#ifdef DSV4_TRACE
 __device__ __forceinline__ void trace_mark(const DecodeArgs& a, int role, int slot) {
-    if (a.trace != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && slot < 1024)
+    if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 1024)
         a.trace[role * 1024 + slot] = ptx::globaltimer_ns();
 }
-
-// Start (which = 0) and end (1) time of every block, in the last quarter of the trace buffer.
-__device__ __forceinline__ void trace_block(const DecodeArgs& a, int which) {
-    const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-    if (a.trace != nullptr && lin < 240) a.trace[3 * 1024 + 512 + 2 * lin + which] = ptx::globaltimer_ns();
-}
+#else
+__device__ __forceinline__ void trace_mark(const DecodeArgs&, int, int) {}
+#endif
 
 // Two FP8 e4m3 bytes sitting in bits [15:8] and [31:24] of `r` -> two BF16 bit
 // patterns whose values are the FP8 values times 2^-120 (the e4m3 exponent and
@@ -224,130 +268,141 @@ __device__ __forceinline__ void dequant4_f16(uint32_t w, __half2 scale2, uint32_
 // contiguous bytes: measured on this part, an SM pulls records about 1.6 times
 // faster in this shape than with 64 bytes per entry per instruction, and the
 // record fetch is what the loader warps spend most of their time on.
-//
-// G = 2 groups (8 entries per warp) in the ordinary kernel; G = 1 (4 entries per warp) when the
-// two blocks of a cluster pair share the work: each block then fetches and dequantises half of
-// every tile and forwards it to the other block.
-template <int SRC, int G = 2>
+template <int SRC>
 struct LoaderRegs {
-    uint4 lat[G][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
-    uint4 rope[G];           // [group]: RoPE 16-byte column lane%8 of that entry
-    uint32_t sc[G][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
+    uint4 lat[2][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
+    uint4 rope[2];           // [group]: RoPE 16-byte column lane%8 of that entry
+    uint32_t sc[2][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
     uint32_t vmask;          // bit i = entry i of this warp takes part (same in all lanes)
 };
 
-// Where an entry lives: for the packed layouts the address of its 656-byte
-// record; for the reference layout its row number in the plane, with bit 62 set
-// for the sliding-window planes.  Lanes 0..7 of a loader warp resolve the warp's
-// 8 entries one tile ahead of the data loads, so that the index -> block table
-// -> row dependency chain is off the critical path.
+// Where an entry lives, as a 32-bit record number with bit 31 = "takes part" and bit 30 = "second pool"
+// (the window buffer / the sliding-window planes or pages): for the packed layout the number of its
+// 656-byte record in the pool (page * 64 + slot) or in the window buffer (request * win_cap + row); for
+// packed reference pages page << 6 | slot; for the reference planes the row number in the plane.  The
+// resolver warp works these out several tiles ahead of the data loads, in stages, so that no stage uses
+// the result of a load issued in the same step: the index -> block table -> record chain is off the
+// critical path.
+constexpr uint32_t kIdValid = 1u << 31, kIdSecond = 1u << 30, kIdNumber = (1u << 30) - 1u;
+
+// What a tile's position in its row needs to be resolved (the same in all lanes of a warp).
+struct TileCtx {
+    int n, b;
+    int n_tok, kv_len_n;
+    int v0;              // first entry of the tile in its row
+    uint32_t meta;       // row | head group << 16 | first tile of its item << 24 | last tile << 25 | bit 31: a tile at all
+};
+constexpr uint32_t kMetaFirst = 1u << 24, kMetaLast = 1u << 25, kMetaTile = 1u << 31;
+
+// A resolution in flight: the block-table value requested (not yet looked at) and what is known already.
+struct PendingId {
+    int page;          // block-table value on its way; kNoPage: `id` is final
+    uint32_t id;       // paged: kIdValid | second pool | slot in the page;  otherwise the final record number
+};
+constexpr int kNoPage = -2;
+
+// Stage 1 (CSA only): the index-list value of entry `ent` of the tile, -1 where there is none.
+__device__ __forceinline__ int resolve_index(const DecodeArgs& a, const TileCtx& c, int ent) {
+    const int v = c.v0 + ent;
+    if ((c.meta & kMetaTile) && v < c.n_tok) return __ldg(a.indices + int64_t(c.n) * a.topk + v);
+    return -1;
+}
+
+// Stage 2: issue the block-table load (where there is one).  `e` is the index-list value (CSA).  An entry
+// whose page slot lies outside the block table, or whose window row lies outside the window buffer, is
+// reported and left out; nothing is read through it.
 template <int SRC>
-__device__ __forceinline__ unsigned long long loader_resolve(const DecodeArgs& a, int b, int n, int v, int n_tok,
-                                                             int kv_len_n, bool& valid) {
-    valid = v < n_tok;
-    unsigned long long key = 0;
+__device__ __forceinline__ PendingId resolve_issue(const DecodeArgs& a, const TileCtx& c, int e, int ent) {
+    PendingId p{kNoPage, 0u};
+    const int v = c.v0 + ent;
+    const bool in_row = (c.meta & kMetaTile) && v < c.n_tok;
     if constexpr (SRC == kSrcCsa) {
-        int e = -1;
-        if (valid) e = __ldg(a.indices + int64_t(n) * a.topk + v);
-        valid = (e >= 0) && (e < kv_len_n);
-        if (valid) {
-            const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (e >> 6));
-            key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (e & 63)) * 656);
+        if (e >= 0 && e < c.kv_len_n) {
+            if ((e >> 6) < a.max_pages) {
+                p.page = __ldg(a.block_table + int64_t(c.b) * a.max_pages + (e >> 6));
+                p.id = kIdValid | uint32_t(e & 63);
+            } else {
+                report_status(a.status, kStatusBadIndex, 4, e);
+            }
         }
     } else if constexpr (SRC == kSrcHca) {
-        if (valid) {
-            if (v < kv_len_n) {
-                const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (v >> 6));
-                key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (v & 63)) * 656);
+        if (in_row) {
+            if (v < c.kv_len_n) {
+                if ((v >> 6) < a.max_pages) {
+                    p.page = __ldg(a.block_table + int64_t(c.b) * a.max_pages + (v >> 6));
+                    p.id = kIdValid | uint32_t(v & 63);
+                } else {
+                    report_status(a.status, kStatusBadIndex, 4, v);
+                }
+            } else if (v - c.kv_len_n < a.win_cap) {
+                p.id = kIdValid | kIdSecond | uint32_t(c.b * a.win_cap + (v - c.kv_len_n));
             } else {
-                key = reinterpret_cast<unsigned long long>(a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656);
+                report_status(a.status, kStatusBadIndex, 4, v);
             }
         }
     } else if constexpr (SRC == kSrcRefPaged) {
-        // key = address of the token's 576 data bytes (a multiple of 64) | slot of the token in its page
         // a token outside its block table, or a table value outside the pool, is left out of the
         // softmax instead of being read
-        if (valid) {
+        if (in_row) {
             const int slot_mask = (1 << a.pg_page_shift) - 1;
-            const bool swa = v >= kv_len_n;
-            const int w = swa ? v - kv_len_n : v;
+            const bool swa = v >= c.kv_len_n;
+            const int w = swa ? v - c.kv_len_n : v;
             const uint8_t* pool = swa ? a.pg_swa : a.pg_kv;
             const int32_t* table = swa ? a.pg_swa_table : a.block_table;
             const int cols = swa ? a.pg_swa_max_pages : a.max_pages;
-            const int64_t pages = swa ? a.pg_swa_num_pages : a.pg_num_pages;
-            valid = pool != nullptr && (w >> a.pg_page_shift) < cols;
-            if (valid) {
-                const int page = __ldg(table + int64_t(b) * cols + (w >> a.pg_page_shift));
-                valid = page >= 0 && page < pages;
-                if (valid)
-                    key = reinterpret_cast<unsigned long long>(pool + int64_t(page) * a.pg_page_bytes + (w & slot_mask) * 576) |
-                          (unsigned long long)(w & slot_mask);
+            if (pool != nullptr && (w >> a.pg_page_shift) < cols) {
+                p.page = __ldg(table + int64_t(c.b) * cols + (w >> a.pg_page_shift));
+                p.id = kIdValid | (swa ? kIdSecond : 0u) | uint32_t(w & slot_mask);
             }
         }
     } else {
-        if (valid) {
-            key = (v < a.ref_m_cur) ? (unsigned long long)(int64_t(b) * a.ref_m_cur + v)
-                                    : ((unsigned long long)(int64_t(b) * a.ref_swa_len + (v - a.ref_m_cur)) | (1ull << 62));
-        }
+        if (in_row)
+            p.id = kIdValid | ((v < a.ref_m_cur) ? uint32_t(c.b * a.ref_m_cur + v)
+                                                 : (uint32_t(c.b * a.ref_swa_len + (v - a.ref_m_cur)) | kIdSecond));
     }
-    return key;
+    return p;
 }
 
-// Two entries at once, with the two chains of dependent loads side by side.
+// Stage 3 (a step later, when the block-table value has arrived): the record number.  A table value
+// outside the pool is reported and the entry left out.
 template <int SRC>
-__device__ __forceinline__ void loader_resolve2(const DecodeArgs& a, int b, int n, int va, int ntok_a, int vb, int ntok_b,
-                                                int kv_len_n, unsigned long long& key_a, bool& valid_a,
-                                                unsigned long long& key_b, bool& valid_b) {
-    if constexpr (SRC == kSrcCsa) {
-        valid_a = va < ntok_a;
-        valid_b = vb < ntok_b;
-        const int ea = valid_a ? __ldg(a.indices + int64_t(n) * a.topk + va) : -1;
-        const int eb = valid_b ? __ldg(a.indices + int64_t(n) * a.topk + vb) : -1;
-        valid_a = (ea >= 0) && (ea < kv_len_n);
-        valid_b = (eb >= 0) && (eb < kv_len_n);
-        const int pa = valid_a ? __ldg(a.block_table + int64_t(b) * a.max_pages + (ea >> 6)) : 0;
-        const int pb = valid_b ? __ldg(a.block_table + int64_t(b) * a.max_pages + (eb >> 6)) : 0;
-        key_a = valid_a ? reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(pa) * 64 + (ea & 63)) * 656) : 0ull;
-        key_b = valid_b ? reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(pb) * 64 + (eb & 63)) * 656) : 0ull;
+__device__ __forceinline__ uint32_t resolve_finish(const DecodeArgs& a, const PendingId& p) {
+    if (p.page == kNoPage || !(p.id & kIdValid)) return p.id;
+    if constexpr (SRC == kSrcRefPaged) {
+        const int64_t pages = (p.id & kIdSecond) ? a.pg_swa_num_pages : a.pg_num_pages;
+        if (p.page < 0 || p.page >= pages) return 0u;
+        return (p.id & (kIdValid | kIdSecond)) | (uint32_t(p.page) << 6) | (p.id & 63u);
     } else {
-        key_a = loader_resolve<SRC>(a, b, n, va, ntok_a, kv_len_n, valid_a);
-        key_b = loader_resolve<SRC>(a, b, n, vb, ntok_b, kv_len_n, valid_b);
+        if (p.page < 0 || (long long)p.page >= a.num_pages) {
+            report_status(a.status, kStatusBadIndex, 4, p.page);
+            return 0u;
+        }
+        return kIdValid | (uint32_t(p.page) * 64u + (p.id & 63u));
     }
 }
 
-// Warp-wide: resolve the 8 entries [v0, v0+8) (lanes 0..7), return the key in
-// those lanes and the valid mask in all lanes.
-template <int SRC, int E = 8>
-__device__ __forceinline__ unsigned long long loader_resolve_warp(const DecodeArgs& a, int b, int n, int v0, int lane,
-                                                                  int n_tok, int kv_len_n, uint32_t& vmask) {
-    bool valid = false;
-    unsigned long long key = 0;
-    if (lane < E) key = loader_resolve<SRC>(a, b, n, v0 + lane, n_tok, kv_len_n, valid);
-    vmask = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
-    return key;
-}
-
-// Issue the loads of one tile for this lane's two entries (keys held by lanes 0..7).
-template <int SRC, int G>
-__device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long long key, uint32_t vmask, int lane,
-                                             LoaderRegs<SRC, G>& r) {
+// Issue the loads of one tile for this lane's two entries (record numbers id[0], id[1]).
+template <int SRC>
+__device__ __forceinline__ void loader_fetch(const DecodeArgs& a, const uint32_t (&id)[2], uint32_t vmask, int lane,
+                                             LoaderRegs<SRC>& r) {
     r.vmask = vmask;
     const int piece = lane & 7;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < 2; ++g) {
         const int i = 4 * g + (lane >> 3);
-        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
         if (!((vmask >> i) & 1u)) continue;
+        const uint32_t num = id[g] & kIdNumber;
+        const bool second = (id[g] & kIdSecond) != 0u;
         if constexpr (!is_ref_layout(SRC)) {
-            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
+            const uint8_t* row = (second ? a.win_pool : a.kv_pool) + int64_t(num) * 656;
 #pragma unroll
             for (int j = 0; j < 4; ++j) r.lat[g][j] = ptx::ldg_nc_v4(row + j * 128 + piece * 16);
             const uint4 s4 = ptx::ldg_nc_v4(row + 512);
             r.sc[g][0] = s4.x;  r.sc[g][1] = s4.y;  r.sc[g][2] = s4.z;  r.sc[g][3] = s4.w;
             r.rope[g] = ptx::ldg_nc_v4(row + 528 + piece * 16);
         } else if constexpr (SRC == kSrcRefPaged) {
-            const int slot = int(k & 63ull);
-            const uint8_t* lp = reinterpret_cast<const uint8_t*>(k & ~63ull);
+            const int slot = int(num & 63u);
+            const uint8_t* lp = (second ? a.pg_swa : a.pg_kv) + int64_t(num >> 6) * a.pg_page_bytes + slot * 576;
             // the page's scale area starts after its page_size tokens: 8 bytes per token
             const uint8_t* sp = lp + int64_t((1 << a.pg_page_shift) - slot) * 576 + slot * 8;
 #pragma unroll
@@ -357,11 +412,10 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long 
             r.sc[g][0] = s2.x;  r.sc[g][1] = s2.y;
             r.rope[g] = ptx::ldg_nc_v4(lp + 448 + piece * 16);
         } else {
-            const bool swa = (k >> 62) & 1ull;
-            const int64_t e = int64_t(k & ~(1ull << 62));
-            const uint8_t* lp = (swa ? a.ref_ks : a.ref_kc) + e * 448;
-            const uint8_t* sp = (swa ? a.ref_ks_s : a.ref_kc_s) + e * 7;
-            const uint8_t* rp = reinterpret_cast<const uint8_t*>(swa ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
+            const int64_t e = int64_t(num);
+            const uint8_t* lp = (second ? a.ref_ks : a.ref_kc) + e * 448;
+            const uint8_t* sp = (second ? a.ref_ks_s : a.ref_kc_s) + e * 7;
+            const uint8_t* rp = reinterpret_cast<const uint8_t*>(second ? a.ref_ks_rope : a.ref_kc_rope) + e * 128;
 #pragma unroll
             for (int j = 0; j < 3; ++j) r.lat[g][j] = ptx::ldg_nc_v4(lp + j * 128 + piece * 16);
             // the last span holds only chunk 6 (bytes 384..447 of the 448-byte row)
@@ -377,26 +431,20 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, unsigned long 
     }
 }
 
-// Pull the 656-byte records of the warp's 8 entries (keys in lanes 0..7) into L2
-// ahead of the loads: lane/4 picks the entry, lane%4 the 128-byte piece.
+// Pull the record of one entry into L2 ahead of the loads (the packed layouts: one contiguous record).
 template <int SRC>
-__device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint32_t vmask, int lane) {
+__device__ __forceinline__ void prefetch_record_l2(const DecodeArgs& a, uint32_t id) {
+    if (!(id & kIdValid)) return;
+    const uint32_t num = id & kIdNumber;
+    const bool second = (id & kIdSecond) != 0u;
     if constexpr (!is_ref_layout(SRC)) {
-        const int i = lane >> 2;
-        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-        if ((vmask >> i) & 1u) {
-            const uint8_t* row = reinterpret_cast<const uint8_t*>(k);
-            ptx::prefetch_l2(row + (lane & 3) * 128);
-            if ((lane & 3) < 2) ptx::prefetch_l2(row + 512 + (lane & 3) * 128);
-        }
+        const uint8_t* row = (second ? a.win_pool : a.kv_pool) + int64_t(num) * 656;
+#pragma unroll
+        for (int j = 0; j < 6; ++j) ptx::prefetch_l2(row + j * 128);
     } else if constexpr (SRC == kSrcRefPaged) {
-        const int i = lane >> 2;
-        const unsigned long long k = __shfl_sync(0xFFFFFFFFu, key, i);
-        if ((vmask >> i) & 1u) {
-            const uint8_t* lp = reinterpret_cast<const uint8_t*>(k & ~63ull);
-            ptx::prefetch_l2(lp + (lane & 3) * 128);
-            if ((lane & 3) == 0) ptx::prefetch_l2(lp + 512);
-        }
+        const uint8_t* lp = (second ? a.pg_swa : a.pg_kv) + int64_t(num >> 6) * a.pg_page_bytes + int(num & 63u) * 576;
+#pragma unroll
+        for (int j = 0; j < 5; ++j) ptx::prefetch_l2(lp + j * 128);
     }
 }
 
@@ -406,13 +454,13 @@ __device__ __forceinline__ void loader_prefetch_l2(unsigned long long key, uint3
 // One store instruction writes 4 rows x 2 chunks x 4 column positions, arranged
 // (see the end of the function) so that it needs as few shared-memory wavefronts
 // as 512 bytes can: four.
-template <int NCHUNK, int SRC, int G>
-__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC, G>& r, int j) {
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r, int j) {
     const uint32_t piece = uint32_t(lane & 7);
     const uint32_t c = 2u * uint32_t(j) + (piece >> 2);        // this lane's chunk
     const uint32_t p = piece & 3u;                             // 16 latent bytes -> 16-byte columns 2p, 2p+1
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < 2; ++g) {
         const int i = 4 * g + (lane >> 3);
         const int t = t0 + i;
         const bool valid = (r.vmask >> i) & 1u;
@@ -421,15 +469,6 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
         if (is_ref_layout(SRC) && c >= uint32_t(NCHUNK - 1)) continue;   // reference layout: span 3 ends with chunk 6
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
         if (valid) {
-            float s120;
-            if constexpr (is_ref_layout(SRC)) {
-                // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
-                // scale, as in the reference's dequantiser
-                const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
-                s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
-            } else {
-                s120 = __uint_as_float(r.sc[g][j]) * 1.329227995784916e36f;   // one FP32 scale per 128 elements; x 2^120
-            }
             const uint4 x = r.lat[g][j];
             if constexpr (use_f16(SRC)) {
                 // scales above 146 would take 448 x scale past FP16's largest finite value: such blocks saturate
@@ -439,6 +478,10 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
                 dequant4_f16(x.z, scale2, w1.x, w1.y);
                 dequant4_f16(x.w, scale2, w1.z, w1.w);
             } else {
+                // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
+                // scale, as in the reference's dequantiser
+                const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
+                const float s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
                 const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
                 dequant4(x.x, scale2, w0.x, w0.y);
                 dequant4(x.y, scale2, w0.z, w0.w);
@@ -457,11 +500,11 @@ __device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int la
 }
 
 // The RoPE tail (chunk NCHUNK-1, a plain copy): 4 rows x 8 columns per store instruction.
-template <int NCHUNK, int SRC, int G>
-__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC, G>& r) {
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r) {
     const uint32_t piece = uint32_t(lane & 7);
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < 2; ++g) {
         const int i = 4 * g + (lane >> 3);
         const int t = t0 + i;
         const bool valid = (r.vmask >> i) & 1u;
@@ -475,32 +518,34 @@ __device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int la
     }
 }
 
-// BF16 -> FP16 in place over the Q chunks that stay in shared memory, one share per thread of
-// the softmax and loader warps (threads 0 .. kStageThreads-1), then the proxy fence that makes
-// the result visible to the MMAs' reads.  Element-wise, so the swizzled layout is untouched.
+// BF16 -> FP16 in place over the Q chunks that stay in shared memory, one share per loader
+// thread, then the proxy fence that makes the result visible to the MMAs' reads.
+// Element-wise, so the swizzled layout is untouched.
 template <int BYTES>
-__device__ __forceinline__ void convert_q_smem(uint32_t q_base, int tid) {
-    for (int i = tid; i < BYTES / 16; i += kStageThreads) {
+__device__ __forceinline__ void convert_q_smem(uint32_t q_base, int ltid) {
+#pragma unroll 5
+    for (int i = ltid; i < BYTES / 16; i += kLoaderThreads) {
         uint4 x = ptx::lds_v4(q_base + uint32_t(i) * 16u);
         x.x = ptx::bf16x2_to_f16x2(x.x);  x.y = ptx::bf16x2_to_f16x2(x.y);
         x.z = ptx::bf16x2_to_f16x2(x.z);  x.w = ptx::bf16x2_to_f16x2(x.w);
         ptx::sts_v4(q_base + uint32_t(i) * 16u, x);
     }
-    ptx::fence_proxy_async_smem();
 }
 
-// Copy Q chunks [g0, g1) of the 32 head rows of lane quarter `warp % 4` from the staging area to
-// tensor memory: head row = tensor-memory lane, two 16-bit values per 32-bit column, in K order
-// (the A-operand layout of the MMA); converted to FP16 on the way when the kernel runs on FP16.
+// Copy Q chunks g0 and g0 + 1 of the 32 head rows of lane quarter `lw % 4` from their staging area (the
+// swizzled 16 KB chunks the TMA wrote) to tensor memory: head row = tensor-memory lane, two 16-bit values per
+// 32-bit column, in K order (the A-operand layout of the MMA); converted to FP16 on the way when the kernel
+// runs on FP16.
 template <bool F16>
-__device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint32_t tmem, int warp, int lane, int g0, int g1) {
-    const int quarter = warp & 3;
+__device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint32_t tmem, int lw, int lane) {
+    const int quarter = lw & 3;
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const uint32_t srow = stage_base + uint32_t(r) * 128u;
     const uint32_t sw = uint32_t(r & 7);
-#pragma unroll 1
-    for (int g = g0; g < g1; ++g) {
+    const int g0 = 2 * (lw >> 2);
+#pragma unroll
+    for (int g = g0; g < g0 + 2; ++g) {
         uint32_t w32[32];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -515,18 +560,33 @@ __device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint3
     }
 }
 
-// PAIR: launched as clusters of two blocks along x - the two blocks of a row and head group (the two
-// halves of the value columns).  Both need the whole dequantised tile, so each fetches and
-// dequantises half of its entries into its own stage, and a forwarder warp sends that half on to
-// the same place in the other block's stage by bulk copies through distributed shared memory;
-// everything after that is as in the ordinary kernel.  Bit-identical results; measured slower
-// than the ordinary kernel (the copy sits in the two-stage ring), so it is a selectable variant.
-template <int NCHUNK, int SRC, bool PAIR = false>
+// The Q rows of an item pulled into L2 ahead of their use: 128 rows x NCHUNK x 128 bytes, spread over the calling threads.
+template <int NCHUNK>
+__device__ __forceinline__ void prefetch_q_l2(const DecodeArgs& a, int n, int hg, int t, int nthreads) {
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.q + (int64_t(n) * a.H + hg * kHeadsPerCta) * (64 * NCHUNK));
+    const int rows = min(kHeadsPerCta, a.H - hg * kHeadsPerCta);
+    for (int l = t; l < rows * NCHUNK; l += nthreads) ptx::prefetch_l2(base + int64_t(l) * 128);
+}
+
+// The row lengths of an item, from the per-row length arrays.
+template <int SRC>
+__device__ __forceinline__ void row_lengths(const DecodeArgs& a, int n, int& n_tok, int& kv_len_n) {
+    if constexpr (SRC == kSrcCsa) {
+        const int raw = (a.topk_len != nullptr) ? __ldg(a.topk_len + n) : a.topk;
+        n_tok = min(max(raw, 0), a.topk);
+        kv_len_n = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
+    } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
+        kv_len_n = max(__ldg(a.kv_len + n), 0);
+        n_tok = kv_len_n + max(__ldg(a.win_len + n), 0);
+    } else {
+        kv_len_n = a.ref_m_cur;
+        n_tok = a.ref_m_cur + a.ref_swa_len;
+    }
+}
+
+template <int NCHUNK, int SRC>
 __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid_constant__ DecodeArgs a) {
-    static_assert(!PAIR || !is_ref_layout(SRC), "the cluster-pair variant is written for the packed layout");
     using L = SmemLayout<NCHUNK>;
-    constexpr int G = PAIR ? 1 : 2;            // groups of 4 entries per loader warp and tile
-    constexpr int E = 4 * G;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -538,310 +598,262 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int half = blockIdx.x & 1;
-    const int hg = blockIdx.x >> 1;
-    const int n = blockIdx.y;                // row = b * s_q + query token
-    const int split = blockIdx.z;
-    const int b = n / a.s_q;
-    // the other block of the pair sees this block's shared memory at (address + peer_delta)
-    const uint32_t peer_delta = PAIR ? ptx::mapa(smem_base, uint32_t(half ^ 1)) - smem_base : 0u;
+    const bool sched = a.sched_pair_begin != nullptr;
+    const int rows = a.B * a.s_q;
+    const unsigned long long wait_ns = a.wait_ns;
 
-    // The per-row lengths are requested here and used only after the set-up below: the Q load and the
-    // barrier initialisation do not wait for them.
-    int raw_len0 = 0, raw_len1 = 0;
-    if constexpr (SRC == kSrcCsa) {
-        raw_len0 = (a.topk_len != nullptr) ? __ldg(a.topk_len + n) : a.topk;
-        raw_len1 = (a.kv_len != nullptr) ? __ldg(a.kv_len + n) : 0x7FFFFFFF;
-    } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
-        raw_len0 = __ldg(a.kv_len + n);
-        raw_len1 = __ldg(a.win_len + n);
+    // ── this block's items ──
+    int item_begin = 0, n_items = 1;
+    if (sched) {
+        const int pair = blockIdx.x >> 1;
+        item_begin = __ldg(a.sched_pair_begin + pair);
+        n_items = __ldg(a.sched_pair_begin + pair + 1) - item_begin;
     }
-    if (tid == 32) {
-        // first link of the loaders' chains of dependent loads (index list -> block table -> entries): into L2 now
-        if constexpr (SRC == kSrcCsa) {
-            const int32_t* idx = a.indices + int64_t(n) * a.topk;
-            const int lines = min((a.topk * 4 + 127) / 128, 8);
-            for (int l = 0; l < lines; ++l) ptx::prefetch_l2(reinterpret_cast<const uint8_t*>(idx) + 128 * l);
+    auto get_item = [&](int k) -> Item {
+        Item it;
+        if (sched) {
+            const int4* rec = reinterpret_cast<const int4*>(a.sched_items + int64_t(item_begin + k) * kItemWords);
+            const int4 r0 = __ldg(rec), r1 = __ldg(rec + 1);
+            it.n = r0.x;  it.hg = r0.y;  it.tile0 = r0.z;  it.ntiles = r0.w;
+            it.slot = r1.x;  it.n_tok = r1.y;  it.kv_len_n = r1.z;
+        } else {
+            it.n = blockIdx.y;  it.hg = blockIdx.x >> 1;
+            row_lengths<SRC>(a, it.n, it.n_tok, it.kv_len_n);
+            const int split = blockIdx.z;
+            const int tiles_total = (it.n_tok + kTileN - 1) / kTileN;
+            const int tiles_per_split = (tiles_total + a.num_splits - 1) / a.num_splits;
+            it.tile0 = min(split * tiles_per_split, tiles_total);
+            it.ntiles = min(it.tile0 + tiles_per_split, tiles_total) - it.tile0;
+            it.slot = a.num_splits > 1 ? split : -1;
         }
-        if constexpr (SRC == kSrcCsa || SRC == kSrcHca || SRC == kSrcRefPaged)
-            ptx::prefetch_l2(a.block_table + int64_t(b) * a.max_pages);
-    }
+        it.b = it.n / a.s_q;
+        return it;
+    };
+    // element index of head row 0 of the item's block of partial rows, and of its partial LSEs
+    auto partial_row0 = [&](const Item& it) -> int64_t {
+        return sched ? int64_t(it.slot) * kHeadsPerCta : (int64_t(it.slot) * rows + it.n) * a.H + it.hg * kHeadsPerCta;
+    };
 
     const uint32_t v_off = uint32_t(half ? 4 : 0) * kKvChunkBytes;   // this block's value columns inside a stage
 
-    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full[0][0]);   // [stage][chunk] at +80*stage + 8*chunk
+    const uint32_t bar_kv_full = ptx::smem_u32(&misc->bar_kv_full[0][0]);   // [stage][group] at +8*kNumKvGroups*stage + 8*group
     const uint32_t bar_kv_free = ptx::smem_u32(&misc->bar_kv_free[0]);
     const uint32_t bar_s_full = ptx::smem_u32(&misc->bar_s_full[0]);
     const uint32_t bar_p_full = ptx::smem_u32(&misc->bar_p_full[0]);
     const uint32_t bar_o_full = ptx::smem_u32(&misc->bar_o_full);
     const uint32_t bar_q_full = ptx::smem_u32(&misc->bar_q_full);
     const uint32_t bar_q_ready = ptx::smem_u32(&misc->bar_q_ready);
+    const uint32_t bar_tmem = ptx::smem_u32(&misc->bar_tmem);
+    const uint32_t bar_q_copied = ptx::smem_u32(&misc->bar_q_copied);
+    constexpr uint32_t kKvFullStride = 8 * kNumKvGroups;
+    const uint32_t bar_res_full = ptx::smem_u32(&misc->bar_res_full[0]);
+    const uint32_t bar_res_empty = ptx::smem_u32(&misc->bar_res_empty[0]);
 
     // ── set-up ──
     if (tid == 0) {
-        trace_mark(a, 3, 0);
-        trace_block(a, 0);
         for (int st = 0; st < 2; ++st) {
-            for (int g = 0; g < kNumKvGroups; ++g)
-                ptx::mbar_init(bar_kv_full + 80 * st + 8 * g, kNumLoaderWarps + (PAIR ? 1 : 0));   // + the other block's forwarder
-            for (int j = 0; j < 4; ++j) ptx::mbar_init(ptx::smem_u32(&misc->bar_loc[st][j]), kNumLoaderWarps);
-            ptx::mbar_init(bar_kv_free + 8 * st, PAIR ? 2 : 1);     // PV commits of both blocks: a stage is refilled in both at once
+            for (int g = 0; g < kNumKvGroups; ++g) ptx::mbar_init(bar_kv_full + kKvFullStride * st + 8 * g, kNumLoaderWarps);
+            ptx::mbar_init(bar_kv_free + 8 * st, 1);
             ptx::mbar_init(bar_s_full + 8 * st, 1);
             ptx::mbar_init(bar_p_full + 8 * st, kNumSoftmaxWarps);
         }
         ptx::mbar_init(bar_o_full, 1);
         ptx::mbar_init(bar_q_full, 1);
-        ptx::mbar_init(bar_q_ready, (PAIR ? 2 : 1) * (kNumSoftmaxWarps + kNumLoaderWarps));
-        ptx::fence_mbar_init();
-        {
-            // (issued whether or not this block has tiles: a block without tiles waits for it before it leaves)
-            // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in
-            // the swizzled operand layout: chunks >= kQTmemChunks at their final place, the others
-            // in the staging area.  Rows past the end of Q read as zero; rows of a following
-            // request (H < 128) are computed but never written out.
-            ptx::mbar_arrive_expect_tx(bar_q_full, uint32_t(NCHUNK) * kQChunkBytes);
-            const int row0 = n * a.H + hg * kHeadsPerCta;
-#pragma unroll
-            for (int c = 0; c < NCHUNK; ++c) {
-                const uint32_t dst = (c < kQTmemChunks) ? smem_base + L::kQStageOff + uint32_t(c) * kQChunkBytes
-                                                        : q_base + uint32_t(c - kQTmemChunks) * kQChunkBytes;
-                ptx::tma_load_2d(dst, &a.q_map, c * 64, row0, bar_q_full);
-            }
+        ptx::mbar_init(bar_q_ready, kNumLoaderWarps);
+        ptx::mbar_init(bar_tmem, 1);
+        ptx::mbar_init(bar_q_copied, kNumLoaderWarps);
+        for (int i = 0; i < kRing; ++i) {
+            ptx::mbar_init(bar_res_full + 8 * i, 1);
+            ptx::mbar_init(bar_res_empty + 8 * i, kNumLoaderWarps);
         }
-        trace_mark(a, 3, 10);
+        for (int w = 0; w < kNumSoftmaxWarps; ++w) misc->epi_done[w] = 0u;
+        ptx::fence_mbar_init();
     }
 
-    // ── this block's tile range ──
-    int n_tok, kv_len_n;
-    if constexpr (SRC == kSrcCsa) {
-        n_tok = min(max(raw_len0, 0), a.topk);
-        kv_len_n = raw_len1;
-    } else if constexpr (SRC == kSrcHca || SRC == kSrcRefPaged) {
-        kv_len_n = max(raw_len0, 0);
-        n_tok = kv_len_n + max(raw_len1, 0);
-    } else {
-        kv_len_n = a.ref_m_cur;
-        n_tok = a.ref_m_cur + a.ref_swa_len;
-    }
-    const int tiles_total = (n_tok + kTileN - 1) / kTileN;
-    const int tiles_per_split = (tiles_total + a.num_splits - 1) / a.num_splits;
-    const int tile0 = min(split * tiles_per_split, tiles_total);
-    const int tile1 = min(tile0 + tiles_per_split, tiles_total);
-    const int ntiles = tile1 - tile0;
-
-    // Block-wide rendezvous.  Every role runs the same number of them (one before the
-    // main loops, one at the exit), each from its own branch.
-    // (PAIR: a rendezvous of both blocks - nothing is written to, and no barrier is arrived on, in
-    // the other block before its barriers are initialised.)
-    auto block_sync = [&]() {
-        ptx::tc_fence_before_sync();
-        if constexpr (PAIR) ptx::cluster_sync(); else __syncthreads();
+    // The barriers are initialised before any role starts.  The tensor-memory address is published through a
+    // barrier of its own, so that the resolver and the loaders are at work while it is being allocated.
+    __syncthreads();
+    auto wait_tmem = [&]() -> bool {
+        const bool w = ptx::mbar_wait(bar_tmem, 0u, wait_ns);
         ptx::tc_fence_after_sync();
+        return w;
     };
-    // Q staging released / Q in tensor memory: in a pair the other block's loaders write into this
-    // block's stage 1 as well, so they are told too.
-    auto arrive_q_ready = [&]() {
-        ptx::mbar_arrive(bar_q_ready);
-        if constexpr (PAIR) ptx::mbar_arrive_cluster(bar_q_ready + peer_delta);
-    };
-    auto wait_q_ready = [&]() {
-        return PAIR ? ptx::mbar_wait_cluster(bar_q_ready, 0u, kWaitTimeoutNs) : ptx::mbar_wait(bar_q_ready, 0u, kWaitTimeoutNs);
-    };
+
+    // Running counters, the same in every role: `gt` counts the tiles the block has gone through over all
+    // its items (tile gt lives in stage gt & 1 and is the (gt >> 1)-th use of that stage's barriers), `qn`
+    // the items that had tiles (the per-item barriers are in their qn-th phase).
 
     if (warp >= kFirstLoaderWarp && warp < kMmaWarp) {
         // ───────────── loader warps ─────────────
-        // Two register sets, one per KV stage: while one tile is dequantised and stored, the
-        // loads of the next one are in flight.  Keys run two tiles ahead of the loads, and the
-        // records they name are pulled into L2 at that point.  The larger register allowance
+        // The tiles of all the block's items form one stream, described tile by tile by the resolver warp (record
+        // numbers, validity mask, tag).  Two register sets: while one tile is dequantised and stored, the loads of
+        // the next one are in flight - also across the boundary between two items.  The larger register allowance
         // holds for this branch only.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kLoaderRegs));
         const int lw = warp - kFirstLoaderWarp;
-        const int row0 = PAIR ? 32 * half + 4 * lw : 8 * lw;      // this warp's E entries: tile rows row0 .. row0+E-1
-        LoaderRegs<SRC, G> regs_a, regs_b;
-        // keys of the tiles two and three ahead of the one being stored (records already
-        // pulled into L2), and of the tile four ahead (resolved, not yet prefetched)
-        unsigned long long key1 = 0, key2 = 0, key3 = 0, key4 = 0;
-        uint32_t vm1 = 0, vm2 = 0, vm3 = 0, vm4 = 0;
-        int e_ahead = -1;        // CSA: this lane's index-list value of the tile resolved next (lanes 0-7)
-        if (lw == 0 && lane == 0) trace_mark(a, 3, 4);
-        if (ntiles > 0) {
-            // one round of dependent loads for the first four tiles: lanes 0-7, 8-15, 16-23, 24-31
-            // (lanes 0-7 also resolve tile 4, as a second chain of loads in flight beside the first)
-            bool valid = false, valid4 = false;
-            const int which = lane >> 3;
-            unsigned long long key, k4;
-            loader_resolve2<SRC>(a, b, n, (tile0 + which) * kTileN + row0 + (lane & 7), (which < ntiles && (lane & 7) < E) ? n_tok : 0,
-                                 (tile0 + 4) * kTileN + row0 + (lane & 7), (4 < ntiles && lane < E) ? n_tok : 0,
-                                 kv_len_n, key, valid, k4, valid4);
-            const uint32_t bal = __ballot_sync(0xFFFFFFFFu, valid);
-            vm4 = __ballot_sync(0xFFFFFFFFu, valid4) & 0xFFu;
-            key4 = k4;
-            if constexpr (SRC == kSrcCsa) {
-                // the index-list values of tile 5 (lanes 0-7), on their way one step before they are needed
-                const int v5 = (tile0 + 5) * kTileN + row0 + lane;
-                if (lane < E && 5 < ntiles && v5 < n_tok) e_ahead = __ldg(a.indices + int64_t(n) * a.topk + v5);
+        const int ltid = tid - kFirstLoaderWarp * 32;
+        const int row0 = 8 * lw;      // this warp's 8 entries: tile rows row0 .. row0+7
+        LoaderRegs<SRC> regs_a, regs_b;
+        uint32_t ma = 0, mb = 0;      // tags of the tiles in the two register sets
+        uint32_t gt = 0, qn = 0;
+        uint32_t pend[2] = {0u, 0u};     // the epilogue (by its running number) that must have released the stage before it is written again
+        bool lok = true;
+
+        // start the loads of tile t of the stream into `regs`; its tag goes to mt (0 past the end of the stream)
+        auto fetch_tile = [&](uint32_t t, LoaderRegs<SRC>& regs, uint32_t& mt) {
+            const uint32_t slot = t % kRing;
+            const bool w = ptx::mbar_wait(bar_res_full + 8 * slot, (t / kRing) & 1u, wait_ns);
+            if (!__all_sync(0xFFFFFFFFu, w)) {
+                report_status(a.status, kStatusWaitResolver, 2, int(t));
+                lok = false;
+                mt = 0u;
+                return;
             }
-            if (lw == 0 && lane == 0) trace_mark(a, 3, 5);
-            vm2 = (bal >> 16) & 0xFFu;
-            vm3 = (bal >> 24) & 0xFFu;
-            key2 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 16);
-            key3 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 24);
-            // Only what the first tile needs goes out before the main loop: the number of loads
-            // an SM keeps in flight is limited, and everything queued here delays tile 0.
-            loader_fetch<SRC>(a, key, bal & 0xFFu, lane, regs_a);
-            if (lw == 0 && lane == 0) trace_mark(a, 3, 6);
-            key1 = __shfl_sync(0xFFFFFFFFu, key, (lane & 7) + 8);   // -> lanes 0..7
-            vm1 = (bal >> 8) & 0xFFu;
+            const TileSlot& ts = misc->ring[slot];
+            mt = ts.meta;
+            if (!(mt & kMetaTile)) return;       // end of the stream (nothing to release: the resolver has stopped)
+            uint32_t id[2];
+            id[0] = ts.id[row0 + (lane >> 3)];
+            id[1] = ts.id[row0 + 4 + (lane >> 3)];
+            const uint32_t vmask = uint32_t(ts.mask >> row0) & 0xFFu;
+            loader_fetch<SRC>(a, id, vmask, lane, regs);
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_res_empty + 8 * slot);
+        };
+        // Only what the first tile needs goes out before the main loop: the number of loads an SM keeps in
+        // flight is limited, and everything queued here delays tile 0.
+        fetch_tile(0u, regs_a, ma);
+        if (!__all_sync(0xFFFFFFFFu, wait_tmem())) {
+            report_status(a.status, kStatusWaitQ, 2, -1);
+            lok = false;
         }
-        if (lw == 0 && lane == 0) trace_mark(a, 3, 7);
-        block_sync();
-        if (lw == 0 && lane == 0) trace_mark(a, 3, 8);
-        if (ntiles > 0) {
-            bool lok = true;
-            {
-                // the loaders' share of the Q set-up, while their first loads are in flight: warps
-                // 4-7 copy chunk 2 to tensor memory, warps 8-11 chunk 3, and (FP16 route) every
-                // thread converts its part of the chunks that stay in shared memory
-                const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
+        const uint32_t tmem = misc->tmem_base;
+
+        // one step: store the tile in `regs` (tag `mt`), then start the loads of the tile after next into the same set
+        auto tile_step = [&](LoaderRegs<SRC>& regs, uint32_t& mt, auto first_tag) {
+            constexpr bool kFirstStep = decltype(first_tag)::value;
+            const uint32_t g = gt;
+            const int st = int(g & 1u);
+            if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g));
+            if (mt & kMetaFirst) {
+                // Q of the item that starts here has been sent for by the MMA thread (TMA, once the previous item's Q.K^T
+                // had completed and this tile's stage was free): the chunks that stay in shared memory land at their
+                // place and are converted there; the chunks that live in tensor memory land in this tile's stage,
+                // which is written only after every loader warp has copied its share out of it.
+                const bool w = ptx::mbar_wait(bar_q_full, qn & 1u, wait_ns);
+                if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn));
                 if (!__all_sync(0xFFFFFFFFu, w)) {
-                    report_timeout(a.status, kStatusWaitQ, 2, tile0);
+                    report_status(a.status, kStatusWaitQ, 2, int(g));
                     lok = false;
                 } else {
-                    const uint32_t tmem_q = misc->tmem_base;
-                    const int g = 2 + (lw >> 2);
-                    copy_q_chunks_to_tmem<use_f16(SRC)>(smem_base + L::kQStageOff, tmem_q, warp, lane, g, g + 1);
-                    if constexpr (use_f16(SRC)) convert_q_smem<L::kQBytes>(q_base, tid);
+                    copy_q_chunks_to_tmem<use_f16(SRC)>(kv_base + uint32_t(st) * L::kKvStageBytes, tmem, lw, lane);
+                    if constexpr (use_f16(SRC)) convert_q_smem<L::kQBytes>(q_base, ltid);
+                    ptx::fence_proxy_async_smem();
                     ptx::tmem_wait_st();
                     ptx::tc_fence_before_sync();
                 }
                 __syncwarp();
-                if (lane == 0) arrive_q_ready();     // also after a time-out, so that nobody waits for this warp
+                if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn) + 1);
+                if (lane == 0) {
+                    ptx::mbar_arrive(bar_q_ready);      // also after a time-out, so that nobody waits for this warp
+                    ptx::mbar_arrive(bar_q_copied);
+                }
+                if (!lok) return;
+                // the staging area is this tile's stage: no loader warp writes it before all have read it
+                if (!__all_sync(0xFFFFFFFFu, ptx::mbar_wait(bar_q_copied, qn & 1u, wait_ns))) {
+                    report_status(a.status, kStatusWaitQ, 2, int(g));
+                    lok = false;
+                    return;
+                }
+                if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn) + 2);
             }
-            auto tile_step = [&](LoaderRegs<SRC, G>& regs, int it) {
-                const int st = it & 1;
-                if (it == 1) {
-                    // stage 1 doubles as the Q staging area until the copy to tensor memory is done
-                    const bool w = wait_q_ready();
-                    if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_timeout(a.status, kStatusWaitQ, 2, tile0 + it);
-                        lok = false;
-                        return;
-                    }
+            if (g >= 2u) {
+                // warp-uniform outcome: the warp-collective operations below need all lanes
+                const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, ((g >> 1) - 1u) & 1u, wait_ns);
+                if (!__all_sync(0xFFFFFFFFu, w)) {
+                    report_status(a.status, kStatusWaitKvFree, 2, int(g));
+                    lok = false;
+                    return;
                 }
-                if (it >= 2) {
-                    // warp-uniform outcome: the warp-collective operations below need all lanes
-                    const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, uint32_t((it >> 1) - 1) & 1u, kWaitTimeoutNs);
-                    if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_timeout(a.status, kStatusWaitKvFree, 2, tile0 + it);
-                        lok = false;
-                        return;
-                    }
+            }
+            if (pend[st] != 0u) {
+                // the stage held the output staging of an earlier item: wait until all four softmax warps are through with it
+                const unsigned long long t0 = ptx::globaltimer_ns();
+                bool free_now = false;
+                while (true) {
+                    free_now = misc->epi_done[0] >= pend[st] && misc->epi_done[1] >= pend[st] &&
+                               misc->epi_done[2] >= pend[st] && misc->epi_done[3] >= pend[st];
+                    if (free_now || ptx::globaltimer_ns() - t0 > wait_ns) break;
                 }
-                if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it);
-                if (it != 0 && !(a.dbg & 2)) {
-                    // the key resolved during the previous step has arrived by now: start pulling
-                    // its records into L2 (using it earlier would stall on the block-table load)
-                    loader_prefetch_l2<SRC>(key4, vm4, lane);
+                if (!__all_sync(0xFFFFFFFFu, free_now)) {
+                    report_status(a.status, kStatusWaitEpilogue, 2, int(g));
+                    lok = false;
+                    return;
                 }
-                if constexpr (PAIR) {
-                    if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_bytes[st][0])[8 * half + lw] = uint8_t(regs.vmask);
-                } else {
-                    if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
-                }
-                // in two groups (chunks 0-3, then the rest with the RoPE tail), so that the QK MMAs of this tile
-                // start while it is still being written; one proxy fence and one arrival per group
-                const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
-                auto group_done = [&](int g) {
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive(bar_kv_full + 80 * st + 8 * g);
-                        if constexpr (PAIR) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][2 * g + 1]));   // the forwarder takes it from here
-                    }
-                };
-                // (pair: the forwarder is told span by span, so that its copies run beside the stores)
-                auto span_done = [&](int j) {
-                    if constexpr (PAIR) {
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&misc->bar_loc[st][j]));
-                    }
-                };
-                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 0);
-                span_done(0);
-                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 1);
-                group_done(0);
-                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 2);
-                span_done(2);
-                loader_store_span<NCHUNK, SRC, G>(kv_st, row0, lane, regs, 3);
-                loader_store_rope<NCHUNK, SRC, G>(kv_st, row0, lane, regs);
-                group_done(1);
-                if (lw == 0 && lane == 0) trace_mark(a, 2, 2 * it + 1);
-                if (it == 0) {
-                    // Tile 0 is complete.  The loads of tile 1 and the records of tiles 2 and 3 are
-                    // requested only here: queued earlier they would hold up the stores above (the
-                    // load/store unit takes about a microsecond to accept a tile's worth of loads).
-                    if (1 < ntiles) loader_fetch<SRC>(a, key1, vm1, lane, regs_b);
-                    loader_prefetch_l2<SRC>(key2, vm2, lane);
-                    loader_prefetch_l2<SRC>(key3, vm3, lane);
-                }
-                // this set is free again: loads of tile it+2, keys of tile it+5
-                if (it + 2 < ntiles) loader_fetch<SRC>(a, key2, vm2, lane, regs);
-                key2 = key3;  vm2 = vm3;
-                key3 = key4;  vm3 = vm4;
-                if constexpr (SRC == kSrcCsa) {
-                    // Tile it+5: its index-list values were requested one step ago, so the ballot below
-                    // does not wait for a load; the block-table load issued here is consumed a step
-                    // later, and the index-list values of tile it+6 are requested now.
-                    const bool valid = e_ahead >= 0 && e_ahead < kv_len_n;       // e_ahead is -1 past the list or the tiles
-                    unsigned long long key = 0;
-                    if (valid) {
-                        const int page = __ldg(a.block_table + int64_t(b) * a.max_pages + (e_ahead >> 6));
-                        key = reinterpret_cast<unsigned long long>(a.kv_pool + (int64_t(page) * 64 + (e_ahead & 63)) * 656);
-                    }
-                    vm4 = __ballot_sync(0xFFFFFFFFu, valid) & 0xFFu;
-                    key4 = key;
-                    const int v6 = (tile0 + it + 6) * kTileN + row0 + lane;
-                    e_ahead = (lane < E && it + 6 < ntiles && v6 < n_tok) ? __ldg(a.indices + int64_t(n) * a.topk + v6) : -1;
-                } else {
-                    key4 = loader_resolve_warp<SRC, E>(a, b, n, (tile0 + it + 5) * kTileN + row0, lane,
-                                                    (it + 5 < ntiles) ? n_tok : 0, kv_len_n, vm4);
-                }
+                __threadfence_block();
+                pend[st] = 0u;
+            }
+            if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 1);
+            if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
+            // in two groups (chunks 0-3, then the rest with the RoPE tail), so that the QK MMAs of this tile
+            // start while it is still being written; one proxy fence and one arrival per group
+            const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
+            const bool drop = a.dbg_drop_tile >= 0 && g == uint32_t(a.dbg_drop_tile);
+            auto group_done = [&](int grp) {
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && !drop) ptx::mbar_arrive(bar_kv_full + kKvFullStride * st + 8 * grp);
             };
-            for (int it = 0; it < ntiles && lok; it += 2) {
-                tile_step(regs_a, it);
-                if (it + 1 < ntiles && lok) tile_step(regs_b, it + 1);
+            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 0);
+            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 1);
+            group_done(0);
+            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 2);
+            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 3);
+            loader_store_rope<NCHUNK, SRC>(kv_st, row0, lane, regs);
+            group_done(1);
+            if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 2);
+            if (mt & kMetaLast) {
+                ++qn;
+                pend[st] = qn;       // the item's output is staged in the stage of its last tile
             }
+            ++gt;
+            if constexpr (kFirstStep) {
+                // The stream's first tile is complete.  The loads of the second are requested only here: queued
+                // earlier they would hold up the stores above (the load/store unit takes about a microsecond to
+                // accept a tile's worth of loads).
+                fetch_tile(1u, regs_b, mb);
+            }
+            // this set is free again: loads of the tile after next
+            if (lok) fetch_tile(g + 2u, regs, mt);
+            if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 3);
+        };
+        if (lok && (ma & kMetaTile)) tile_step(regs_a, ma, std::true_type{});
+        while (lok && ((ma | mb) & kMetaTile)) {
+            if (mb & kMetaTile) tile_step(regs_b, mb, std::false_type{});
+            if (lok && (ma & kMetaTile)) tile_step(regs_a, ma, std::false_type{});
         }
     } else if (warp >= kMmaWarp) {
-        // ───────────── last warpgroup: MMA issue (one thread of warp 12), tensor-memory owner ─────────────
+        // ───────────── last warpgroup: MMA issue (one thread each of warps 12 and 13), tensor-memory owner ─────────────
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIdleRegs));
         if (warp == kMmaWarp) {
             ptx::tmem_alloc(ptx::smem_u32(&misc->tmem_base), kTmemCols);
             ptx::tmem_relinquish();
-            if (lane == 0) trace_mark(a, 3, 9);
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tmem);
         }
-        block_sync();
-        const uint32_t tmem = misc->tmem_base;
-        if (ntiles > 0 && warp == kMmaWarp) {
+        if (warp == kMmaWarp) {
             if (lane == 0) {
+                const bool have_tmem = wait_tmem();
+                const uint32_t tmem = misc->tmem_base;
                 constexpr uint32_t idesc_qk = use_f16(SRC) ? ptx::make_idesc_f16(128, kTileN, false, false)
                                                             : ptx::make_idesc_bf16(128, kTileN, false, false);
-                bool ok = true;
-                // Q: shared-memory chunks landed (TMA) and tensor-memory chunks copied
-                if (!ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs) || !wait_q_ready()) {
-                    report_timeout(a.status, kStatusWaitQ, 1, tile0);
-                    ok = false;
-                }
-                ptx::tc_fence_after_sync();
-                // S(it) = Q . K(it)^T into S buffer it&1; one tile ahead of the PV MMAs so that
-                // the softmax of tile it overlaps the QK MMAs of tile it+1.
-                // Chunks [C0, C1) (4 MMAs each) of S(it) = Q . K(it)^T into S buffer it&1; the chunk
-                // range is a compile-time constant so that the descriptors fold to immediates.
                 constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);        // 8-row groups 1 KB apart
                 const uint32_t q_lo = ptx::smem_desc_lo(q_base, 16);
-                auto issue_qk_range = [&](int it, auto c0_tag, auto c1_tag) {
+                // Chunks [C0, C1) (4 MMAs each) of S = Q . K^T of the tile in stage st into S buffer st; the chunk
+                // range is a compile-time constant so that the descriptors fold to immediates.
+                auto issue_qk_range = [&](int st, auto c0_tag, auto c1_tag) {
                     constexpr int C0 = decltype(c0_tag)::value, C1 = decltype(c1_tag)::value;
-                    const int st = it & 1;
                     const uint32_t k_lo = ptx::smem_desc_lo(kv_base + uint32_t(st) * L::kKvStageBytes, 16);
                     const uint32_t d = tmem + kTmemS + uint32_t(st) * kTileN;
 #pragma unroll
@@ -851,7 +863,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             // descriptor start addresses advance by constants (in 16-byte units)
                             const uint32_t b_lo = k_lo + uint32_t((c * kKvChunkBytes + k * 32) >> 4);
                             if (c < kQTmemChunks) {
-                                // A = Q columns in tensor memory: 16 BF16 = 8 columns per K step
+                                // A = Q columns in tensor memory: 16 values = 8 columns per K step
                                 ptx::mma_bf16_ts2(d, tmem + kTmemQ + c * 32 + k * 8, b_lo, kDescHi, idesc_qk, (c | k) ? 1u : 0u);
                             } else {
                                 const uint32_t a_lo = q_lo + uint32_t(((c - kQTmemChunks) * kQChunkBytes + k * 32) >> 4);
@@ -860,172 +872,302 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         }
                     }
                 };
-                // QK is issued group by group as the loaders deliver them; between groups a ready P
-                // goes first.
-                constexpr int kNumGroups = kNumKvGroups;
-                static_assert(kNumGroups == 2, "group dispatch below is written for 2 groups");
-                // the groups the loaders deliver: chunks 0-3, then the rest with the RoPE tail
-                auto issue_qk_group = [&](int it, int g) {
-                    if (g == 0) issue_qk_range(it, std::integral_constant<int, 0>{}, std::integral_constant<int, 4>{});
-                    else issue_qk_range(it, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK>{});
-                };
+                static_assert(kNumKvGroups == 2, "group dispatch below is written for 2 groups");
                 // This thread issues only S = Q.K^T, group by group as the loaders deliver them; O += P.V is
                 // issued by a thread of the next warp.  No order is needed between the two streams beyond
                 // what the barriers already give: S(t+2) and the refill of stage t&1 both follow the
-                // kv_free arrival of P(t).V(t), and P(t) follows S(t).  A P that becomes ready then never
-                // waits for this thread to finish issuing a group.
-                for (int it = 0; it < ntiles && ok; ++it) {
-                    const int st = it & 1;
-                    for (int g = 0; g < kNumGroups; ++g) {
-                        const uint32_t bar = bar_kv_full + 80 * st + 8 * g, par = uint32_t(it >> 1) & 1u;
-                        if (!(PAIR ? ptx::mbar_wait_cluster(bar, par, kWaitTimeoutNs) : ptx::mbar_wait(bar, par, kWaitTimeoutNs))) {
-                            report_timeout(a.status, kStatusWaitKvFull, 1, tile0 + it);
+                // kv_free arrival of P(t).V(t), and P(t) follows S(t).
+                bool ok = have_tmem;
+                uint32_t gt = 0, qn = 0;
+                uint32_t pend0 = 0u, pend1 = 0u;         // per stage: the epilogue (running number) whose output staging it holds
+                uint32_t last_bar = 0, last_par = 0;     // the S commit of the last tile issued
+                bool have_last = false;
+                Item cur = get_item(0);
+                for (int k = 0; k < n_items && ok; ++k) {
+                    // (the next item's record is requested now: a load issued at the end of the item would queue up
+                    // behind the loaders' traffic for a microsecond or two)
+                    const Item nxt = (k + 1 < n_items) ? get_item(k + 1) : cur;
+                    const int ntiles = cur.ntiles;
+                    if (ntiles > 0) {
+                        trace_mark(a, 1, 700 + 4 * int(qn));
+                        // every Q.K^T of the previous item must have completed before its Q is replaced
+                        if (have_last && !ptx::mbar_wait(last_bar, last_par, wait_ns)) {
+                            report_status(a.status, kStatusWaitSFull, 1, cur.tile0);
+                            ok = false;
+                            break;
+                        }
+                        trace_mark(a, 1, 700 + 4 * int(qn) + 1);
+                        // ... and the stage of the item's first tile must be free: the chunks bound for tensor memory are
+                        // staged there
+                        const int st0 = int(gt & 1u);
+                        if (gt >= 2u && !ptx::mbar_wait(bar_kv_free + 8 * st0, ((gt >> 1) - 1u) & 1u, wait_ns)) {
+                            report_status(a.status, kStatusWaitKvFree, 1, int(gt));
+                            ok = false;
+                            break;
+                        }
+                        trace_mark(a, 1, 700 + 4 * int(qn) + 2);
+                        // (it may also still hold the output staging of the item before the previous one, when that one
+                        // had a single tile)
+                        {
+                            const uint32_t need = st0 ? pend1 : pend0;
+                            if (need != 0u) {
+                                const unsigned long long t0 = ptx::globaltimer_ns();
+                                bool free_now = false;
+                                while (true) {
+                                    free_now = misc->epi_done[0] >= need && misc->epi_done[1] >= need &&
+                                               misc->epi_done[2] >= need && misc->epi_done[3] >= need;
+                                    if (free_now || ptx::globaltimer_ns() - t0 > wait_ns) break;
+                                }
+                                if (!free_now) {
+                                    report_status(a.status, kStatusWaitEpilogue, 1, int(gt));
+                                    ok = false;
+                                    break;
+                                }
+                                __threadfence_block();
+                                if (st0) pend1 = 0u; else pend0 = 0u;
+                            }
+                        }
+                        // Q tile [128 heads x NCHUNK*64] bf16 by TMA, one 64-column box per chunk, landing in the
+                        // swizzled operand layout: chunks >= kQTmemChunks at their final place, the others in the
+                        // staging area.  Rows past the end of Q read as zero; rows of a following request (H < 128)
+                        // are computed but never written out.
+                        trace_mark(a, 1, 600 + int(qn));
+                        ptx::mbar_arrive_expect_tx(bar_q_full, uint32_t(NCHUNK) * kQChunkBytes);
+                        const int qrow0 = cur.n * a.H + cur.hg * kHeadsPerCta;
+#pragma unroll
+                        for (int c = 0; c < NCHUNK; ++c) {
+                            const uint32_t dst = (c < kQTmemChunks) ? kv_base + uint32_t(st0) * L::kKvStageBytes + uint32_t(c) * kQChunkBytes
+                                                                    : q_base + uint32_t(c - kQTmemChunks) * kQChunkBytes;
+                            ptx::tma_load_2d(dst, &a.q_map, c * 64, qrow0, bar_q_full);
+                        }
+                        if (!ptx::mbar_wait(bar_q_ready, qn & 1u, wait_ns)) {
+                            report_status(a.status, kStatusWaitQ, 1, cur.tile0);
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after_sync();
-                        if (g == 0) trace_mark(a, 1, 2 * it);
-                        issue_qk_group(it, g);
+                        for (int it = 0; it < ntiles && ok; ++it) {
+                            const uint32_t g = gt + uint32_t(it);
+                            const int st = int(g & 1u);
+                            const uint32_t par = (g >> 1) & 1u;
+                            for (int grp = 0; grp < kNumKvGroups; ++grp) {
+                                if (!ptx::mbar_wait(bar_kv_full + kKvFullStride * st + 8 * grp, par, wait_ns)) {
+                                    report_status(a.status, kStatusWaitKvFull, 1, cur.tile0 + it);
+                                    ok = false;
+                                    break;
+                                }
+                                ptx::tc_fence_after_sync();
+                                trace_mark(a, 1, 4 * int(g) + grp);
+                                if (grp == 0) issue_qk_range(st, std::integral_constant<int, 0>{}, std::integral_constant<int, 4>{});
+                                else issue_qk_range(st, std::integral_constant<int, 4>{}, std::integral_constant<int, NCHUNK>{});
+                            }
+                            if (ok) {
+                                trace_mark(a, 1, 4 * int(g) + 2);
+                                ptx::mma_commit(bar_s_full + 8 * st);
+                                last_bar = bar_s_full + 8 * st;  last_par = par;  have_last = true;
+                            }
+                        }
+                        gt += uint32_t(ntiles);
+                        ++qn;
+                        if ((gt - 1u) & 1u) pend1 = qn; else pend0 = qn;     // the item's output is staged in the stage of its last tile
                     }
-                    if (ok) ptx::mma_commit(bar_s_full + 8 * st);
+                    cur = nxt;
                 }
             }
             __syncwarp();
-        } else if (ntiles > 0 && warp == kMmaWarp + 1) {
+        } else if (warp == kMmaWarp + 1) {
             // ───────────── O += P . V issue (one thread) ─────────────
             if (lane == 0) {
+                bool ok = wait_tmem();
+                if (!ok) report_status(a.status, kStatusWaitQ, 3, -1);
+                const uint32_t tmem = misc->tmem_base;
                 constexpr uint32_t idesc_pv = use_f16(SRC) ? ptx::make_idesc_f16(128, kDvHalf, false, true)
                                                             : ptx::make_idesc_bf16(128, kDvHalf, false, true);
                 constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);
-                bool ok = true;
-                for (int it = 0; it < ntiles; ++it) {
-                    const int st = it & 1;
-                    if (!ptx::mbar_wait(bar_p_full + 8 * st, uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
-                        report_timeout(a.status, kStatusWaitPFull, 1, tile0 + it);
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
-                    ptx::tc_fence_after_sync();
-                    trace_mark(a, 1, 2 * it + 1);
-                    const uint32_t p_tmem = tmem + kTmemS + uint32_t(st) * kTileN;
-                    // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart (leading
-                    // offset), 8-entry groups 1 KB apart; A = P in tensor memory, 8 columns per step
-                    const uint32_t v_lo = ptx::smem_desc_lo(kv_st + v_off, kKvChunkBytes);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        ptx::mma_bf16_ts2(tmem + kTmemO, p_tmem + k * 8, v_lo + uint32_t((k * 2048) >> 4), kDescHi, idesc_pv,
-                                          (it | k) ? 1u : 0u);
-                    ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
-                    if constexpr (PAIR) ptx::mma_commit_cluster(bar_kv_free + 8 * st + peer_delta);   // the other block's forwarder copies into it
-                    trace_mark(a, 1, 512 + 4 * it + 3);
-                }
-                if (ok) ptx::mma_commit(bar_o_full);
-            }
-            __syncwarp();
-        } else if (PAIR && ntiles > 0 && warp == kMmaWarp + 2) {
-            // ───────────── forwarder (cluster pair): this block's half of every group, once its loader
-            // warps have written it, goes to the same place in the other block by bulk copies that
-            // complete on the other block's kv_full barrier (no load/store-unit work, no registers)
-            if (lane == 0) {
-                constexpr uint32_t kHalfChunk = uint32_t(kKvChunkBytes) / 2;       // 32 rows x 128 bytes
-                for (int it = 0; it < ntiles; ++it) {
-                    const int st = it & 1;
-                    const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes + uint32_t(half) * kHalfChunk;
-                    bool fok = true;
-                    for (int j = 0; j < 4 && fok; ++j) {
-                        if (!ptx::mbar_wait(ptx::smem_u32(&misc->bar_loc[st][j]), uint32_t(it >> 1) & 1u, kWaitTimeoutNs)) {
-                            report_timeout(a.status, kStatusWaitKvFull, 3, tile0 + it);
-                            fok = false;
+                uint32_t gt = 0;
+                Item cur = get_item(0);
+                for (int k = 0; k < n_items && ok; ++k) {
+                    const Item nxt = (k + 1 < n_items) ? get_item(k + 1) : cur;
+                    const int ntiles = cur.ntiles;
+                    for (int it = 0; it < ntiles; ++it) {
+                        const uint32_t g = gt + uint32_t(it);
+                        const int st = int(g & 1u);
+                        // (the first P of an item is written after the softmax warps have read the previous item's O out
+                        // of tensor memory, so the overwrite below needs no barrier of its own)
+                        if (!ptx::mbar_wait(bar_p_full + 8 * st, (g >> 1) & 1u, wait_ns)) {
+                            report_status(a.status, kStatusWaitPFull, 1, cur.tile0 + it);
+                            ok = false;
                             break;
                         }
-                        const int g = j >> 1;
-                        const uint32_t rbar = bar_kv_full + 80 * st + 8 * g + peer_delta;
-                        if (j == 0) {
-                            // this block's eight 4-bit validity masks of the tile
-                            const unsigned long long vb = *reinterpret_cast<volatile unsigned long long*>(&misc->valid_bytes[st][8 * half]);
-                            asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(ptx::smem_u32(&misc->valid_bytes[st][8 * half]) + peer_delta), "l"(vb) : "memory");
-                        }
-                        if ((j & 1) == 0) {
-                            // one arrival per group, announcing all of the group's bytes
-                            asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(rbar),
-                                         "r"(uint32_t(g == 0 ? 4 : NCHUNK - 4) * kHalfChunk) : "memory");
-                        }
-                        const int c0 = 2 * j, c1 = j == 3 ? NCHUNK : 2 * j + 2;
-                        for (int c = c0; c < c1; ++c) {
-                            const uint32_t src = kv_st + uint32_t(c) * kKvChunkBytes;
-                            asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(src + peer_delta),
-                                         "r"(src), "r"(kHalfChunk), "r"(rbar) : "memory");
-                        }
+                        const uint32_t kv_st = kv_base + uint32_t(st) * L::kKvStageBytes;
+                        ptx::tc_fence_after_sync();
+                        trace_mark(a, 3, 2 * int(g));
+                        const uint32_t p_tmem = tmem + kTmemS + uint32_t(st) * kTileN;
+                        // B = V[16 entries x 256 cols], MN-major: 64-col groups 8 KB apart (leading
+                        // offset), 8-entry groups 1 KB apart; A = P in tensor memory, 8 columns per step
+                        const uint32_t v_lo = ptx::smem_desc_lo(kv_st + v_off, kKvChunkBytes);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            ptx::mma_bf16_ts2(tmem + kTmemO, p_tmem + kk * 8, v_lo + uint32_t((kk * 2048) >> 4), kDescHi, idesc_pv,
+                                              (it | kk) ? 1u : 0u);
+                        ptx::mma_commit(bar_kv_free + 8 * st);   // stage reusable, and O includes tile it
                     }
-                    if (!fok) break;
+                    if (ok && ntiles > 0) ptx::mma_commit(bar_o_full);
+                    gt += uint32_t(ntiles);
+                    cur = nxt;
                 }
             }
+            __syncwarp();
+        } else if (warp == kResolveWarp) {
+            // ───────────── resolver: where does every entry of the next tiles live? ─────────────
+            // Walks the block's items in order; for every tile it writes the 64 record numbers, the validity mask
+            // and a tag into a ring in shared memory, up to kRing tiles ahead of the loaders.  A lane owns entries
+            // lane and lane + 32 of a tile.  The dependent loads (index list -> block table) are issued one step
+            // and looked at the next; the records and, at the start of an item, its Q rows are pulled into L2.
+            int ck = 0, ct = 0;
+            Item ci{};
+            auto kc_seek = [&]() {        // the first item at or after ck that has tiles
+                ct = 0;
+                while (ck < n_items) {
+                    ci = get_item(ck);
+                    if (ci.ntiles > 0) break;
+                    ++ck;
+                }
+            };
+            auto kc_ctx = [&]() -> TileCtx {
+                TileCtx c{};
+                if (ck < n_items) {
+                    c.n = ci.n;  c.b = ci.b;  c.n_tok = ci.n_tok;  c.kv_len_n = ci.kv_len_n;
+                    c.v0 = (ci.tile0 + ct) * kTileN;
+                    c.meta = kMetaTile | uint32_t(ci.n) | (uint32_t(ci.hg) << 16) | (ct == 0 ? kMetaFirst : 0u) |
+                             (ct == ci.ntiles - 1 ? kMetaLast : 0u);
+                }
+                return c;
+            };
+            auto kc_advance = [&]() {
+                if (ck >= n_items) return;
+                if (++ct >= ci.ntiles) { ++ck;  kc_seek(); }
+            };
+            kc_seek();
+            bool rok = true;
+            uint32_t t = 0;            // tiles published so far
+            auto publish = [&](uint32_t meta, uint32_t id0, uint32_t id1) {
+                const uint32_t slot = t % kRing;
+                if (t >= uint32_t(kRing)) {
+                    const bool w = ptx::mbar_wait(bar_res_empty + 8 * slot, ((t / kRing) - 1u) & 1u, wait_ns);
+                    if (!__all_sync(0xFFFFFFFFu, w)) {
+                        report_status(a.status, kStatusWaitResolver, 4, int(t));
+                        rok = false;
+                        return;
+                    }
+                }
+                TileSlot& ts = misc->ring[slot];
+                ts.id[lane] = id0;
+                ts.id[lane + 32] = id1;
+                const uint32_t lo = __ballot_sync(0xFFFFFFFFu, (id0 & kIdValid) != 0u);
+                const uint32_t hi = __ballot_sync(0xFFFFFFFFu, (id1 & kIdValid) != 0u);
+                if (lane == 0) {
+                    ts.mask = uint64_t(lo) | (uint64_t(hi) << 32);
+                    ts.meta = meta;
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_res_full + 8 * slot);
+                ++t;
+            };
+            // three-stage pipeline over the stream: index values of the tile two ahead, block-table values of the
+            // next tile, record numbers of this one
+            TileCtx c0 = kc_ctx();  kc_advance();
+            TileCtx c1 = kc_ctx();  kc_advance();
+            int e1a = -1, e1b = -1;
+            PendingId p0a, p0b;
+            {
+                int e0a = -1, e0b = -1;
+                if constexpr (SRC == kSrcCsa) {
+                    e0a = resolve_index(a, c0, lane);      e0b = resolve_index(a, c0, lane + 32);
+                    e1a = resolve_index(a, c1, lane);      e1b = resolve_index(a, c1, lane + 32);
+                }
+                p0a = resolve_issue<SRC>(a, c0, e0a, lane);
+                p0b = resolve_issue<SRC>(a, c0, e0b, lane + 32);
+            }
+            if (c0.meta & kMetaTile) prefetch_q_l2<NCHUNK>(a, c0.n, int((c0.meta >> 16) & 0xFFu), lane, 32);
+            while (rok && (c0.meta & kMetaTile)) {
+                // the next tile's block-table loads go out before this tile's are looked at
+                const TileCtx c2 = kc_ctx();  kc_advance();
+                const PendingId p1a = resolve_issue<SRC>(a, c1, e1a, lane);
+                const PendingId p1b = resolve_issue<SRC>(a, c1, e1b, lane + 32);
+                if constexpr (SRC == kSrcCsa) {
+                    e1a = resolve_index(a, c2, lane);      e1b = resolve_index(a, c2, lane + 32);
+                }
+                const uint32_t id0 = resolve_finish<SRC>(a, p0a), id1 = resolve_finish<SRC>(a, p0b);
+                prefetch_record_l2<SRC>(a, id0);
+                prefetch_record_l2<SRC>(a, id1);
+                publish(c0.meta, id0, id1);
+                if ((c1.meta & (kMetaTile | kMetaFirst)) == (kMetaTile | kMetaFirst))
+                    prefetch_q_l2<NCHUNK>(a, c1.n, int((c1.meta >> 16) & 0xFFu), lane, 32);
+                c0 = c1;  c1 = c2;
+                p0a = p1a;  p0b = p1b;
+            }
+            // two end marks: the loaders look two tiles ahead
+            if (rok) publish(0u, 0u, 0u);
+            if (rok) publish(0u, 0u, 0u);
             __syncwarp();
         }
     } else {
         // ───────────── softmax + epilogue warps ─────────────
-        block_sync();
+        bool ok = __all_sync(0xFFFFFFFFu, wait_tmem());
+        if (!ok) report_status(a.status, kStatusWaitQ, 0, -1);
         const uint32_t tmem = misc->tmem_base;
-        bool ok = true;
-        if (ntiles > 0) {
-            const bool w = ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs);
-            if (!__all_sync(0xFFFFFFFFu, w)) {
-                report_timeout(a.status, kStatusWaitQ, 0, tile0);
-                ok = false;
-            }
-            if (tid == 0) trace_mark(a, 3, 11);
-            if (ok) {
-                // chunks 0-1 here, chunks 2 and 3 by the loader warps (each warp serves its lane quarter)
-                static_assert(kQTmemChunks == 4, "the split of the copy below is written for four chunks");
-                copy_q_chunks_to_tmem<use_f16(SRC)>(smem_base + L::kQStageOff, tmem, warp, lane, 0, 2);
-                if constexpr (use_f16(SRC)) {
-                    // the Q chunks that stay in shared memory: BF16 -> FP16 in place (element-wise, so
-                    // the swizzled layout is untouched), then made visible to the MMAs' reads
-                    // (shared with the loader warps: see convert_q_smem)
-                    convert_q_smem<L::kQBytes>(q_base, tid);
+        const int r = warp * 32 + lane;                // head row inside the group
+        const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+        uint32_t gt = 0, qn = 0;
+        Item cur = get_item(0);
+        for (int k = 0; k < n_items && ok; ++k) {
+            const int ntiles = cur.ntiles;
+            const int n = cur.n, hg = cur.hg;
+            const bool final_out = cur.slot < 0;
+            const int h = hg * kHeadsPerCta + r;
+            const bool write = h < a.H;
+            const int64_t prow0 = final_out ? 0 : partial_row0(cur);
+            // destination of this thread's head row (this block's half of the value columns), and of its LSE
+            __nv_bfloat16* const out_rows = final_out ? a.out + (int64_t(n) * a.H + hg * kHeadsPerCta) * 512 + half * kDvHalf
+                                                      : reinterpret_cast<__nv_bfloat16*>(a.partial_o) + prow0 * 512 + half * kDvHalf;
+            if (ntiles <= 0) {
+                // Nothing to attend to: zero output, LSE = -inf.
+                for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumSoftmaxWarps * 32) {
+                    const int rr = i / (kDvHalf / 8), v = i % (kDvHalf / 8);
+                    if (hg * kHeadsPerCta + rr < a.H)
+                        *reinterpret_cast<uint4*>(out_rows + int64_t(rr) * 512 + v * 8) = make_uint4(0, 0, 0, 0);
                 }
-                ptx::tmem_wait_st();
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) arrive_q_ready();
+                if (half == 0 && write) {
+                    if (final_out) {
+                        if (a.lse != nullptr) a.lse[int64_t(n) * a.H + h] = -CUDART_INF_F;
+                    } else {
+                        a.partial_lse[prow0 + r] = -CUDART_INF_F;
+                    }
+                }
+                if (k + 1 < n_items) cur = get_item(k + 1);
+                continue;
             }
-        }
-        if (tid == 0) trace_mark(a, 3, 1);
-        if (ntiles > 0) {
-            const int r = warp * 32 + lane;                // head row inside the group
-            const uint32_t lane_addr = uint32_t(warp * 32) << 16;
             float m_ref = -CUDART_INF_F;                   // reference maximum used in exp2 (log2 units)
             float l_sum = 0.f;
             for (int it = 0; it < ntiles && ok; ++it) {
-                const int st = it & 1;
+                const uint32_t g = gt + uint32_t(it);
+                const int st = int(g & 1u);
                 const uint32_t s_tmem = tmem + lane_addr + kTmemS + uint32_t(st) * kTileN;
                 {
-                    const bool w = ptx::mbar_wait(bar_s_full + 8 * st, uint32_t(it >> 1) & 1u, kWaitTimeoutNs);
+                    const bool w = ptx::mbar_wait(bar_s_full + 8 * st, (g >> 1) & 1u, wait_ns);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_timeout(a.status, kStatusWaitSFull, 0, tile0 + it);
+                        report_status(a.status, kStatusWaitSFull, 0, cur.tile0 + it);
                         ok = false;  break;
                     }
                 }
                 ptx::tc_fence_after_sync();
-                if (tid == 0) trace_mark(a, 0, 2 * it);
+                if (tid == 0) trace_mark(a, 0, 4 * int(g));
                 uint32_t s0[32], s1[32];
                 ptx::tmem_ld32(s_tmem, s0);
                 ptx::tmem_ld32(s_tmem + 32, s1);
                 ptx::tmem_wait_ld();
-                uint64_t vmask;
-                if constexpr (PAIR) {
-                    // sixteen 4-bit masks, one per loader warp of the pair
-                    const uint4 vb = ptx::lds_v4(ptx::smem_u32(&misc->valid_bytes[st][0]));
-                    if ((vb.x & vb.y & vb.z & vb.w) == 0x0F0F0F0Fu) {
-                        vmask = ~0ull;
-                    } else {
-                        auto nib = [](uint32_t w) { return (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u); };
-                        vmask = uint64_t(nib(vb.x) | (nib(vb.y) << 16)) | (uint64_t(nib(vb.z) | (nib(vb.w) << 16)) << 32);
-                    }
-                } else {
-                    vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
-                }
+                const uint64_t vmask = *reinterpret_cast<volatile uint64_t*>(&misc->valid_mask[st]);
                 if (vmask != ~0ull) {
                     // entries that do not take part (padding, the end of the list): -inf before the scale
                     const uint32_t vm0 = uint32_t(vmask), vm1 = uint32_t(vmask >> 32);
@@ -1040,8 +1182,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        t4[k] = fmaxf(t4[k], fmaxf(__uint_as_float(s0[i + k]), __uint_as_float(s1[i + k])));
+                    for (int kk = 0; kk < 4; ++kk)
+                        t4[kk] = fmaxf(t4[kk], fmaxf(__uint_as_float(s0[i + kk]), __uint_as_float(s1[i + kk])));
                 }
                 const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * a.scale_log2;
                 // Lazy reference maximum: move it only when the true maximum exceeds it by
@@ -1076,9 +1218,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 // Rescale O where the reference maximum moved.  The PV MMAs of the previous
                 // tile must have finished first (their commit is that stage's kv_free).
                 if (it > 0 && __any_sync(0xFFFFFFFFu, moved)) {
-                    const bool w = ptx::mbar_wait(bar_kv_free + 8 * ((it - 1) & 1), uint32_t((it - 1) >> 1) & 1u, kWaitTimeoutNs);
+                    const uint32_t gp = g - 1u;
+                    const bool w = ptx::mbar_wait(bar_kv_free + 8 * int(gp & 1u), (gp >> 1) & 1u, wait_ns);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_timeout(a.status, kStatusWaitKvFree, 0, tile0 + it);
+                        report_status(a.status, kStatusWaitKvFree, 0, cur.tile0 + it);
                         ok = false;  break;
                     }
                     ptx::tc_fence_after_sync();
@@ -1092,32 +1235,31 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         ptx::tmem_st32(tmem + lane_addr + kTmemO + c * 32, o);
                     }
                 }
-                // P (BF16, two entries per column) over the first 32 columns of this S buffer:
+                // P (two entries per column) over the first 32 columns of this S buffer:
                 // the A operand of the PV MMAs.  S has been read into registers above.
                 ptx::tmem_st32(s_tmem, pk);
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_p_full + 8 * st);
-                if (tid == 0) trace_mark(a, 0, 2 * it + 1);
+                if (tid == 0) trace_mark(a, 0, 4 * int(g) + 1);
             }
             // ── epilogue ──
+            const int tile_end = cur.tile0 + ntiles;
+            if (k + 1 < n_items) cur = get_item(k + 1);      // the next item's record arrives while this one is written out
             if (ok) {
-                const bool w = ptx::mbar_wait(bar_o_full, 0u, kWaitTimeoutNs);
+                const bool w = ptx::mbar_wait(bar_o_full, qn & 1u, wait_ns);
                 if (!__all_sync(0xFFFFFFFFu, w)) {
-                    report_timeout(a.status, kStatusWaitOFull, 0, tile1);
+                    report_status(a.status, kStatusWaitOFull, 0, tile_end);
                     ok = false;
                 }
             }
             if (ok) {
                 ptx::tc_fence_after_sync();
-                if (tid == 0) trace_mark(a, 3, 2);
+                if (tid == 0) trace_mark(a, 0, 4 * int(gt + uint32_t(ntiles) - 1u) + 2);
                 // A merge kernel launched as a programmatic dependent may be made resident once every block of
                 // this grid is here (or gone): by then no block of this grid is waiting for an SM any more.
-                if (tid == 0 && a.num_splits > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-                const int h = hg * kHeadsPerCta + r;
-                const bool write = h < a.H;
-                const bool final_out = a.num_splits == 1;
+                if (tid == 0 && k == n_items - 1 && (sched || a.num_splits > 1)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
                 float denom = l_sum;
                 if (final_out && a.attn_sink != nullptr && write) {
                     const float s2 = __ldg(a.attn_sink + h) * 1.4426950408889634f;
@@ -1125,25 +1267,25 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 }
                 const float inv = (l_sum > 0.f) ? 1.f / denom : 0.f;
                 const float lse2 = (l_sum > 0.f) ? m_ref + log2f(l_sum) : -CUDART_INF_F;
-                const int64_t row = int64_t(n) * a.H + h;
-                // O leaves through shared memory (Q and the KV stages are free by now): each thread owns a
-                // row in tensor memory, but rows are 1 KB apart in global memory, so the rows are first
-                // laid down in shared memory (pitch = row + 16 bytes: conflict-free both ways) and then
-                // written out 512 contiguous bytes per warp instruction.
-                // (split partials are written as BF16 too: the merge reads them back at once, and at
-                // eight splits their traffic exceeds the KV bytes; the FP32 form remains for a.partial_f32)
-                const bool bf16_out = final_out || !a.partial_f32;
-                const uint32_t row_bytes = bf16_out ? uint32_t(kDvHalf) * 2u : uint32_t(kDvHalf) * 4u;
-                const uint32_t pitch = row_bytes + 16u;
-                static_assert(4 * 32 * (kDvHalf * 4 + 16) <= L::kQBytes + 2 * L::kKvStageBytes, "epilogue staging must fit in the Q + KV area");
-                const uint32_t stg = q_base + uint32_t(warp) * (32u * (uint32_t(kDvHalf) * 4u + 16u));
-                const uint32_t my = stg + uint32_t(lane) * pitch;
+                // O leaves through shared memory: each thread owns a row in tensor memory, but rows are 1 KB apart
+                // in global memory, so 128 columns at a time are laid down in shared memory (pitch = 256 + 16
+                // bytes: conflict-free both ways) and written out 2 x 256 contiguous bytes per warp instruction.
+                // The staging area is the KV stage of the item's last tile, which nothing else uses until the
+                // loaders have seen this warp's epi_done count (the other stage may already hold the next item's
+                // first tile).  Split partials are BF16 as well: the merge reads them back at once, and at eight
+                // splits their traffic would otherwise exceed the KV bytes.
+                const uint32_t s_last = (gt + uint32_t(ntiles) - 1u) & 1u;
+                const uint32_t stg = kv_base + s_last * L::kKvStageBytes + uint32_t(warp) * L::kEpiWarpBytes;
+                const uint32_t my = stg + uint32_t(lane) * L::kEpiPitch;
+                const int hw0 = hg * kHeadsPerCta + warp * 32;                   // first head row of this warp
+                uint8_t* gbase = reinterpret_cast<uint8_t*>(out_rows + int64_t(warp) * 32 * 512);
 #pragma unroll 1
-                for (int c = 0; c < kDvHalf / 32; ++c) {
-                    uint32_t o[32];
-                    ptx::tmem_ld32(tmem + lane_addr + kTmemO + c * 32, o);
-                    ptx::tmem_wait_ld();
-                    if (bf16_out) {
+                for (int pass = 0; pass < L::kEpiPasses; ++pass) {
+#pragma unroll 1
+                    for (int c = 0; c < L::kEpiCols / 32; ++c) {
+                        uint32_t o[32];
+                        ptx::tmem_ld32(tmem + lane_addr + kTmemO + pass * L::kEpiCols + c * 32, o);
+                        ptx::tmem_wait_ld();
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
                             uint4 w;
@@ -1153,89 +1295,40 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             w.w = ptx::pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
                             ptx::sts_v4(my + uint32_t(c) * 64u + uint32_t(v) * 16u, w);
                         }
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            uint4 w;
-                            w.x = __float_as_uint(__uint_as_float(o[4 * v + 0]) * inv);
-                            w.y = __float_as_uint(__uint_as_float(o[4 * v + 1]) * inv);
-                            w.z = __float_as_uint(__uint_as_float(o[4 * v + 2]) * inv);
-                            w.w = __float_as_uint(__uint_as_float(o[4 * v + 3]) * inv);
-                            ptx::sts_v4(my + uint32_t(c) * 128u + uint32_t(v) * 16u, w);
-                        }
                     }
-                }
-                __syncwarp();
-                if (tid == 0) trace_mark(a, 3, 12);
-                {
-                    const uint32_t vecs_per_row = row_bytes / 16u;                  // 32 or 64
-                    const int h0 = hg * kHeadsPerCta + warp * 32;                   // first head row of this warp
-                    const int64_t prow = ((int64_t(split) * gridDim.y + n) * a.H) * 512 + half * kDvHalf;   // element index
-                    uint8_t* gbase = final_out
-                        ? reinterpret_cast<uint8_t*>(a.out + (int64_t(n) * a.H) * 512 + half * kDvHalf)
-                        : (bf16_out ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(a.partial_o) + prow)
-                                    : reinterpret_cast<uint8_t*>(a.partial_o + prow));
-                    const int64_t grow = bf16_out ? 512 * 2 : 512 * 4;              // bytes between head rows in global memory
+                    __syncwarp();
+                    constexpr uint32_t kVecs = uint32_t(L::kEpiCols) / 8u;      // 16-byte pieces per staged row
 #pragma unroll 4
-                    for (uint32_t q = uint32_t(lane); q < 32u * vecs_per_row; q += 32u) {
-                        const uint32_t rl = q / vecs_per_row, vc = q % vecs_per_row;
-                        if (h0 + int(rl) < a.H) {
-                            const uint4 w = ptx::lds_v4(stg + rl * pitch + vc * 16u);
-                            *reinterpret_cast<uint4*>(gbase + int64_t(h0 + int(rl)) * grow + vc * 16u) = w;
+                    for (uint32_t q = uint32_t(lane); q < 32u * kVecs; q += 32u) {
+                        const uint32_t rl = q / kVecs, vc = q % kVecs;
+                        if (hw0 + int(rl) < a.H) {
+                            const uint4 w = ptx::lds_v4(stg + rl * L::kEpiPitch + vc * 16u);
+                            *reinterpret_cast<uint4*>(gbase + int64_t(rl) * 1024 + pass * (L::kEpiCols * 2) + vc * 16u) = w;
                         }
                     }
+                    __syncwarp();
                 }
-                if (tid == 0) trace_mark(a, 3, 13);
+                if (lane == 0) {
+                    __threadfence_block();
+                    misc->epi_done[warp] = qn + 1u;
+                }
+                if (tid == 0) trace_mark(a, 0, 4 * int(gt + uint32_t(ntiles) - 1u) + 3);
                 if (write && half == 0) {
                     if (final_out) {
-                        if (a.lse != nullptr) a.lse[row] = (l_sum > 0.f) ? lse2 * 0.6931471805599453f : -CUDART_INF_F;
+                        if (a.lse != nullptr) a.lse[int64_t(n) * a.H + h] = (l_sum > 0.f) ? lse2 * 0.6931471805599453f : -CUDART_INF_F;
                     } else {
-                        a.partial_lse[int64_t(split) * gridDim.y * a.H + row] = lse2;
+                        a.partial_lse[prow0 + r] = lse2;
                     }
                 }
             }
-        }
-    }
-    if (ntiles <= 0) {
-        // Nothing to attend to in this split: zero output, LSE = -inf.  The Q tile is on its way into
-        // shared memory all the same and must have landed before the block leaves.
-        if (tid == 0 && !ptx::mbar_wait(bar_q_full, 0u, kWaitTimeoutNs)) report_timeout(a.status, kStatusWaitQ, 3, tile0);
-        const bool final_out = a.num_splits == 1;
-        for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumThreads) {
-            const int r = i / (kDvHalf / 8), v = i % (kDvHalf / 8);
-            const int h = hg * kHeadsPerCta + r;
-            if (h >= a.H) continue;
-            const int64_t row = int64_t(n) * a.H + h;
-            const int col = half * kDvHalf + v * 8;
-            if (final_out) {
-                *reinterpret_cast<uint4*>(a.out + row * 512 + col) = make_uint4(0, 0, 0, 0);
-            } else if (!a.partial_f32) {
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.partial_o) +
-                                          (int64_t(split) * gridDim.y * a.H + row) * 512 + col) = make_uint4(0, 0, 0, 0);
-            } else {
-                float4* dst = reinterpret_cast<float4*>(a.partial_o + (int64_t(split) * gridDim.y * a.H + row) * 512 + col);
-                dst[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                dst[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        if (half == 0 && tid < kHeadsPerCta) {
-            const int h = hg * kHeadsPerCta + tid;
-            if (h < a.H) {
-                const int64_t row = int64_t(n) * a.H + h;
-                if (final_out) {
-                    if (a.lse != nullptr) a.lse[row] = -CUDART_INF_F;
-                } else {
-                    a.partial_lse[int64_t(split) * gridDim.y * a.H + row] = -CUDART_INF_F;
-                }
-            }
+            gt += uint32_t(ntiles);
+            ++qn;
         }
     }
 
     // ── common exit: every thread gets here, with or without an error ──
-    // (PAIR: both blocks, so that neither leaves while the other may still arrive on its barriers)
     ptx::tc_fence_before_sync();
-    if constexpr (PAIR) ptx::cluster_sync(); else __syncthreads();
-    if (tid == 0) { trace_mark(a, 3, 3);  trace_block(a, 1); }
+    __syncthreads();
     if (warp == kMmaWarp) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(misc->tmem_base, kTmemCols);

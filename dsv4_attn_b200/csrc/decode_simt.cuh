@@ -24,16 +24,20 @@ __device__ __forceinline__ RowRef resolve_row(const DecodeArgs& a, int b, int n,
     if (v >= n_tok) return r;
     if constexpr (SRC == kSrcCsa) {
         const int e = a.indices[int64_t(n) * a.topk + v];
-        if (e < 0 || e >= kv_len_n) return r;
+        if (e < 0 || e >= kv_len_n || (e >> 6) >= a.max_pages) return r;
         const int page = a.block_table[int64_t(b) * a.max_pages + (e >> 6)];
+        if (page < 0 || (long long)page >= a.num_pages) return r;     // same rule as the tensor-core kernel: left out, not read
         const uint8_t* row = a.kv_pool + (int64_t(page) * 64 + (e & 63)) * 656;
         r = RowRef{row, row + 512, row + 528, true};
     } else if constexpr (SRC == kSrcHca) {
         const uint8_t* row;
         if (v < kv_len_n) {
+            if ((v >> 6) >= a.max_pages) return r;
             const int page = a.block_table[int64_t(b) * a.max_pages + (v >> 6)];
+            if (page < 0 || (long long)page >= a.num_pages) return r;
             row = a.kv_pool + (int64_t(page) * 64 + (v & 63)) * 656;
         } else {
+            if (v - kv_len_n >= a.win_cap) return r;
             row = a.win_pool + (int64_t(b) * a.win_cap + (v - kv_len_n)) * 656;
         }
         r = RowRef{row, row + 512, row + 528, true};

@@ -26,7 +26,7 @@
 #include <stdint.h>
 
 #include "ptx.cuh"
-#include "decode_kernel.cuh"   // report_timeout, status codes, kWaitTimeoutNs
+#include "decode_kernel.cuh"   // report_timeout, status codes, kDefaultWaitNs
 
 namespace dsv4 {
 
@@ -140,8 +140,8 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
             const int pages_vis = (vis_max + kIdxPageKeys - 1) / kIdxPageKeys;
             for (int i = 0; i < ntiles && ok; ++i) {
                 const int st = i % kIdxStages;
-                if (i >= kIdxStages && !ptx::mbar_wait(bar_empty + 8 * st, uint32_t(i / kIdxStages - 1) & 1u, kWaitTimeoutNs)) {
-                    report_timeout(a.status, kStatusWaitIndexer, 0, tile0 + i);
+                if (i >= kIdxStages && !ptx::mbar_wait(bar_empty + 8 * st, uint32_t(i / kIdxStages - 1) & 1u, kDefaultWaitNs)) {
+                    report_status(a.status, kStatusWaitIndexer, 0, tile0 + i);
                     ok = false;
                     break;
                 }
@@ -167,12 +167,12 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
         // ───────────── MMA issue: S^T[128 keys x N] = K[128 x 128] . Q[N x 128]^T, four K steps of 32 ─────────────
         if (lane == 0) {
             const uint32_t idesc = make_idesc_e4m3(kIdxTileKeys, N);
-            if (!ptx::mbar_wait(bar_q, 0u, kWaitTimeoutNs)) { report_timeout(a.status, kStatusWaitIndexer, 1, -1);  ok = false; }
+            if (!ptx::mbar_wait(bar_q, 0u, kDefaultWaitNs)) { report_status(a.status, kStatusWaitIndexer, 1, -1);  ok = false; }
             for (int i = 0; i < ntiles && ok; ++i) {
                 const int st = i % kIdxStages, d = i & 1;
-                if (!ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kWaitTimeoutNs) ||
-                    (i >= 2 && !ptx::mbar_wait(bar_acc_empty + 8 * d, uint32_t(i / 2 - 1) & 1u, kWaitTimeoutNs))) {
-                    report_timeout(a.status, kStatusWaitIndexer, 1, tile0 + i);
+                if (!ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kDefaultWaitNs) ||
+                    (i >= 2 && !ptx::mbar_wait(bar_acc_empty + 8 * d, uint32_t(i / 2 - 1) & 1u, kDefaultWaitNs))) {
+                    report_status(a.status, kStatusWaitIndexer, 1, tile0 + i);
                     ok = false;
                     break;
                 }
@@ -197,10 +197,10 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
         vis[1] = (a.s_q > 1) ? min(__ldg(a.n_vis + b * a.s_q + 1), a.max_pages * kIdxPageKeys) : 0;
         for (int i = 0; i < ntiles && ok; ++i) {
             const int st = i % kIdxStages, d = i & 1;
-            const bool w = ptx::mbar_wait(bar_acc_full + 8 * d, uint32_t(i / 2) & 1u, kWaitTimeoutNs) &&
-                           ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kWaitTimeoutNs);
+            const bool w = ptx::mbar_wait(bar_acc_full + 8 * d, uint32_t(i / 2) & 1u, kDefaultWaitNs) &&
+                           ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kDefaultWaitNs);
             if (!__all_sync(0xFFFFFFFFu, w)) {
-                report_timeout(a.status, kStatusWaitIndexer, 2, tile0 + i);
+                report_status(a.status, kStatusWaitIndexer, 2, tile0 + i);
                 ok = false;
                 break;
             }

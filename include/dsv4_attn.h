@@ -6,7 +6,12 @@
  * Conventions (the same ones the reference project's C entry point follows,
  * hca/sm100/kernel.cu:269-358):
  *   - every pointer is a raw DEVICE pointer owned by the caller; the library
- *     allocates nothing and keeps no state between calls;
+ *     allocates nothing.  State kept between calls: per-device "attribute set"
+ *     flags and the address of the built-in scratch array of
+ *     dsv4_csa_sparse_decode_fwd_noalloc (each written once), and the test
+ *     switches at the end of this file.  The 32 MiB scratch array is part of the
+ *     library image: every GPU context that loads the library holds it, whether or
+ *     not that entry point is ever called;
  *   - work is enqueued on the `stream` argument (a cudaStream_t passed as
  *     void*, NULL = default stream) and the call returns without synchronising;
  *   - the return value is 0 on success, otherwise a cudaError_t value
@@ -38,8 +43,13 @@ extern "C" {
 #define DSV4_MAX_SPLITS    64
 
 /* Words of the optional `status` array a kernel writes when one of its bounded
- * waits gives up (it never traps and never spins without limit). */
-#define DSV4_STATUS_WORDS  4   /* [0] error code (0 = none), [1] block x|y<<8|z<<20, [2] role, [3] tile */
+ * waits gives up (it never traps and never spins without limit), or when an index,
+ * a length or a block-table value points outside the cache (code 7: the entry is
+ * left out of the softmax and nothing is read through it).  When status[0] != 0
+ * after a call, `out` and `lse` of that call are undefined: pass `status` wherever
+ * the inputs are not trusted. */
+#define DSV4_STATUS_WORDS  4   /* [0] error code (0 = none), [1] block x|y<<8|z<<20, [2] role, [3] tile or entry */
+#define DSV4_STATUS_BAD_INDEX 7
 
 /*
  * CSA sparse decode.  For each request b and query token j the kernel gathers
@@ -49,8 +59,11 @@ extern "C" {
  * Takes the place of the reference's gather + attention core on pre-projected
  * tensors (bench/bench/reference.py:576-580 followed by :516-545); the
  * parameter-struct style follows hca/params.h:10-77 and csa/params.h:12-39.
- * Arithmetic: FP32 accumulation; Q, P and the dequantised entries pass through FP16 operands,
- * so |q| must stay below 65504 and block scales above 146 (entries beyond +-65408) saturate.
+ * Arithmetic: FP32 accumulation; Q, P and the dequantised entries pass through FP16 operands.
+ * PRECONDITIONS of that operand type (both packed-layout entry points): |q| < 65504, and block
+ * scales <= 146 - a block with a larger scale (entries beyond +-65408) is clamped to 146.  Inputs
+ * of the N(0,1) kind the cache is built for are far inside both; dsv4_attn_b200.api offers a
+ * host-side check (check_fp16_range=True) for callers that cannot vouch for theirs.
  */
 typedef struct Dsv4CsaSparseDecodeParams {
     int32_t B;                  /* requests */
@@ -61,7 +74,7 @@ typedef struct Dsv4CsaSparseDecodeParams {
     int32_t num_splits;         /* >= 1; > 1 needs partial_o / partial_lse */
     float   sm_scale;           /* softmax scale, usually 1/sqrt(576) */
     int32_t reserved0;
-    int64_t num_pages;          /* pages in kv_pool (bounds checking of block_table is the caller's) */
+    int64_t num_pages;          /* pages in kv_pool: block-table values outside [0, num_pages) are not followed (status code 7) */
     const void*    q;           /* bf16  [B, s_q, H, 576] */
     const void*    kv_pool;     /* uint8 [num_pages, 64, 656] */
     const int32_t* block_table; /* int32 [B, max_pages] */
@@ -76,6 +89,9 @@ typedef struct Dsv4CsaSparseDecodeParams {
     float*         partial_o;   /* scratch of num_splits*B*s_q*H*512 floats when num_splits > 1 (contents unspecified afterwards) */
     float*         partial_lse; /* float [num_splits, B*s_q, H], log2 units */
     int32_t*       status;      /* optional int32 [DSV4_STATUS_WORDS], zeroed by the caller */
+    const void*    sched;       /* optional plan written by dsv4_attn_plan for this batch (kind CSA, same B, s_q, H and
+                                   lengths): num_splits is then ignored and partial_o / partial_lse must have the sizes
+                                   dsv4_attn_sched_bytes reports */
 } Dsv4CsaSparseDecodeParams;
 
 int dsv4_csa_sparse_decode_fwd(const Dsv4CsaSparseDecodeParams* p, void* stream);
@@ -148,6 +164,7 @@ typedef struct Dsv4HcaDenseDecodeParams {
     float*         partial_o;
     float*         partial_lse;
     int32_t*       status;
+    const void*    sched;       /* optional plan (kind HCA), as in Dsv4CsaSparseDecodeParams */
 } Dsv4HcaDenseDecodeParams;
 
 int dsv4_hca_dense_decode_fwd(const Dsv4HcaDenseDecodeParams* p, void* stream);
@@ -193,6 +210,58 @@ int dsv4_attn_plan_splits(int rows, int H, int max_len, int num_sms);
 /* Bytes of partial_o + partial_lse a call with these sizes needs (0 when
  * num_splits == 1).  partial_lse starts at the returned `*lse_offset`. */
 int64_t dsv4_attn_workspace_bytes(int rows, int H, int num_splits, int64_t* lse_offset);
+
+/*
+ * Split-KV scheduler.  dsv4_attn_plan launches a small planner kernel (one block; no host
+ * synchronisation, no allocation, capturable into a CUDA graph) that reads the per-row lengths
+ * of a batch and writes a work list into `sched`: every (row, group of 128 heads) is cut into
+ * items of 64-entry tiles so that the SMs of the device get equal shares of tiles plus per-item
+ * set-up; a row that fits one share is written out directly, a row that straddles shares gets
+ * partial slots that the merge adds up.  The decode entry points given that `sched` then run as
+ * resident blocks (two per pair of SMs, one half of the value columns each) that walk their share
+ * of the list, keep tensor memory and barriers alive between items and fetch the next item's
+ * queries and first tiles while the current one finishes.  A plan depends only on B, s_q, H and
+ * the length arrays, so one plan serves every layer of a decode step that shares them.
+ * num_splits = 0 lets the planner balance; num_splits >= 1 cuts every unit into exactly that many
+ * equal pieces (what a caller that fixes the split count asks for) and deals the pieces out.
+ * Replaces the reference's static one-tile-per-split rule (hca/sm100/helpers.h:831-869,
+ * hca/sm100/kernel.cu:99-102,248-257).
+ *
+ * dsv4_attn_sched_bytes: size of `sched` for a shape, and the sizes of the partial_o (BF16 slots)
+ * and partial_lse areas the decode call then needs.  num_sms = 0 -> the current device.
+ */
+#define DSV4_PLAN_CSA 0
+#define DSV4_PLAN_HCA 1
+typedef struct Dsv4PlanParams {
+    int32_t kind;               /* DSV4_PLAN_CSA or DSV4_PLAN_HCA */
+    int32_t B;
+    int32_t s_q;
+    int32_t H;
+    int32_t topk;               /* CSA: length of each index list */
+    int32_t num_splits;         /* 0 = balance over the SMs, >= 1 = that many pieces per unit */
+    int32_t num_sms;            /* 0 = all SMs of the current device (fewer may be given, never more) */
+    int32_t reserved0;
+    const int32_t* topk_len;    /* CSA, optional int32 [B, s_q] */
+    const int32_t* kv_len;      /* HCA int32 [B, s_q]; CSA: optional, passed through to the items */
+    const int32_t* win_len;     /* HCA int32 [B, s_q] */
+    void*   sched;              /* device buffer, 16-byte aligned */
+    int64_t sched_bytes;
+} Dsv4PlanParams;
+
+int64_t dsv4_attn_sched_bytes(int rows, int H, int num_splits, int num_sms, int64_t* partial_o_bytes,
+                              int64_t* partial_lse_bytes);
+int dsv4_attn_plan(const Dsv4PlanParams* p, void* stream);
+
+/* The same plan computed serially on the host: every pointer of `p` (length arrays and `sched`) is then a
+ * HOST pointer and num_sms must be given (> 0; no device is asked).  For inspecting what the planner does
+ * and for testing its arithmetic without a GPU - the decode entry points take device plans only.  Items of
+ * one block pair may come in another order than from the kernel.  Layout of the buffer in int32 words:
+ * [0,16) info (items, partial slots, 1 = capacity exceeded, cost share per pair); [16, 16+1025) first item of
+ * every pair; then, each padded to 4 words, pieces per unit and first slot per unit (units = rows x head
+ * groups); a 64-bit scratch word per unit (padded to an even count); then the items, 8 words each: row, head
+ * group, first tile, tiles, partial slot (-1 = writes the final output), entries of the row, the row's second
+ * length (CSA: causal bound; HCA: compressed entries), 0. */
+int dsv4_attn_plan_host(const Dsv4PlanParams* p);
 
 /*
  * The reference's entry point, kept symbol- and argument-compatible
@@ -436,24 +505,18 @@ int dsv4_kv_quantize_insert(const Dsv4KvQuantizeInsertParams* p, void* stream);
 int dsv4_csa_sparse_decode_simt(const Dsv4CsaSparseDecodeParams* p, void* stream);
 int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream);
 
-/*
- * Profiling aid.  While a non-NULL device buffer of 4 x 1024 uint64 is set,
- * thread block (0,0,0) of every decode launch stores %globaltimer values of
- * its pipeline phases there (role 0 softmax, 1 MMA issue, 2 loader, 3 block
- * phases; two slots per tile).  Process-wide, not thread-safe; pass NULL to
- * switch it off.  No counterpart in the reference.
- */
-void dsv4_debug_set_trace(void* device_buffer);
-
-/* Profiling aid: pipeline experiment switches for the next launches (0 = product
- * behaviour).  bit1: no L2 prefetch of the cache entries; bit4: use the cluster-pair
- * kernel (two blocks split the query/key columns and exchange halves of S through
- * distributed shared memory) instead of the default kernel; bit5 (packed layout only): the two
- * blocks of a row and head group run as a cluster pair in which each fetches and dequantises half
- * of every tile and forwards it to the other (results bit-identical to the default kernel).
- * bit6: launch the split-KV merge as an ordinary kernel instead of as a programmatic dependent of
- * the decode kernel.  No counterpart in the reference. */
+/* Test switches, process-wide (read once per call); 0 = product behaviour.  bit6: launch the split-KV
+ * merge and the indexer's top-k as ordinary kernels instead of as programmatic dependents of the kernel
+ * before them.  No counterpart in the reference. */
 void dsv4_debug_set_flags(int flags);
+
+/* Test aid for the error path of the bounded waits.  wait_ns: limit of every wait inside the decode
+ * kernels (0 = the default, 2 s).  drop_tile >= 0: in every decode block the loaders withhold the
+ * hand-over of the tile with that running number, so that the waits behind it run out; the kernel
+ * must then return with `status` naming the wait (no trap, no fault) and the next launch must be
+ * unaffected.  drop_tile = -1 switches it off.  The reference's counterpart is the trap after a
+ * cycle budget in hca/sm100/helpers.h:183-206. */
+void dsv4_debug_set_wait(unsigned long long wait_ns, int drop_tile);
 
 /* Library identification: (major << 16) | minor. */
 int dsv4_attn_version(void);

@@ -30,30 +30,45 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
 
 
-def test_struct_sizes_match_header():
-    """ctypes mirrors of the parameter structs have the C layout (checked by
-    compiling a tiny C program against the header)."""
-    import subprocess, tempfile, sys
+STRUCTS = {
+    # C struct name -> ctypes mirror
+    "Dsv4CsaSparseDecodeParams": "CsaSparseDecodeParams",
+    "Dsv4HcaDenseDecodeParams": "HcaDenseDecodeParams",
+    "Dsv4CombineParams": "CombineParams",
+    "Dsv4PlanParams": "PlanParams",
+    "Dsv4CsaCompressReduceParams": "CsaCompressReduceParams",
+    "Dsv4IndexerTopkParams": "IndexerTopkParams",
+    "Dsv4RopeNormParams": "RopeNormParams",
+    "Dsv4HcaPackedDecodeParams": "HcaPackedDecodeParams",
+    "Dsv4CacheDest": "CacheDest",
+    "Dsv4HcaCompressParams": "HcaCompressParams",
+    "Dsv4KvQuantizeInsertParams": "KvQuantizeInsertParams",
+}
+
+
+def test_struct_layouts_match_header():
+    """Every ctypes mirror of a parameter struct has the C layout: size and the offset of
+    every field, printed by a tiny C program compiled against the header."""
+    import subprocess, tempfile
     from dsv4_attn_b200 import _lib
-    src = r'''
-#include <stdio.h>
-#include <stddef.h>
-#include "dsv4_attn.h"
-int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(Dsv4CsaSparseDecodeParams), offsetof(Dsv4CsaSparseDecodeParams, status),
-         sizeof(Dsv4HcaDenseDecodeParams), offsetof(Dsv4HcaDenseDecodeParams, status),
-         sizeof(Dsv4CombineParams), offsetof(Dsv4CombineParams, stride_lse_n));
-  return 0; }
-'''
+    header = (ROOT / "include" / "dsv4_attn.h").read_text()
+    declared = set(re.findall(r"typedef struct (Dsv4\w+)", header))
+    assert declared == set(STRUCTS), f"structs without a layout check: {declared ^ set(STRUCTS)}"
+    lines, want = [], []
+    for cname, pyname in STRUCTS.items():
+        mirror = getattr(_lib, pyname)
+        lines.append(f'printf("%zu\\n", sizeof({cname}));')
+        want.append(ctypes.sizeof(mirror))
+        for fname, _ in mirror._fields_:
+            lines.append(f'printf("%zu\\n", offsetof({cname}, {fname}));')
+            want.append(getattr(mirror, fname).offset)
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "dsv4_attn.h"\nint main(void) {\n' + "\n".join(lines) + "\nreturn 0; }\n"
     with tempfile.TemporaryDirectory() as td:
         c = Path(td) / "s.c"
         c.write_text(src)
         exe = Path(td) / "s"
         subprocess.run(["gcc", "-I", str(ROOT / "include"), str(c), "-o", str(exe)], check=True)
         got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
-    want = [ctypes.sizeof(_lib.CsaSparseDecodeParams), _lib.CsaSparseDecodeParams.status.offset,
-            ctypes.sizeof(_lib.HcaDenseDecodeParams), _lib.HcaDenseDecodeParams.status.offset,
-            ctypes.sizeof(_lib.CombineParams), _lib.CombineParams.stride_lse_n.offset]
     assert got == want
 
 

@@ -329,63 +329,6 @@ def test_reference_entry_point_split_path(lib):
     gu.check_out(gu.out_to_f32(O), want, "hca_decode_fwd split")
 
 
-def test_cluster_pair_kernel_variant(lib):
-    """The alternative decode kernel (a cluster pair splits the query/key columns
-    and exchanges halves of S through distributed shared memory), selected with
-    the profiling switch, gives the same results as the default kernel."""
-    lib.LIB.dsv4_debug_set_flags(16)
-    try:
-        case = orc.make_csa_case(seed=81, B=3, s_q=2, H=128, n_entries=[700, 1500, 90], topk=512, ragged=True)
-        want_out, want_lse = orc.csa_sparse_decode(case.q, case.pool, case.block_table, case.indices,
-                                                   case.sm_scale, kv_len=case.kv_len)
-        for splits in (1, 3):
-            out, lse = run_csa(lib, case, num_splits=splits)
-            gu.check_out(out, want_out, f"pair kernel splits={splits}")
-            gu.check_lse(lse, want_lse, f"pair kernel splits={splits}")
-        h = orc.make_hca_case(seed=82, B=2, s_q=1, H=128, kv_len=[782, 100], win_len=[128, 7], with_sink=True)
-        want_out, want_lse = orc.hca_dense_decode(h.q, h.pool, h.block_table, h.kv_len, h.win, h.win_len, h.sm_scale,
-                                                  sink=h.sink)
-        out, lse = run_hca(lib, h, num_splits=1)
-        gu.check_out(out, want_out, "pair kernel hca")
-        gu.check_lse(lse, want_lse, "pair kernel hca")
-        z, kw = golden("ref_layout_ragged")
-        c = orc.make_ref_layout_case(**kw)
-        d = gu.dev
-        O = lib.hca_decode_fwd(d(c.Q, torch.bfloat16), d(c.Kc), d(c.Kc_s), d(c.Kc_rope, torch.bfloat16),
-                               d(c.Kswa), d(c.Kswa_s), d(c.Kswa_rope, torch.bfloat16), d(c.sink), c.sm_scale,
-                               M_cur=kw["M_cur"], swa_len=kw["swa_len"])
-        torch.cuda.synchronize()
-        gu.check_out(gu.out_to_f32(O), z["out_fp8_dequant"], "pair kernel reference layout")
-    finally:
-        lib.LIB.dsv4_debug_set_flags(0)
-
-
-def test_shared_loader_cluster_pair_variant(lib):
-    """The other selectable variant of the decode kernel - the two blocks of a row and head
-    group form a cluster pair, each fetches and dequantises half of every tile and forwards it to
-    the other by bulk copies through distributed shared memory - computes exactly what the
-    default kernel computes: same operands, same MMAs, bit-identical output."""
-    case = orc.make_csa_case(seed=83, B=3, s_q=2, H=128, n_entries=[700, 1500, 90], topk=512, ragged=True)
-    h = orc.make_hca_case(seed=84, B=2, s_q=1, H=128, kv_len=[782, 100], win_len=[128, 7], with_sink=True)
-    base = {}
-    for splits in (1, 3):
-        base[("csa", splits)] = run_csa(lib, case, num_splits=splits)
-    base[("hca", 1)] = run_hca(lib, h, num_splits=1)
-    lib.LIB.dsv4_debug_set_flags(32)
-    try:
-        for splits in (1, 3):
-            out, lse = run_csa(lib, case, num_splits=splits)
-            assert np.array_equal(out, base[("csa", splits)][0]) and np.array_equal(lse, base[("csa", splits)][1])
-        out, lse = run_hca(lib, h, num_splits=1)
-        assert np.array_equal(out, base[("hca", 1)][0]) and np.array_equal(lse, base[("hca", 1)][1])
-        want_out, want_lse = orc.hca_dense_decode(h.q, h.pool, h.block_table, h.kv_len, h.win, h.win_len, h.sm_scale,
-                                                  sink=h.sink)
-        gu.check_out(out, want_out, "shared-loader pair hca")
-        gu.check_lse(lse, want_lse, "shared-loader pair hca")
-    finally:
-        lib.LIB.dsv4_debug_set_flags(0)
-
-
 @pytest.mark.parametrize("page_size", [16, 64])
 def test_packed_pages_decode_vs_reference_outputs(lib, page_size):
     """Packed cache pages read in place: the reference-layout golden cases repacked into
