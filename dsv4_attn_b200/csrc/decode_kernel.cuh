@@ -560,6 +560,22 @@ __device__ __forceinline__ void copy_q_chunks_to_tmem(uint32_t stage_base, uint3
     }
 }
 
+// A loader warp's share of the Q set-up of an item: wait for the TMA,
+// copy two of the staged chunks to tensor memory, convert this thread's part of the chunks that stay in shared
+// memory.  Returns false when the wait ran out.
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ bool loader_q_setup(uint32_t bar_q_full, uint32_t parity, unsigned long long wait_ns, uint32_t stage_base,
+                                            uint32_t tmem, uint32_t q_base, int lw, int lane, int ltid) {
+    const bool w = ptx::mbar_wait(bar_q_full, parity, wait_ns);
+    if (!__all_sync(0xFFFFFFFFu, w)) return false;
+    copy_q_chunks_to_tmem<use_f16(SRC)>(stage_base, tmem, lw, lane);
+    if constexpr (use_f16(SRC)) convert_q_smem<SmemLayout<NCHUNK>::kQBytes>(q_base, ltid);
+    ptx::fence_proxy_async_smem();
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before_sync();
+    return true;
+}
+
 // The Q rows of an item pulled into L2 ahead of their use: 128 rows x NCHUNK x 128 bytes, spread over the calling threads.
 template <int NCHUNK>
 __device__ __forceinline__ void prefetch_q_l2(const DecodeArgs& a, int n, int hg, int t, int nthreads) {
@@ -696,29 +712,51 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         LoaderRegs<SRC> regs_a, regs_b;
         uint32_t ma = 0, mb = 0;      // tags of the tiles in the two register sets
         uint32_t gt = 0, qn = 0;
-        uint32_t pend[2] = {0u, 0u};     // the epilogue (by its running number) that must have released the stage before it is written again
+        uint32_t pend0 = 0u, pend1 = 0u;     // per stage: the epilogue (by its running number) that must have released it before it is written again
         bool lok = true;
 
-        // start the loads of tile t of the stream into `regs`; its tag goes to mt (0 past the end of the stream)
-        auto fetch_tile = [&](uint32_t t, LoaderRegs<SRC>& regs, uint32_t& mt) {
+        // What the resolvers wrote for tile t of the stream, read into registers ahead of its loads: this lane's two
+        // record numbers, this warp's validity bits, the tile's tag (0 past the end of the stream).
+        struct TileInfo { uint32_t id[2]; uint32_t vmask; uint32_t meta; };
+        auto peek_tile = [&](uint32_t t) -> TileInfo {
+            TileInfo ti{{0u, 0u}, 0u, 0u};
             const uint32_t slot = t % kRing;
-            const bool w = ptx::mbar_wait(bar_res_full + 8 * slot, (t / kRing) & 1u, wait_ns);
-            if (!__all_sync(0xFFFFFFFFu, w)) {
-                report_status(a.status, kStatusWaitResolver, 2, int(t));
-                lok = false;
-                mt = 0u;
-                return;
-            }
             const TileSlot& ts = misc->ring[slot];
-            mt = ts.meta;
-            if (!(mt & kMetaTile)) return;       // end of the stream (nothing to release: the resolver has stopped)
-            uint32_t id[2];
-            id[0] = ts.id[row0 + (lane >> 3)];
-            id[1] = ts.id[row0 + 4 + (lane >> 3)];
-            const uint32_t vmask = uint32_t(ts.mask >> row0) & 0xFFu;
-            loader_fetch<SRC>(a, id, vmask, lane, regs);
+            // The slot is normally long written (the resolver runs several tiles ahead): probe its barrier and read
+            // the slot in one go, so that the two round trips through the shared-memory path overlap; only if the
+            // probe fails, wait and read again.
+            bool ready = ptx::mbar_test_wait(bar_res_full + 8 * slot, (t / kRing) & 1u);
+            ti.meta = ts.meta;
+            ti.id[0] = ts.id[row0 + (lane >> 3)];
+            ti.id[1] = ts.id[row0 + 4 + (lane >> 3)];
+            uint64_t mask = ts.mask;
+            if (!__all_sync(0xFFFFFFFFu, ready)) {
+                ready = ptx::mbar_wait(bar_res_full + 8 * slot, (t / kRing) & 1u, wait_ns);
+                if (!__all_sync(0xFFFFFFFFu, ready)) {
+                    report_status(a.status, kStatusWaitResolver, 2, int(t));
+                    lok = false;
+                    ti.meta = 0u;
+                    return ti;
+                }
+                ti.meta = *reinterpret_cast<const volatile uint32_t*>(&ts.meta);
+                ti.id[0] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + (lane >> 3)]);
+                ti.id[1] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + 4 + (lane >> 3)]);
+                mask = *reinterpret_cast<const volatile uint64_t*>(&ts.mask);
+            }
+            if (!(ti.meta & kMetaTile)) return ti;       // end of the stream (nothing to release: the resolver has stopped)
+            ti.vmask = uint32_t(mask >> row0) & 0xFFu;
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_res_empty + 8 * slot);
+            return ti;
+        };
+        // start the loads of that tile into `regs`; its tag goes to mt
+        auto issue_tile = [&](const TileInfo& ti, LoaderRegs<SRC>& regs, uint32_t& mt) {
+            mt = ti.meta;
+            if (mt & kMetaTile) loader_fetch<SRC>(a, ti.id, ti.vmask, lane, regs);
+        };
+        auto fetch_tile = [&](uint32_t t, LoaderRegs<SRC>& regs, uint32_t& mt) {
+            const TileInfo ti = peek_tile(t);
+            issue_tile(ti, regs, mt);
         };
         // Only what the first tile needs goes out before the main loop: the number of loads an SM keeps in
         // flight is limited, and everything queued here delays tile 0.
@@ -728,6 +766,38 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             lok = false;
         }
         const uint32_t tmem = misc->tmem_base;
+
+        // the stage of tile `g` must be free before it is written: the P.V of the tile two before it has completed, and
+        // an output staged there (an item that ended with that tile) has been written out
+        auto wait_stage_free = [&](uint32_t g) {
+            const int st = int(g & 1u);
+            if (g >= 2u) {
+                // warp-uniform outcome: the warp-collective operations below need all lanes
+                const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, ((g >> 1) - 1u) & 1u, wait_ns);
+                if (!__all_sync(0xFFFFFFFFu, w)) {
+                    report_status(a.status, kStatusWaitKvFree, 2, int(g));
+                    lok = false;
+                    return;
+                }
+            }
+            const uint32_t need = st ? pend1 : pend0;
+            if (need != 0u) {
+                const unsigned long long t0 = ptx::globaltimer_ns();
+                bool free_now = false;
+                while (true) {
+                    free_now = misc->epi_done[0] >= need && misc->epi_done[1] >= need &&
+                               misc->epi_done[2] >= need && misc->epi_done[3] >= need;
+                    if (free_now || ptx::globaltimer_ns() - t0 > wait_ns) break;
+                }
+                if (!__all_sync(0xFFFFFFFFu, free_now)) {
+                    report_status(a.status, kStatusWaitEpilogue, 2, int(g));
+                    lok = false;
+                    return;
+                }
+                __threadfence_block();
+                if (st) pend1 = 0u; else pend0 = 0u;
+            }
+        };
 
         // one step: store the tile in `regs` (tag `mt`), then start the loads of the tile after next into the same set
         auto tile_step = [&](LoaderRegs<SRC>& regs, uint32_t& mt, auto first_tag) {
@@ -740,17 +810,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 // had completed and this tile's stage was free): the chunks that stay in shared memory land at their
                 // place and are converted there; the chunks that live in tensor memory land in this tile's stage,
                 // which is written only after every loader warp has copied its share out of it.
-                const bool w = ptx::mbar_wait(bar_q_full, qn & 1u, wait_ns);
-                if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn));
-                if (!__all_sync(0xFFFFFFFFu, w)) {
+                if (!loader_q_setup<NCHUNK, SRC>(bar_q_full, qn & 1u, wait_ns, kv_base + uint32_t(st) * L::kKvStageBytes, tmem, q_base,
+                                                 lw, lane, ltid)) {
                     report_status(a.status, kStatusWaitQ, 2, int(g));
                     lok = false;
-                } else {
-                    copy_q_chunks_to_tmem<use_f16(SRC)>(kv_base + uint32_t(st) * L::kKvStageBytes, tmem, lw, lane);
-                    if constexpr (use_f16(SRC)) convert_q_smem<L::kQBytes>(q_base, ltid);
-                    ptx::fence_proxy_async_smem();
-                    ptx::tmem_wait_st();
-                    ptx::tc_fence_before_sync();
                 }
                 __syncwarp();
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn) + 1);
@@ -767,32 +830,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 }
                 if (lw == 0 && lane == 0) trace_mark(a, 2, 600 + 4 * int(qn) + 2);
             }
-            if (g >= 2u) {
-                // warp-uniform outcome: the warp-collective operations below need all lanes
-                const bool w = ptx::mbar_wait(bar_kv_free + 8 * st, ((g >> 1) - 1u) & 1u, wait_ns);
-                if (!__all_sync(0xFFFFFFFFu, w)) {
-                    report_status(a.status, kStatusWaitKvFree, 2, int(g));
-                    lok = false;
-                    return;
-                }
-            }
-            if (pend[st] != 0u) {
-                // the stage held the output staging of an earlier item: wait until all four softmax warps are through with it
-                const unsigned long long t0 = ptx::globaltimer_ns();
-                bool free_now = false;
-                while (true) {
-                    free_now = misc->epi_done[0] >= pend[st] && misc->epi_done[1] >= pend[st] &&
-                               misc->epi_done[2] >= pend[st] && misc->epi_done[3] >= pend[st];
-                    if (free_now || ptx::globaltimer_ns() - t0 > wait_ns) break;
-                }
-                if (!__all_sync(0xFFFFFFFFu, free_now)) {
-                    report_status(a.status, kStatusWaitEpilogue, 2, int(g));
-                    lok = false;
-                    return;
-                }
-                __threadfence_block();
-                pend[st] = 0u;
-            }
+            wait_stage_free(g);
+            if (!lok) return;
             if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 1);
             if (lane == 0) reinterpret_cast<volatile uint8_t*>(&misc->valid_mask[st])[lw] = uint8_t(regs.vmask);
             // in two groups (chunks 0-3, then the rest with the RoPE tail), so that the QK MMAs of this tile
@@ -814,7 +853,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 2);
             if (mt & kMetaLast) {
                 ++qn;
-                pend[st] = qn;       // the item's output is staged in the stage of its last tile
+                if (st) pend1 = qn; else pend0 = qn;       // the item's output is staged in the stage of its last tile
             }
             ++gt;
             if constexpr (kFirstStep) {
@@ -880,23 +919,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 bool ok = have_tmem;
                 uint32_t gt = 0, qn = 0;
                 uint32_t pend0 = 0u, pend1 = 0u;         // per stage: the epilogue (running number) whose output staging it holds
-                uint32_t last_bar = 0, last_par = 0;     // the S commit of the last tile issued
-                bool have_last = false;
                 Item cur = get_item(0);
                 for (int k = 0; k < n_items && ok; ++k) {
-                    // (the next item's record is requested now: a load issued at the end of the item would queue up
-                    // behind the loaders' traffic for a microsecond or two)
-                    const Item nxt = (k + 1 < n_items) ? get_item(k + 1) : cur;
                     const int ntiles = cur.ntiles;
                     if (ntiles > 0) {
-                        trace_mark(a, 1, 700 + 4 * int(qn));
-                        // every Q.K^T of the previous item must have completed before its Q is replaced
-                        if (have_last && !ptx::mbar_wait(last_bar, last_par, wait_ns)) {
-                            report_status(a.status, kStatusWaitSFull, 1, cur.tile0);
-                            ok = false;
-                            break;
+                        // every Q.K^T of the previous item must have completed before its Q is replaced (its last
+                        // tile's S commit is the last one this thread made) ...
+                        if (gt > 0u) {
+                            const uint32_t gl = gt - 1u;
+                            if (!ptx::mbar_wait(bar_s_full + 8 * int(gl & 1u), (gl >> 1) & 1u, wait_ns)) {
+                                report_status(a.status, kStatusWaitSFull, 1, int(gt));
+                                ok = false;
+                                break;
+                            }
                         }
-                        trace_mark(a, 1, 700 + 4 * int(qn) + 1);
                         // ... and the stage of the item's first tile must be free: the chunks bound for tensor memory are
                         // staged there
                         const int st0 = int(gt & 1u);
@@ -905,7 +941,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             ok = false;
                             break;
                         }
-                        trace_mark(a, 1, 700 + 4 * int(qn) + 2);
                         // (it may also still hold the output staging of the item before the previous one, when that one
                         // had a single tile)
                         {
@@ -941,7 +976,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             ptx::tma_load_2d(dst, &a.q_map, c * 64, qrow0, bar_q_full);
                         }
                         if (!ptx::mbar_wait(bar_q_ready, qn & 1u, wait_ns)) {
-                            report_status(a.status, kStatusWaitQ, 1, cur.tile0);
+                            report_status(a.status, kStatusWaitQ, 1, int(gt));
                             ok = false;
                             break;
                         }
@@ -952,7 +987,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             const uint32_t par = (g >> 1) & 1u;
                             for (int grp = 0; grp < kNumKvGroups; ++grp) {
                                 if (!ptx::mbar_wait(bar_kv_full + kKvFullStride * st + 8 * grp, par, wait_ns)) {
-                                    report_status(a.status, kStatusWaitKvFull, 1, cur.tile0 + it);
+                                    report_status(a.status, kStatusWaitKvFull, 1, int(g));
                                     ok = false;
                                     break;
                                 }
@@ -964,14 +999,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                             if (ok) {
                                 trace_mark(a, 1, 4 * int(g) + 2);
                                 ptx::mma_commit(bar_s_full + 8 * st);
-                                last_bar = bar_s_full + 8 * st;  last_par = par;  have_last = true;
                             }
                         }
                         gt += uint32_t(ntiles);
                         ++qn;
                         if ((gt - 1u) & 1u) pend1 = qn; else pend0 = qn;     // the item's output is staged in the stage of its last tile
                     }
-                    cur = nxt;
+                    if (k + 1 < n_items) cur = get_item(k + 1);
                 }
             }
             __syncwarp();
@@ -987,7 +1021,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 uint32_t gt = 0;
                 Item cur = get_item(0);
                 for (int k = 0; k < n_items && ok; ++k) {
-                    const Item nxt = (k + 1 < n_items) ? get_item(k + 1) : cur;
                     const int ntiles = cur.ntiles;
                     for (int it = 0; it < ntiles; ++it) {
                         const uint32_t g = gt + uint32_t(it);
@@ -995,7 +1028,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                         // (the first P of an item is written after the softmax warps have read the previous item's O out
                         // of tensor memory, so the overwrite below needs no barrier of its own)
                         if (!ptx::mbar_wait(bar_p_full + 8 * st, (g >> 1) & 1u, wait_ns)) {
-                            report_status(a.status, kStatusWaitPFull, 1, cur.tile0 + it);
+                            report_status(a.status, kStatusWaitPFull, 3, int(g));
                             ok = false;
                             break;
                         }
@@ -1014,7 +1047,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     }
                     if (ok && ntiles > 0) ptx::mma_commit(bar_o_full);
                     gt += uint32_t(ntiles);
-                    cur = nxt;
+                    if (k + 1 < n_items) cur = get_item(k + 1);
                 }
             }
             __syncwarp();
@@ -1049,8 +1082,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 if (++ct >= ci.ntiles) { ++ck;  kc_seek(); }
             };
             kc_seek();
+            auto kc_next = [&]() -> TileCtx {
+                const TileCtx c = kc_ctx();
+                kc_advance();
+                return c;
+            };
             bool rok = true;
-            uint32_t t = 0;            // tiles published so far
+            uint32_t t = 0;            // the stream tile published next
             auto publish = [&](uint32_t meta, uint32_t id0, uint32_t id1) {
                 const uint32_t slot = t % kRing;
                 if (t >= uint32_t(kRing)) {
@@ -1072,12 +1110,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 }
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_res_full + 8 * slot);
+                if (lane == 0) trace_mark(a, 3, 512 + int(t));
                 ++t;
             };
             // three-stage pipeline over the stream: index values of the tile two ahead, block-table values of the
             // next tile, record numbers of this one
-            TileCtx c0 = kc_ctx();  kc_advance();
-            TileCtx c1 = kc_ctx();  kc_advance();
+            TileCtx c0 = kc_next();
+            TileCtx c1 = kc_next();
             int e1a = -1, e1b = -1;
             PendingId p0a, p0b;
             {
@@ -1089,10 +1128,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 p0a = resolve_issue<SRC>(a, c0, e0a, lane);
                 p0b = resolve_issue<SRC>(a, c0, e0b, lane + 32);
             }
-            if (c0.meta & kMetaTile) prefetch_q_l2<NCHUNK>(a, c0.n, int((c0.meta >> 16) & 0xFFu), lane, 32);
+            if ((c0.meta & (kMetaTile | kMetaFirst)) == (kMetaTile | kMetaFirst))
+                prefetch_q_l2<NCHUNK>(a, c0.n, int((c0.meta >> 16) & 0xFFu), lane, 32);
             while (rok && (c0.meta & kMetaTile)) {
                 // the next tile's block-table loads go out before this tile's are looked at
-                const TileCtx c2 = kc_ctx();  kc_advance();
+                const TileCtx c2 = kc_next();
                 const PendingId p1a = resolve_issue<SRC>(a, c1, e1a, lane);
                 const PendingId p1b = resolve_issue<SRC>(a, c1, e1b, lane + 32);
                 if constexpr (SRC == kSrcCsa) {
@@ -1123,16 +1163,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
         Item cur = get_item(0);
         for (int k = 0; k < n_items && ok; ++k) {
             const int ntiles = cur.ntiles;
-            const int n = cur.n, hg = cur.hg;
-            const bool final_out = cur.slot < 0;
-            const int h = hg * kHeadsPerCta + r;
-            const bool write = h < a.H;
-            const int64_t prow0 = final_out ? 0 : partial_row0(cur);
-            // destination of this thread's head row (this block's half of the value columns), and of its LSE
-            __nv_bfloat16* const out_rows = final_out ? a.out + (int64_t(n) * a.H + hg * kHeadsPerCta) * 512 + half * kDvHalf
-                                                      : reinterpret_cast<__nv_bfloat16*>(a.partial_o) + prow0 * 512 + half * kDvHalf;
+            const int n = cur.n, hg = cur.hg, slot = cur.slot, tile0 = cur.tile0;
+            // destination of the item's head rows (this block's half of the value columns) and of their LSEs; worked
+            // out where it is needed, so that nothing of it is held in registers through the tile loop
+            auto destination = [&](int64_t& prow0) -> __nv_bfloat16* {
+                Item it{};
+                it.n = n;  it.hg = hg;  it.slot = slot;
+                prow0 = slot < 0 ? 0 : partial_row0(it);
+                return slot < 0 ? a.out + (int64_t(n) * a.H + hg * kHeadsPerCta) * 512 + half * kDvHalf
+                                : reinterpret_cast<__nv_bfloat16*>(a.partial_o) + prow0 * 512 + half * kDvHalf;
+            };
             if (ntiles <= 0) {
                 // Nothing to attend to: zero output, LSE = -inf.
+                const bool final_out = slot < 0;
+                const int h = hg * kHeadsPerCta + r;
+                const bool write = h < a.H;
+                int64_t prow0;
+                __nv_bfloat16* const out_rows = destination(prow0);
                 for (int i = tid; i < kHeadsPerCta * (kDvHalf / 8); i += kNumSoftmaxWarps * 32) {
                     const int rr = i / (kDvHalf / 8), v = i % (kDvHalf / 8);
                     if (hg * kHeadsPerCta + rr < a.H)
@@ -1157,7 +1204,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 {
                     const bool w = ptx::mbar_wait(bar_s_full + 8 * st, (g >> 1) & 1u, wait_ns);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_status(a.status, kStatusWaitSFull, 0, cur.tile0 + it);
+                        report_status(a.status, kStatusWaitSFull, 0, tile0 + it);
                         ok = false;  break;
                     }
                 }
@@ -1221,7 +1268,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     const uint32_t gp = g - 1u;
                     const bool w = ptx::mbar_wait(bar_kv_free + 8 * int(gp & 1u), (gp >> 1) & 1u, wait_ns);
                     if (!__all_sync(0xFFFFFFFFu, w)) {
-                        report_status(a.status, kStatusWaitKvFree, 0, cur.tile0 + it);
+                        report_status(a.status, kStatusWaitKvFree, 0, tile0 + it);
                         ok = false;  break;
                     }
                     ptx::tc_fence_after_sync();
@@ -1245,8 +1292,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 if (tid == 0) trace_mark(a, 0, 4 * int(g) + 1);
             }
             // ── epilogue ──
-            const int tile_end = cur.tile0 + ntiles;
+            const int tile_end = tile0 + ntiles;
             if (k + 1 < n_items) cur = get_item(k + 1);      // the next item's record arrives while this one is written out
+            const bool final_out = slot < 0;
+            const int h = hg * kHeadsPerCta + r;
+            const bool write = h < a.H;
+            int64_t prow0;
+            __nv_bfloat16* const out_rows = destination(prow0);
             if (ok) {
                 const bool w = ptx::mbar_wait(bar_o_full, qn & 1u, wait_ns);
                 if (!__all_sync(0xFFFFFFFFu, w)) {
