@@ -21,8 +21,15 @@ R chosen so that the copies together are several times larger than L2 - so every
 step finds its inputs in HBM, not in L2, without a flush inside the timed region.
 The same step timed alone (L2 flushed by a 512 MiB write before each launch, one
 event pair per launch, eager launch) is reported beside it as "isolated".
-`--impl reference` times the CPU restatement of the reference's PyTorch decode
-path (the oracle) on a bounded sample of the same workload on the host cores.
+`--impl reference` times the reference's own PyTorch decode path
+(bench/bench/reference.py, hca_decode_forward in fp32 mode on exactly dequantised,
+gathered rows) on the host cores, on a bounded sample of the same workload; where
+the staged copy of the reference's Python is absent it falls back to the numpy
+restatement (the oracle) and says "port".
+
+After every timed region, and outside it, a sample of rows of the step's result is
+compared with the CPU oracle; the line carries the errors and the run fails when they
+are out of tolerance.
 """
 from __future__ import annotations
 
@@ -46,14 +53,23 @@ METRIC = "decode_attn_kv_bandwidth"
 UNIT = "TB/s"
 
 WORKLOADS = {
-    # name: (kind, kwargs)  -- shapes of the benchmark configurations
-    "hca_b64_h128_ctx100k": ("hca", dict(B=64, s_q=1, H=128, kv_len=782, win_len=128)),
+    # name: (kind, kwargs)  -- shapes of the benchmark configurations.  num_splits = n: the static grid of
+    # rows x head groups x n blocks; plan_splits = n: resident blocks walking a plan of the device scheduler
+    # (n = 0: the scheduler balances, n >= 1: exactly n pieces per row and head group)
+    "hca_b64_h128_ctx100k": ("hca", dict(B=64, s_q=1, H=128, kv_len=782, win_len=128, num_splits=1)),
     "csa_b64_h128_topk512_ctx3072": ("csa", dict(B=64, s_q=1, H=128, n_entries=768, topk=512, num_splits=1)),
-    "csa_b128_nextn2_topk2048_ctx100k_split8": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048, num_splits=8)),
-    # the same shape with the split count left to the library's planner
-    "csa_b128_nextn2_topk2048_ctx100k_planned": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048)),
-    "csa_b64_h128_topk2048_ctx100k": ("csa", dict(B=64, s_q=1, H=128, n_entries=25000, topk=2048)),
+    # configuration 3 with the 8 splits it names: as 8 scheduled pieces per row, and on the static grid
+    "csa_b128_nextn2_topk2048_ctx100k_split8": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048, plan_splits=8)),
+    "csa_b128_nextn2_topk2048_ctx100k_split8_static_grid": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048, num_splits=8)),
+    # the same shape with the cutting left to the scheduler
+    "csa_b128_nextn2_topk2048_ctx100k_planned": ("csa", dict(B=128, s_q=2, H=128, n_entries=25000, topk=2048, plan_splits=0)),
+    "csa_b64_h128_topk2048_ctx100k": ("csa", dict(B=64, s_q=1, H=128, n_entries=25000, topk=2048, num_splits=1)),
+    # small batches, where the scheduler has to spread few rows over all SMs
+    "hca_b8_h128_ctx100k_planned": ("hca", dict(B=8, s_q=1, H=128, kv_len=782, win_len=128, plan_splits=0)),
+    "csa_b8_h128_topk2048_ctx100k_planned": ("csa", dict(B=8, s_q=1, H=128, n_entries=25000, topk=2048, plan_splits=0)),
 }
+PARITY_ROWS = 16
+TOL = dict(max_abs=2e-2, mean_abs=2e-3, lse_rel=1e-3)
 # The mixed data-parallel workload: a global batch of 1024 requests with log-normal raw
 # context (median 8k, sigma 1.0 - the configuration leaves sigma open - clipped to
 # [1k, 128k]), sharded over the GPUs by context length; one CSA layer and one HCA layer
@@ -155,12 +171,12 @@ def build_workload(name, seed, device):
     from dsv4_attn_b200 import synth
     kind, kw = WORKLOADS[name]
     kw = dict(kw)
-    splits = kw.pop("num_splits", None)
+    mode = {"num_splits": kw.pop("num_splits", None), "plan_splits": kw.pop("plan_splits", None)}
     if kind == "hca":
         w = synth.make_hca(seed, device=device, **kw)
     else:
         w = synth.make_csa(seed, device=device, **kw)
-    return kind, w, splits
+    return kind, w, mode
 
 
 def build_mixed(rank, world, device):
@@ -170,37 +186,66 @@ def build_mixed(rank, world, device):
     return synth.make_mixed(4000 + rank, [ctx[i] for i in mine], device=device), len(mine)
 
 
-def make_step(kind, w, splits):
-    """Returns (fn() -> (out, lse), launches per call, num_splits).  All buffers
-    (outputs, split workspace) are allocated once, outside the timed region."""
+def make_step(kind, w, mode):
+    """Returns (fn() -> (out, lse), launches per call, description of the split mode, status, plan).  All buffers
+    (outputs, split workspace, the plan) are made once, outside the timed region: a plan depends on the
+    batch's lengths only and serves every layer of a decode step."""
     import torch
     import dsv4_attn_b200 as lib
     B, s_q, H, _ = w.q.shape
     rows = B * s_q
-    if kind == "hca":
-        if splits is None:
-            splits = lib.plan_splits(rows, H, w.max_len)
+    dev = w.q.device
+    plan_splits, splits = mode.get("plan_splits"), mode.get("num_splits")
+    plan = ws = None
+    if plan_splits is not None:
+        if kind == "hca":
+            plan = lib.plan_hca(B, s_q, H, w.kv_len, w.win_len, num_splits=plan_splits)
+        else:
+            plan = lib.plan_csa(B, s_q, H, w.indices.shape[-1], topk_len=w.topk_len, kv_len=w.kv_len, num_splits=plan_splits)
+        desc = f"scheduled, {plan_splits if plan_splits else 'balanced'} pieces"
+        launches = 2
     else:
         if splits is None:
-            splits = lib.plan_splits(rows, H, w.indices.shape[-1])
-    out = torch.empty(B, s_q, H, 512, dtype=torch.bfloat16, device=w.q.device)
-    lse = torch.empty(B, s_q, H, dtype=torch.float32, device=w.q.device)
-    ws = lib.alloc_workspace(rows, H, splits, w.q.device) if splits > 1 else None
-    status = lib.new_status(w.q.device)
+            splits = lib.plan_splits(rows, H, w.max_len if kind == "hca" else w.indices.shape[-1])
+        ws = lib.alloc_workspace(rows, H, splits, dev) if splits > 1 else None
+        desc = f"static grid, {splits} split(s)"
+        launches = 2 if splits > 1 else 1
+    # out and lse live in one buffer, so that a host that wants them gets them with one copy
+    res = torch.empty(rows * H * 512 * 2 + rows * H * 4, dtype=torch.uint8, device=dev)
+    out = res[:rows * H * 512 * 2].view(torch.bfloat16).view(B, s_q, H, 512)
+    lse = res[rows * H * 512 * 2:].view(torch.float32).view(B, s_q, H)
+    status = lib.new_status(dev)
     if kind == "hca":
         def fn(q=None, kv_len=None, win_len=None):
             return lib.hca_dense_decode(w.q if q is None else q, w.kv_pool, w.block_table,
                                         w.kv_len if kv_len is None else kv_len, w.win_pool,
                                         w.win_len if win_len is None else win_len, w.sm_scale,
                                         attn_sink=w.attn_sink, num_splits=splits, out=out, lse=lse,
-                                        workspace=ws, status=status, max_len=w.max_len)
+                                        workspace=ws, status=status, max_len=w.max_len, plan=plan)
     else:
         def fn(q=None, indices=None):
             return lib.csa_sparse_decode(w.q if q is None else q, w.kv_pool, w.block_table,
                                          w.indices if indices is None else indices, w.sm_scale, kv_len=w.kv_len,
                                          topk_len=w.topk_len, num_splits=splits, out=out, lse=lse, workspace=ws,
-                                         status=status)
-    return fn, (2 if splits > 1 else 1), splits, status
+                                         status=status, plan=plan)
+    fn.result = res
+    return fn, launches, desc, status, plan
+
+
+def parity_sample(kind, w, out, lse, count=PARITY_ROWS):
+    """Rows of a step's result against the CPU oracle (outside every timed region).  Raises when out of tolerance."""
+    from oracle import sample_check as sc
+    if kind == "hca":
+        rows = sc.pick_rows(w.kv_len + w.win_len, count)
+        r = sc.check_hca_rows(w.q, w.kv_pool, w.block_table, w.kv_len, w.win_pool, w.win_len, w.sm_scale, out, lse, rows,
+                              sink=w.attn_sink)
+    else:
+        rows = sc.pick_rows(w.topk_len, count)
+        r = sc.check_csa_rows(w.q, w.kv_pool, w.block_table, w.indices, w.sm_scale, out, lse, rows, kv_len=w.kv_len,
+                              topk_len=w.topk_len)
+    if not sc.within_tolerance(r, **TOL):
+        raise RuntimeError(f"result out of tolerance against the oracle: {r}")
+    return {k: r[k] for k in ("parity_checked_rows", "max_abs", "mean_abs", "lse_rel")}
 
 
 def time_steps(fn, steps, warmup, flush, barrier):
@@ -261,41 +306,67 @@ def time_rotating(fns, steps, warmup, flush, barrier):
     return e0.elapsed_time(e1), ("graph" if graph is not None else "eager")
 
 
+def bind_near_gpu(dev):
+    """Keep this rank on the cores (and so its pinned buffers in the memory) of the NUMA node its GPU hangs on.
+    A launcher leaves the ranks unbound, and a pinned buffer on the far socket has to cross the socket link on every
+    copy.  Changes this process's CPU affinity only; returns what it found, for the record."""
+    import torch
+    info = {"numa_node": None, "cpus_before": None, "cpus_after": None}
+    try:
+        info["cpus_before"] = len(os.sched_getaffinity(0))
+        pr = torch.cuda.get_device_properties(dev)
+        bus = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            cpus = set()
+            for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+        info["cpus_after"] = len(os.sched_getaffinity(0))
+    except Exception as e:  # noqa: BLE001 - a box without that sysfs view: stay unbound
+        info["error"] = f"{type(e).__name__}: {e}"
+    return info
+
+
 def e2e_steps(kind, insts, steps, warmup, flush, barrier):
     """Same metric through the public API with HOST buffers: every step copies its inputs
     (q and the per-step index / length tensors) from pinned host memory, runs the decode,
-    and reads the result (out, lse) back to pinned host memory.  The three stages run on
-    their own streams (copy-in, compute, copy-out) chained by events, so that the copies of
+    and reads the result (out, lse) back to pinned host memory.  The inputs of a step lie in ONE pinned
+    buffer and go up in one copy; out and lse share one device buffer and come back in one copy.  The three
+    stages run on their own streams (copy-in, compute, copy-out) chained by events, so that the copies of
     neighbouring steps overlap the compute, as a serving engine would run them; step i
     works on instance i mod R (its own KV pool, staging and output buffers).  Returns
-    (total ms of the K steps, h2d bytes per step, d2h bytes per step)."""
+    (total ms of the K steps, h2d bytes per step, d2h bytes per step, copy rates) - the last being the
+    host link measured with the same buffers and no compute: uploads alone, downloads alone, both at once."""
     import torch
     R = len(insts)
     dev = insts[0][0].q.device
-    # One copy-in stream: back-to-back uploads on one stream reach the host link's rate (52 GB/s measured
-    # for 9.4 MB pieces), and while results are read back at the same time a split upload was slower
-    # (270 against 250 us per step; copies alone: 241 against 211 us per step for both directions).
     s_in, s_c, s_out = (torch.cuda.Stream(dev) for _ in range(3))
     main = torch.cuda.current_stream(dev)
     slots = []
     for w, fn, _ in insts:
-        hq = w.q.cpu().pin_memory()
-        dq = torch.empty_like(w.q)
-        if kind == "hca":
-            h1, h2 = w.kv_len.cpu().pin_memory(), w.win_len.cpu().pin_memory()
-            d1, d2 = torch.empty_like(w.kv_len), torch.empty_like(w.win_len)
-        else:
-            h1, d1 = w.indices.cpu().pin_memory(), torch.empty_like(w.indices)
-            h2 = d2 = None
-        out, lse = fn()
-        ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-        hl = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
-        slots.append(dict(fn=fn, hq=hq, dq=dq, h1=h1, d1=d1, h2=h2, d2=d2, ho=ho, hl=hl, ev_in=torch.cuda.Event(),
-                          ev_c=None, ev_o=None))
+        parts = [w.q] + ([w.kv_len, w.win_len] if kind == "hca" else [w.indices])
+        offs, total = [], 0
+        for t in parts:
+            offs.append(total)
+            total += -(-t.numel() * t.element_size() // 256) * 256
+        hin = torch.empty(total, dtype=torch.uint8).pin_memory()
+        din = torch.empty(total, dtype=torch.uint8, device=dev)
+        views = []
+        for t, o in zip(parts, offs):
+            nb = t.numel() * t.element_size()
+            hin[o:o + nb].copy_(t.contiguous().view(-1).view(torch.uint8).cpu())
+            views.append(din[o:o + nb].view(t.dtype).view(t.shape))
+        fn()
+        hres = torch.empty(fn.result.numel(), dtype=torch.uint8).pin_memory()
+        slots.append(dict(fn=fn, hin=hin, din=din, views=views, hres=hres, ev_in=torch.cuda.Event(), ev_c=None, ev_o=None))
     z = slots[0]
-    h2d = z["hq"].numel() * z["hq"].element_size() + z["h1"].numel() * z["h1"].element_size() + \
-        (z["h2"].numel() * z["h2"].element_size() if z["h2"] is not None else 0)
-    d2h = z["ho"].numel() * z["ho"].element_size() + z["hl"].numel() * z["hl"].element_size()
+    h2d = sum(t.numel() * t.element_size() for t in z["views"])
+    d2h = z["hres"].numel()
     torch.cuda.synchronize()
 
     def run(n):
@@ -303,23 +374,19 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
             k = slots[i % R]
             with torch.cuda.stream(s_in):
                 if k["ev_c"] is not None:
-                    s_in.wait_event(k["ev_c"])          # this instance's staging buffers are free again
-                k["dq"].copy_(k["hq"], non_blocking=True)
-                k["d1"].copy_(k["h1"], non_blocking=True)
-                if k["h2"] is not None:
-                    k["d2"].copy_(k["h2"], non_blocking=True)
+                    s_in.wait_event(k["ev_c"])          # this instance's staging buffer is free again
+                k["din"].copy_(k["hin"], non_blocking=True)
                 k["ev_in"].record(s_in)
             with torch.cuda.stream(s_c):
                 s_c.wait_event(k["ev_in"])
                 if k["ev_o"] is not None:
                     s_c.wait_event(k["ev_o"])           # its previous result has been read back
-                o, l = k["fn"](k["dq"], k["d1"], k["d2"]) if kind == "hca" else k["fn"](k["dq"], k["d1"])
+                k["fn"](*k["views"])
                 k["ev_c"] = torch.cuda.Event()
                 k["ev_c"].record(s_c)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(k["ev_c"])
-                k["ho"].copy_(o, non_blocking=True)
-                k["hl"].copy_(l, non_blocking=True)
+                k["hres"].copy_(k["fn"].result, non_blocking=True)
                 k["ev_o"] = torch.cuda.Event()
                 k["ev_o"].record(s_out)
 
@@ -371,43 +438,146 @@ def e2e_steps(kind, insts, steps, warmup, flush, barrier):
     e1.record(main)
     torch.cuda.synchronize()
     barrier()
-    return e0.elapsed_time(e1), h2d, d2h
+    total = e0.elapsed_time(e1)
+
+    # the host link alone, all ranks at the same time: the same buffers, no compute
+    def copies(up, down):
+        barrier()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(main)
+        s_in.wait_event(a0)
+        s_out.wait_event(a0)
+        for i in range(steps):
+            k = slots[i % R]
+            if up:
+                with torch.cuda.stream(s_in):
+                    k["din"].copy_(k["hin"], non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_out):
+                    k["hres"].copy_(k["fn"].result, non_blocking=True)
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
+        a1.record(main)
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1) / steps
+    copies(True, True)
+    up_ms, down_ms, both_ms = copies(True, False), copies(False, True), copies(True, True)
+    rates = {"h2d_alone_gbs": h2d / up_ms / 1e6, "d2h_alone_gbs": d2h / down_ms / 1e6,
+             "both_ms_per_step": both_ms, "both_gbs_sum": (h2d + d2h) / both_ms / 1e6}
+    return total, h2d, d2h, rates
 
 
-def cpu_baseline(kind, name, seed=0, target_s=10.0):
-    """The oracle (numpy restatement of the reference's PyTorch decode path)
-    timed on the host cores on a bounded sample of the workload's requests."""
+PYREF = ROOT / "oracle" / "_ref" / "pyref"
+
+
+def claim_host_threads():
+    """All host cores for the CPU arm: launchers such as torchrun export OMP_NUM_THREADS=1, which would
+    time the reference on one core.  Has to run before torch (and its OpenMP runtime) is imported."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0)) or n
+    except (AttributeError, OSError):
+        pass
+    for var in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "OPENBLAS_NUM_THREADS"):
+        os.environ[var] = str(n)
+    return n
+
+
+def reference_python():
+    """The reference's own decode forward (bench/bench/reference.py, staged unchanged by oracle/build_ref.py
+    into a git-ignored folder), or None when it has not been staged."""
+    if not (PYREF / "bench" / "reference.py").exists():
+        return None
+    # loaded by path under a name of its own: the reference's package is called "bench", like this file
+    name = "dsv4_reference_python"
+    if name in sys.modules:
+        return sys.modules[name]
+    try:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location(name, PYREF / "bench" / "reference.py")
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+        return mod
+    except Exception as e:  # noqa: BLE001
+        sys.modules.pop(name, None)
+        print(f"[bench] staged reference does not import ({type(e).__name__}: {e}); using the oracle port", file=sys.stderr)
+        return None
+
+
+def cpu_sample_case(kind, name, seed, sample_B):
+    """A bounded sample of the workload as host arrays: (q [rows, H, 576], rows of exactly dequantised cache
+    entries per query row [rows, n, 576], sink or None, sm_scale, attended entries).  Every row of these
+    workloads attends to the same number of entries, so the sample is one dense batch."""
     import numpy as np
     from oracle import dsv4_oracle as orc
-    _, kw = WORKLOADS[name]
-    kw = {k: v for k, v in kw.items() if k != "num_splits"}
-    sample_B = 4
+    kw = {k: v for k, v in WORKLOADS[name][1].items() if k not in ("num_splits", "plan_splits")}
     kw["B"] = sample_B
     if kind == "hca":
         c = orc.make_hca_case(seed, **kw)
-        run = lambda: orc.hca_dense_decode(c.q, c.pool, c.block_table, c.kv_len, c.win, c.win_len, c.sm_scale)
-        entries = int(c.kv_len.sum() + c.win_len.sum())
+        rows = []
+        for b in range(sample_B):
+            for j in range(kw["s_q"]):
+                n, wl = int(c.kv_len[b, j]), int(c.win_len[b, j])
+                ent = np.concatenate([orc.gather_rows(c.pool, c.block_table[b], np.arange(n)), c.win[b, :wl]], 0)
+                rows.append(orc.unpack_entries(ent))
+        sink = c.sink
     else:
         c = orc.make_csa_case(seed, **kw)
-        run = lambda: orc.csa_sparse_decode(c.q, c.pool, c.block_table, c.indices, c.sm_scale, kv_len=c.kv_len)
-        entries = int((c.indices >= 0).sum())
+        rows = [orc.unpack_entries(orc.gather_rows(c.pool, c.block_table[b], c.indices[b, j]))
+                for b in range(sample_B) for j in range(kw["s_q"])]
+        sink = None
+    kv = np.stack(rows)
+    q = c.q.reshape(-1, c.q.shape[2], c.q.shape[3])
+    return q, kv, sink, c.sm_scale, int(kv.shape[0] * kv.shape[1])
+
+
+def cpu_baseline(kind, name, seed=0, target_s=10.0, sample_B=4):
+    """The reference's CPU implementation of the decode path, timed on the host cores on a bounded sample
+    of the workload's requests: the reference's own hca_decode_forward(dtype="fp32") (bench/bench/reference.py:471-546)
+    on the exactly dequantised (and, for the sparse layer, gathered) rows - what the reference itself checks its
+    kernels against.  Falls back to the numpy restatement (kind "port") when the reference's Python is not staged."""
+    import numpy as np
+    full_B = WORKLOADS[name][1]["B"]
+    q, kv, sink, sm_scale, entries = cpu_sample_case(kind, name, seed, sample_B)
+    ref = reference_python()
+    if ref is not None:
+        import torch
+        threads = claim_host_threads()
+        torch.set_num_threads(threads)
+        H = q.shape[1]
+        tq = torch.from_numpy(q).to(torch.bfloat16)
+        tk = torch.from_numpy(kv)
+        empty = torch.zeros(tk.shape[0], 0, 512)
+        inp = ref.HCADecodeInputs(
+            Q=tq, Kc=tk[..., :512].contiguous(), Kc_rope=tk[..., 512:].to(torch.bfloat16), Kc_scales=None,
+            Kswa=empty, Kswa_rope=torch.zeros(tk.shape[0], 0, 64, dtype=torch.bfloat16), Kswa_scales=None,
+            sink_logits=torch.full((H,), float("-inf")) if sink is None else torch.from_numpy(sink), sm_scale=float(sm_scale))
+        run = lambda: ref.hca_decode_forward(inp, dtype="fp32")
+        kind_s, how = "reference", "the reference's hca_decode_forward(dtype='fp32'), torch CPU"
+        threads_used = torch.get_num_threads()
+    else:
+        from oracle import dsv4_oracle as orc
+        run = lambda: [orc.attend(q[i], kv[i], sm_scale, sink) for i in range(q.shape[0])]
+        kind_s, how = "port", "numpy float32 restatement (the staged reference Python was not found)"
+        try:
+            import threadpoolctl
+            threads_used = max([p.get("num_threads", 1) for p in threadpoolctl.threadpool_info()] or [1])
+        except Exception:
+            threads_used = os.cpu_count() or 1
     run()
     t0 = time.perf_counter()
     iters = 0
     while True:
         run()
         iters += 1
-        if time.perf_counter() - t0 > target_s or iters >= 50:
+        if time.perf_counter() - t0 > target_s or iters >= 5000:
             break
     dt = (time.perf_counter() - t0) / iters
-    try:
-        import threadpoolctl
-        threads = max([p.get("num_threads", 1) for p in threadpoolctl.threadpool_info()] or [1])
-    except Exception:
-        threads = os.cpu_count() or 1
-    return {"value": entries * ENTRY_BYTES / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{sample_B} of {WORKLOADS[name][1]['B']} requests of {name}, {iters} passes, numpy float32 oracle",
-            "ms_per_sample_pass": dt * 1e3, "host_cpus": os.cpu_count()}
+    return {"value": entries * ENTRY_BYTES / dt / 1e12, "unit": UNIT, "cores": threads_used, "kind": kind_s,
+            "sample": f"{sample_B} of {full_B} requests of {name}, {iters} passes, {how}",
+            "ms_per_sample_pass": dt * 1e3, "ms_per_full_step": dt * 1e3 * full_B / sample_B, "host_cpus": os.cpu_count()}
 
 
 def run_ours(args):
@@ -418,6 +588,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    binding = bind_near_gpu(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         barrier = lambda: dist.barrier()
@@ -430,27 +601,36 @@ def run_ours(args):
     def measure(name, steps, warmup, with_e2e):
         """R instances of the workload (together > 3x L2); the K steps rotate over them."""
         insts = []
-        kind, w, splits = build_workload(name, seed=1000 + rank, device=dev)
+        kind, w, mode = build_workload(name, seed=1000 + rank, device=dev)
         B, s_q, H, _ = w.q.shape
         footprint = w.kv_bytes + w.q.numel() * 2 + B * s_q * H * 512 * 2
         R = max(1, min(12, -(-3 * l2_bytes // footprint)))
+        plan_ms = None
         for r in range(R):
             if r > 0:
-                kind, w, splits = build_workload(name, seed=1000 + rank + 101 * r, device=dev)
-            fn, launches, splits_used, status = make_step(kind, w, splits)
+                kind, w, mode = build_workload(name, seed=1000 + rank + 101 * r, device=dev)
+            fn, launches, desc, status, plan = make_step(kind, w, mode)
             insts.append((w, fn, status))
-        total_ms, mode = time_rotating([f for _, f, _ in insts], steps, warmup, flush, barrier)
+        if plan is not None:
+            # what making a plan costs (one launch of the scheduler kernel), outside the step: a plan depends on
+            # the batch's lengths only, so a decode step makes it once and all its layers use it
+            plan_ms = statistics.mean(time_steps(plan.remake, 5, 3, flush, barrier))
+        total_ms, tmode = time_rotating([f for _, f, _ in insts], steps, warmup, flush, barrier)
         w0, fn0, _ = insts[0]
         iso = time_steps(fn0, max(3, min(steps, 10)), 3, flush, barrier)
-        res = {"kind": kind, "kv_bytes": w0.kv_bytes, "total_ms": total_ms, "mode": mode, "instances": R,
-               "isolated_ms": iso, "launches": launches, "splits": splits_used}
+        res = {"kind": kind, "kv_bytes": w0.kv_bytes, "total_ms": total_ms, "mode": tmode, "instances": R,
+               "isolated_ms": iso, "launches": launches, "splits": desc, "plan_us": None if plan_ms is None else plan_ms * 1e3}
         if with_e2e:
-            et, h2d, d2h = e2e_steps(kind, insts, steps, warmup, flush, barrier)
-            res.update(e2e_total_ms=et, h2d=h2d, d2h=d2h)
+            et, h2d, d2h, copies = e2e_steps(kind, insts, steps, warmup, flush, barrier)
+            res.update(e2e_total_ms=et, h2d=h2d, d2h=d2h, copies=copies)
+        # the result of the last timed call on the first instance, against the oracle (not timed)
+        o, l = fn0()
+        torch.cuda.synchronize()
+        res["parity"] = parity_sample(kind, w0, o, l)
         for _, _, status in insts:
             st = status.cpu().tolist()
             if st != [0, 0, 0, 0]:
-                raise RuntimeError(f"{name}: a kernel wait timed out: status={st}")
+                raise RuntimeError(f"{name}: the decode kernel reported status={st}")
         del insts, w, w0
         torch.cuda.empty_cache()
         return res
@@ -482,30 +662,53 @@ def run_ours(args):
     isolated_ms = reduce_max(statistics.mean(head["isolated_ms"]))
     e2e_ms = reduce_max(head["e2e_total_ms"]) / args.steps
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e12
+    # the host link per rank (slowest and fastest rank), measured with all ranks copying at once
+    link = {}
+    for key, val in head["copies"].items():
+        link[key] = {"min_over_ranks": -reduce_max(-val), "max_over_ranks": reduce_max(val)} if world > 1 else val
+    link["compute_ms_per_step"] = ms_per_step
+    link["host_binding_rank0"] = binding
     peak, peak_src = measured_peak_gbs()
     per_gpu_gbs = head["kv_bytes"] / (head["total_ms"] / args.steps * 1e-3) / 1e9
 
     others = {}
     if "mixed" in args.extras:
         (csa_w, hca_w), n_mine = build_mixed(rank, world, dev)
-        fc, lc, sc, st_c = make_step("csa", csa_w, None)
-        fh, lh, sh, st_h = make_step("hca", hca_w, None)
-
-        def both():
-            fc()
-            fh()
-        # one instance: each layer streams far more than L2 holds
         msteps = max(3, min(args.steps, 10))
-        mixed_total, mixed_mode = time_rotating([both], msteps, 3, flush, barrier)
-        mixed_ms = reduce_max(mixed_total) / msteps
+        mixed = {}
+        # the same two layers on the static grid (split count from the host rule) and on plans of the scheduler
+        for label, mode in (("static_grid", {"num_splits": None}), ("scheduled", {"plan_splits": 0})):
+            fc, lc, sc, st_c, pc = make_step("csa", csa_w, dict(mode))
+            fh, lh, sh, st_h, ph = make_step("hca", hca_w, dict(mode))
+
+            def both(fc=fc, fh=fh):
+                fc()
+                fh()
+            # one instance: each layer streams far more than L2 holds
+            tot, mixed_mode = time_rotating([both], msteps, 3, flush, barrier)
+            ms = reduce_max(tot) / msteps
+            oc, lc_ = fc()
+            oh, lh_ = fh()
+            torch.cuda.synchronize()
+            par = {"csa": parity_sample("csa", csa_w, oc, lc_), "hca": parity_sample("hca", hca_w, oh, lh_)}
+            if st_c.cpu().tolist() != [0, 0, 0, 0] or st_h.cpu().tolist() != [0, 0, 0, 0]:
+                raise RuntimeError("mixed workload: the decode kernel reported a status")
+            plan_us = None
+            if pc is not None:
+                plan_us = reduce_max(statistics.mean(time_steps(lambda: (pc.remake(), ph.remake()), 5, 3, flush, barrier))) * 1e3
+            mixed[label] = {"ms_per_step": ms, "split_mode": {"csa": sc, "hca": sh}, "timing": mixed_mode, "parity": par,
+                            "plan_us_both_layers": plan_us}
+            del fc, fh, pc, ph
         mixed_bytes = reduce_sum(csa_w.kv_bytes + hca_w.kv_bytes)
-        if st_c.cpu().tolist() != [0, 0, 0, 0] or st_h.cpu().tolist() != [0, 0, 0, 0]:
-            raise RuntimeError("mixed workload: a kernel wait timed out")
+        best = min(mixed, key=lambda k: mixed[k]["ms_per_step"])
+        mixed_ms = mixed[best]["ms_per_step"]
         others[MIXED] = {"tokens_per_s": MIXED_REQUESTS / (mixed_ms * 1e-3), "ms_per_step": mixed_ms,
                          "us_per_layer": mixed_ms * 1e3 / 2, "kv_tb_per_s": mixed_bytes / (mixed_ms * 1e-3) / 1e12,
                          "kv_bytes": mixed_bytes, "requests_per_gpu": n_mine, "layers_per_step": 2,
-                         "scaling": "strong", "num_splits": {"csa": sc, "hca": sh}, "timing": mixed_mode,
-                         "sharding": "sorted by context, dealt round-robin"}
+                         "scaling": "strong", "path": best, "paths": mixed,
+                         "scheduled_over_static": mixed["static_grid"]["ms_per_step"] / mixed["scheduled"]["ms_per_step"],
+                         "sharding": "sorted by context, dealt round-robin",
+                         "note": "plans are made once per step, outside the layers; their cost is plan_us_both_layers"}
         del csa_w, hca_w
         torch.cuda.empty_cache()
     if "head_sharded" in args.extras and world > 1 and 128 % world == 0:
@@ -649,8 +852,9 @@ def run_ours(args):
             ms = r["total_ms"] / osteps
             others[name] = {"us_per_layer": ms * 1e3, "kv_tb_per_s": r["kv_bytes"] / (ms * 1e-3) / 1e12,
                             "hbm_frac": r["kv_bytes"] / (ms * 1e-3) / 1e9 / peak, "kv_bytes": r["kv_bytes"],
-                            "num_splits": r["splits"], "isolated_us": statistics.mean(r["isolated_ms"]) * 1e3,
-                            "timing": r["mode"], "instances": r["instances"]}
+                            "split_mode": r["splits"], "plan_us": r["plan_us"], "isolated_us": statistics.mean(r["isolated_ms"]) * 1e3,
+                            "timing": r["mode"], "instances": r["instances"], "parity": r["parity"],
+                            "traffic": NCU_DRAM_TRAFFIC.get(name)}
 
     if rank != 0:
         if world > 1:
@@ -661,16 +865,19 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "isolated_us_per_layer": isolated_ms * 1e3,
         "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16 MMA over fp8-e4m3 KV, fp32 accumulate", "data": "synthetic",
+        "vs_baseline": None,
+        "dtype": "fp16 tensor-core operands (fp8-e4m3 KV dequantised with its fp32 scales, bf16 q and the probabilities converted), fp32 accumulate, bf16 out",
+        "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in kw.items()}, "requests_per_gpu": kw["B"],
-                   "num_splits": head["splits"], "entry_bytes": ENTRY_BYTES,
+                   "split_mode": head["splits"], "entry_bytes": ENTRY_BYTES,
                    "timing": f"{head['mode']} replay of the K steps" if head["mode"] == "graph" else "eager back-to-back launches",
                    "l2": f"inputs larger than L2: the steps rotate over {head['instances']} independent instances of the workload "
                          f"({head['instances']} KV pools, queries and outputs; L2 = {l2_bytes >> 20} MiB); the isolated figure flushes L2 "
                          f"with a {L2_FLUSH_BYTES >> 20} MiB write before each launch",
                    "kv_bytes_per_gpu_step": head["kv_bytes"], "parallelism": f"dp{world} over requests, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"],
-                "ms_per_step": e2e_ms, "note": "every step copies q and its length/index tensors from pinned host memory and reads out+lse back to pinned host memory; copy-in, compute and copy-out run on their own streams chained by events, K steps timed as a whole; the KV cache is device-resident state"},
+                "ms_per_step": e2e_ms, "host_link": link,
+                "note": "every step copies q and its length/index tensors from one pinned host buffer (one copy) and reads out+lse back to pinned host memory (one copy); copy-in, compute and copy-out run on their own streams chained by events, K steps timed as a whole; the KV cache is device-resident state; host_link is the same buffers copied with no compute, all ranks at once"},
         "gpu_launches": head["launches"] * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "traffic": NCU_DRAM_TRAFFIC.get(args.workload), "traffic_source": NCU_TRAFFIC_SOURCE if args.workload in NCU_DRAM_TRAFFIC else None,
@@ -678,10 +885,12 @@ def run_ours(args):
         # the same launch against the tensor-core bound: 2 x H x (576 + 512) FLOP per attended entry
         "roofline_tensor": tensor_view(head["kv_bytes"], kw["H"], head["total_ms"] / args.steps),
         "clocks": clocks,
+        "parity": {**head["parity"], "tolerance": TOL, "against": "CPU oracle, rows of the first instance after the timed region"},
         "other_workloads": others,
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(kind, args.workload)
+        line["e2e_vs_cpu_baseline"] = e2e_value / line["cpu_baseline"]["value"]
     print(json.dumps(line), file=args.out, flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -693,23 +902,26 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    claim_host_threads()
     kind, kw = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     vals, base = [], None
     for i in range(args.warmup + args.steps):
-        base = cpu_baseline(kind, args.workload, target_s=1.5)
+        base = cpu_baseline(kind, args.workload, target_s=1.5, sample_B=8)
         if i >= args.warmup:
             vals.append(base)
     v = statistics.mean(b["value"] for b in vals)
-    ms = statistics.mean(b["ms_per_sample_pass"] for b in vals)
+    ms = statistics.mean(b["ms_per_full_step"] for b in vals)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp32 (numpy)", "data": "synthetic",
+        "dtype": "fp32 (torch CPU)" if base["kind"] == "reference" else "fp32 (numpy)", "data": "synthetic",
         "config": {"workload": args.workload, **kw},
         "cpu_baseline": {**base, "value": v},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "CPU restatement (oracle port) of the reference's PyTorch decode path on a bounded sample; the reference's own CUDA decode kernel is not run: as committed it stalls on an mbarrier and then traps",
+        "note": "the reference's own PyTorch decode path on the host cores, each step a bounded sample of the workload "
+                "(ms_per_step is the sample's time scaled to the whole batch); the reference's CUDA decode kernel is not "
+                "run: as committed it stalls on an mbarrier and then traps",
     }
     print(json.dumps(line), file=args.out, flush=True)
 

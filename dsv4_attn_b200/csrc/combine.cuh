@@ -1,6 +1,6 @@
 // LSE-weighted merge of split-KV partial outputs.  One warp per (row, head):
 // the per-split log2 LSEs are reduced with warp shuffles, each lane then owns
-// 2 x 8 consecutive value columns, reads partials with 128-bit loads (four splits
+// 2 x 8 consecutive value columns, reads partials with 128-bit loads (two splits
 // in flight per lane) and writes BF16 with 128-bit stores.
 #pragma once
 
@@ -107,25 +107,25 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
             w_mine = (l == -CUDART_INF_F || denom == -CUDART_INF_F) ? 0.f : exp2f(l - denom);
         }
         const int cnt = min(32, S - s0);
-        // four splits at a time: their loads are all issued before the first is used
-        for (int k0 = 0; k0 < cnt; k0 += 4) {
-            float w[4];
+        // two splits at a time: their loads are issued before the first is used
+        for (int k0 = 0; k0 < cnt; k0 += 2) {
+            float w[2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 2; ++j) {
                 const float x = __shfl_sync(0xFFFFFFFFu, w_mine, (k0 + j) & 31);
                 w[j] = (k0 + j < cnt) ? x : 0.f;      // an empty split has weight 0: its partial may hold anything and is not read
             }
             if (a.partial_bf16) {
                 const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(a.partial_o) + po_off + int64_t(s0 + k0) * po_stride;
-                uint4 v[4][2];
+                uint4 v[2][2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         v[j][i] = (w[j] != 0.f) ? __ldg(reinterpret_cast<const uint4*>(sb + int64_t(j) * po_stride + i * 256))
                                                 : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const uint32_t u[4] = {v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w};
@@ -137,9 +137,9 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
                     }
             } else {
                 const float* src = a.partial_o + po_off + int64_t(s0 + k0) * po_stride;
-                float4 v[4][4];
+                float4 v[2][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const float4* q = reinterpret_cast<const float4*>(src + int64_t(j) * po_stride + i * 256);
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
                         v[j][2 * i + 1] = (w[j] != 0.f) ? __ldg(q + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const float4 v0 = v[j][2 * i], v1 = v[j][2 * i + 1];

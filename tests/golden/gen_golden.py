@@ -236,8 +236,11 @@ REF_CASES = {
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("DSV4_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("DSV4_REFERENCE"))
     args = ap.parse_args()
+    if not args.reference or not (Path(args.reference) / "bench" / "bench" / "reference.py").exists():
+        print("give --reference /path/to/the/reference/checkout or set DSV4_REFERENCE", file=sys.stderr)
+        return 2
     sys.dont_write_bytecode = True
     sys.path.insert(0, str(Path(args.reference) / "bench"))
     from bench import reference as ref  # the reference's own module
