@@ -580,6 +580,124 @@ def cpu_baseline(kind, name, seed=0, target_s=10.0, sample_B=4):
             "ms_per_sample_pass": dt * 1e3, "ms_per_full_step": dt * 1e3 * full_B / sample_B, "host_cpus": os.cpu_count()}
 
 
+AUX_CASES = ("csa_compress_reduce_b1_n65536_c512", "hca_compress_insert_b1_n65536_c576_m128", "kv_quantize_insert_65536rows",
+             "rope_norm_65536x16x576", "combine_fp32_partials_8x256rows", "indexer_topk_b64_n25000_k2048")
+# decode cases for profiler captures only: a quarter of the batch of the 100k-context sparse configuration
+PROFILE_CASES = {
+    "csa_b16_h128_topk2048_ctx100k": ("csa", dict(B=16, s_q=1, H=128, n_entries=25000, topk=2048, num_splits=1)),
+    "csa_b16_h128_topk2048_ctx100k_split8_static_grid": ("csa", dict(B=16, s_q=1, H=128, n_entries=25000, topk=2048, num_splits=8)),
+    "csa_b16_h128_topk2048_ctx100k_split8": ("csa", dict(B=16, s_q=1, H=128, n_entries=25000, topk=2048, plan_splits=8)),
+}
+
+
+def aux_case(name, dev):
+    """The kernels either side of the decode (cache write, pre-pass, merge, indexer) on fixed synthetic inputs.
+    Returns (fn, algorithmic bytes per call, extra fields for the report, check() to call after timing)."""
+    import torch
+    import dsv4_attn_b200 as lib
+    ok = lambda: None
+    if name == "csa_compress_reduce_b1_n65536_c512":
+        # the CSA compressor's second pass (a pure streaming kernel)
+        Bc, nc, cc = 1, 65536, 512
+        streams = [torch.randn(Bc, nc, cc, device=dev).to(torch.bfloat16) for _ in range(4)]
+        biases = [torch.randn(4, cc, device=dev).to(torch.bfloat16) for _ in range(2)]
+        cout = torch.empty(Bc, nc // 4, cc, dtype=torch.bfloat16, device=dev)
+        return (lambda: lib.csa_compress_reduce_fwd(*streams, *biases, 4, out=cout)), 4 * Bc * nc * cc * 2 + cout.numel() * 2, {}, ok
+    if name == "hca_compress_insert_b1_n65536_c576_m128":
+        # the HCA compressor fused with the FP8 quantiser and the paged-cache insert
+        nh, ch, mh = 65536, 576, 128
+        Ch = torch.randn(1, nh, ch, device=dev).to(torch.bfloat16)
+        Zh = (2 * torch.randn(1, nh, ch, device=dev)).to(torch.bfloat16)
+        bh = torch.randn(mh, ch, device=dev).to(torch.bfloat16)
+        n_new = nh // mh
+        pages = (n_new + 63) // 64
+        pool_h = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
+        bt_h = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        pos_h = torch.zeros(1, dtype=torch.int32, device=dev)
+        return (lambda: lib.hca_compress_fwd(Ch, Zh, bh, mh, kv_pool=pool_h, block_table=bt_h, insert_pos=pos_h, want_out=False)), \
+            2 * nh * ch * 2 + n_new * ENTRY_BYTES, {}, ok
+    if name == "kv_quantize_insert_65536rows":
+        Tq, ch = 65536, 576
+        rows_q = torch.randn(1, Tq, ch, device=dev).to(torch.bfloat16)
+        pages = Tq // 64
+        pool_q = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
+        bt_q = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages)
+        pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        return (lambda: lib.kv_quantize_insert(rows_q, pool_q, bt_q, pos)), Tq * (ch * 2 + ENTRY_BYTES), {}, ok
+    if name == "rope_norm_65536x16x576":
+        # RoPE + RMS norm pre-pass on a prefill-sized batch of query vectors
+        xr = torch.randn(65536, 16, 576, device=dev).to(torch.bfloat16)
+        posr = torch.randint(0, 100000, (65536,), dtype=torch.int32, device=dev)
+        wr = torch.ones(576, dtype=torch.bfloat16, device=dev)
+        outr = torch.empty_like(xr)
+        return (lambda: lib.rope_norm(xr, posr, norm_weight=wr, out=outr)), 2 * xr.numel() * 2, {}, ok
+    if name.startswith("combine_"):
+        # the split merge on its own: 8 splits of 256 rows x 128 heads x 512 values, the shape of the sparse
+        # configuration with 8 splits, on FP32 partials (the reference's convention: its merge kernel reads
+        # the same bytes; the library's own split path writes BF16 partials and is covered by the split cases)
+        S, N, H = 8, 256, 128
+        po = torch.randn(S, N, H, 512, device=dev)
+        pl = torch.randn(S, N, H, device=dev)
+        out = torch.empty(N, H, 512, dtype=torch.bfloat16, device=dev)
+        lse = torch.empty(N, H, dtype=torch.float32, device=dev)
+        return (lambda: lib.combine(po, pl, out=out, lse=lse)), po.numel() * po.element_size() + pl.numel() * 4 + out.numel() * 2 + lse.numel() * 4, {}, ok
+    if name == "indexer_topk_b64_n25000_k2048":
+        # the step before the sparse decode: FP8 scoring of every visible entry + top-k
+        Bi, ni, ki = 64, 25000, 2048
+        pages_per = (ni + 63) // 64
+        qf = torch.randint(0, 120, (Bi, 1, 64, 128), dtype=torch.uint8, device=dev)       # positive e4m3 bytes below NaN
+        qf = qf | (torch.randint(0, 2, qf.shape, dtype=torch.uint8, device=dev) << 7)      # random signs
+        qw = torch.randn(Bi, 1, 64, device=dev)
+        kp = torch.randint(0, 120, (Bi * pages_per, 8448), dtype=torch.uint8, device=dev)
+        kp[:, :8192] |= (torch.randint(0, 2, (Bi * pages_per, 8192), dtype=torch.uint8, device=dev) << 7)
+        kp[:, 8192:] = torch.rand(Bi * pages_per, 64, device=dev).add_(0.5).view(torch.uint8).view(Bi * pages_per, 256)
+        bti = torch.randperm(Bi * pages_per, device=dev).to(torch.int32).view(Bi, pages_per)
+        nv = torch.full((Bi, 1), ni, dtype=torch.int32, device=dev)
+        sc_ws = torch.empty(Bi, pages_per * 64, dtype=torch.float32, device=dev)
+        oi = torch.empty(Bi, 1, ki, dtype=torch.int32, device=dev)
+        st_i = lib.new_status(dev)
+
+        def check():
+            if st_i.cpu().tolist() != [0, 0, 0, 0]:
+                raise RuntimeError("indexer: the kernel reported a status")
+        return (lambda: lib.indexer_topk(qf, qw, kp, bti, nv, ki, scores=sc_ws, out=oi, status=st_i)), Bi * ni * 132, {"launches": 2}, check
+    raise KeyError(name)
+
+
+def run_single(args):
+    """One instance of one case, W + K eager calls with L2 flushed before each: the small run that profiler
+    captures are taken on.  Prints one short JSON line (not the benchmark's line)."""
+    import torch
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    name = args.single
+    parity = None
+    if name in AUX_CASES:
+        fn, nbytes, _, check = aux_case(name, dev)
+    else:
+        kind, kw = {**WORKLOADS, **PROFILE_CASES}[name]
+        from dsv4_attn_b200 import synth
+        kw = dict(kw)
+        mode = {"num_splits": kw.pop("num_splits", None), "plan_splits": kw.pop("plan_splits", None)}
+        w = (synth.make_hca if kind == "hca" else synth.make_csa)(1000, device=dev, **kw)
+        fn, _, _, status, _ = make_step(kind, w, mode)
+        nbytes = w.kv_bytes
+
+        def check():
+            if status.cpu().tolist() != [0, 0, 0, 0]:
+                raise RuntimeError(f"{name}: the decode kernel reported status={status.cpu().tolist()}")
+    t = time_steps(fn, args.steps, args.warmup, flush, lambda: None)
+    check()
+    if name not in AUX_CASES:
+        o, l = fn()
+        torch.cuda.synchronize()
+        parity = parity_sample(kind, w, o, l, count=8)
+    ms = statistics.mean(t)
+    print(json.dumps({"single": name, "us": ms * 1e3, "bytes": nbytes, "gb_per_s": nbytes / (ms * 1e-3) / 1e9, "parity": parity}),
+          file=args.out, flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -735,88 +853,22 @@ def run_ours(args):
                 "scaling": "strong", "timing": "isolated (L2 flushed, eager)"}
         del wh
         torch.cuda.empty_cache()
-    if "cache_write" in args.extras and world == 1:
-        # the cache-write side: CSA compressor second pass (a pure streaming kernel)
-        import dsv4_attn_b200 as lib
-        Bc, nc, cc = 1, 65536, 512
-        streams = [torch.randn(Bc, nc, cc, device=dev).to(torch.bfloat16) for _ in range(4)]
-        biases = [torch.randn(4, cc, device=dev).to(torch.bfloat16) for _ in range(2)]
-        cout = torch.empty(Bc, nc // 4, cc, dtype=torch.bfloat16, device=dev)
-        ct = time_steps(lambda: lib.csa_compress_reduce_fwd(*streams, *biases, 4, out=cout), max(3, min(args.steps, 10)), 3,
-                        flush, barrier)
-        cbytes = 4 * Bc * nc * cc * 2 + cout.numel() * 2
-        cms = statistics.mean(ct)
-        others["csa_compress_reduce_b1_n65536_c512"] = {"us": cms * 1e3, "gb_per_s": cbytes / (cms * 1e-3) / 1e9,
-                                                        "hbm_frac": cbytes / (cms * 1e-3) / 1e9 / peak, "bytes": cbytes}
-        del streams, cout
-        # the HCA compressor fused with the FP8 quantiser and the paged-cache insert, and the
-        # stand-alone quantise-and-insert step
-        nh, ch, mh = 65536, 576, 128
-        Ch = torch.randn(1, nh, ch, device=dev).to(torch.bfloat16)
-        Zh = (2 * torch.randn(1, nh, ch, device=dev)).to(torch.bfloat16)
-        bh = torch.randn(mh, ch, device=dev).to(torch.bfloat16)
-        n_new = nh // mh
-        pages = (n_new + 63) // 64
-        pool_h = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
-        bt_h = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
-        pos_h = torch.zeros(1, dtype=torch.int32, device=dev)
-        ht = time_steps(lambda: lib.hca_compress_fwd(Ch, Zh, bh, mh, kv_pool=pool_h, block_table=bt_h, insert_pos=pos_h,
-                                                     want_out=False), max(3, min(args.steps, 10)), 3, flush, barrier)
-        hbytes = 2 * nh * ch * 2 + n_new * ENTRY_BYTES
-        hms = statistics.mean(ht)
-        others["hca_compress_insert_b1_n65536_c576_m128"] = {"us": hms * 1e3, "gb_per_s": hbytes / (hms * 1e-3) / 1e9,
-                                                            "hbm_frac": hbytes / (hms * 1e-3) / 1e9 / peak, "bytes": hbytes}
-        del Ch, Zh
-        Tq = 65536
-        rows_q = torch.randn(1, Tq, ch, device=dev).to(torch.bfloat16)
-        pages = Tq // 64
-        pool_q = torch.zeros(pages, 64, ENTRY_BYTES, dtype=torch.uint8, device=dev)
-        bt_q = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages)
-        qt = time_steps(lambda: lib.kv_quantize_insert(rows_q, pool_q, bt_q, pos_h), max(3, min(args.steps, 10)), 3, flush, barrier)
-        qbytes = Tq * (ch * 2 + ENTRY_BYTES)
-        qms = statistics.mean(qt)
-        others["kv_quantize_insert_65536rows"] = {"us": qms * 1e3, "gb_per_s": qbytes / (qms * 1e-3) / 1e9,
-                                                  "hbm_frac": qbytes / (qms * 1e-3) / 1e9 / peak, "bytes": qbytes}
-        # RoPE + RMS norm pre-pass on a prefill-sized batch of query vectors (65536 tokens x 16 heads x 576)
-        xr = torch.randn(65536, 16, ch, device=dev).to(torch.bfloat16)
-        posr = torch.randint(0, 100000, (65536,), dtype=torch.int32, device=dev)
-        wr = torch.ones(ch, dtype=torch.bfloat16, device=dev)
-        outr = torch.empty_like(xr)
-        rt = time_steps(lambda: lib.rope_norm(xr, posr, norm_weight=wr, out=outr), max(3, min(args.steps, 10)), 3, flush, barrier)
-        rbytes = 2 * xr.numel() * 2
-        rms_ = statistics.mean(rt)
-        others["rope_norm_65536x16x576"] = {"us": rms_ * 1e3, "gb_per_s": rbytes / (rms_ * 1e-3) / 1e9,
-                                            "hbm_frac": rbytes / (rms_ * 1e-3) / 1e9 / peak, "bytes": rbytes}
-        del xr, outr
-        del rows_q, pool_q, pool_h
-        torch.cuda.empty_cache()
-    if "indexer" in args.extras and world == 1:
-        # the step before the sparse decode: FP8 scoring of every visible entry + top-k
-        import dsv4_attn_b200 as lib
-        Bi, ni, ki = 64, 25000, 2048
-        pages_per = (ni + 63) // 64
-        qf = torch.randint(0, 120, (Bi, 1, 64, 128), dtype=torch.uint8, device=dev)       # positive e4m3 bytes below NaN
-        qf = qf | (torch.randint(0, 2, qf.shape, dtype=torch.uint8, device=dev) << 7)      # random signs
-        qw = torch.randn(Bi, 1, 64, device=dev)
-        kp = torch.randint(0, 120, (Bi * pages_per, 8448), dtype=torch.uint8, device=dev)
-        kp[:, :8192] |= (torch.randint(0, 2, (Bi * pages_per, 8192), dtype=torch.uint8, device=dev) << 7)
-        kp[:, 8192:] = torch.rand(Bi * pages_per, 64, device=dev).add_(0.5).view(torch.uint8).view(Bi * pages_per, 256)
-        bti = torch.randperm(Bi * pages_per, device=dev).to(torch.int32).view(Bi, pages_per)
-        nv = torch.full((Bi, 1), ni, dtype=torch.int32, device=dev)
-        sc_ws = torch.empty(Bi, pages_per * 64, dtype=torch.float32, device=dev)
-        oi = torch.empty(Bi, 1, ki, dtype=torch.int32, device=dev)
-        st_i = lib.new_status(dev)
-        it = time_steps(lambda: lib.indexer_topk(qf, qw, kp, bti, nv, ki, scores=sc_ws, out=oi, status=st_i),
-                        max(3, min(args.steps, 10)), 3, flush, barrier)
-        if st_i.cpu().tolist() != [0, 0, 0, 0]:
-            raise RuntimeError("indexer: a kernel wait timed out")
-        ibytes = Bi * ni * 132
-        ims = statistics.mean(it)
-        others["indexer_topk_b64_n25000_k2048"] = {"us": ims * 1e3, "key_gb_per_s": ibytes / (ims * 1e-3) / 1e9,
-                                                   "hbm_frac": ibytes / (ims * 1e-3) / 1e9 / peak, "key_bytes": ibytes,
-                                                   "launches": 2}
-        del qf, kp, sc_ws
-        torch.cuda.empty_cache()
+    if world == 1:
+        groups = {"cache_write": ("csa_compress_reduce_b1_n65536_c512", "hca_compress_insert_b1_n65536_c576_m128",
+                                  "kv_quantize_insert_65536rows", "rope_norm_65536x16x576", "combine_fp32_partials_8x256rows"),
+                  "indexer": ("indexer_topk_b64_n25000_k2048",)}
+        for group, names in groups.items():
+            if group not in args.extras:
+                continue
+            for name in names:
+                fn, nbytes, extra, check = aux_case(name, dev)
+                t = statistics.mean(time_steps(fn, max(3, min(args.steps, 10)), 3, flush, barrier))
+                check()
+                key = "key_" if name.startswith("indexer") else ""
+                others[name] = {"us": t * 1e3, key + "gb_per_s": nbytes / (t * 1e-3) / 1e9, "hbm_frac": nbytes / (t * 1e-3) / 1e9 / peak,
+                                key + "bytes": nbytes, **extra}
+                del fn, check
+                torch.cuda.empty_cache()
     if "decode" in args.extras and world == 1:
         # the reference's own entry point and cache layout (448 e4m3 + 7 UE8M0 + 64 bf16 per token), at the
         # shape the reference harness runs it: B=64, 128 heads, 768 compressed + 128 window tokens
@@ -944,13 +996,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads")
+    ap.add_argument("--single", default=None, choices=list(WORKLOADS) + list(PROFILE_CASES) + list(AUX_CASES),
+                    help="run one instance of one case a few times and exit (for profiler captures); prints a short line of its own")
     ap.add_argument("--extras", default="mixed,head_sharded,cache_write,indexer,decode",
                     help="which groups of other workloads to run: mixed, head_sharded (N > 1), cache_write, indexer, decode (comma-separated)")
     args = ap.parse_args()
     args.extras = set() if args.no_extras else {x for x in args.extras.split(",") if x}
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     args.out = _claim_stdout()
-    if args.impl == "reference":
+    if args.single:
+        run_single(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

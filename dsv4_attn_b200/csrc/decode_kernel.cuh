@@ -225,8 +225,11 @@ __device__ __forceinline__ void report_status(int32_t* status, int code, int rol
 // (role 0 softmax, 1 Q.K^T issue, 2 loader warp 0, 3 P.V issue).  Compiled out of the product.
 #ifdef DSV4_TRACE
 __device__ __forceinline__ void trace_mark(const DecodeArgs& a, int role, int slot) {
-    if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 1024)
-        a.trace[role * 1024 + slot] = ptx::globaltimer_ns();
+    if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 1024) {
+        const long long c = clock64();                      // SM cycles: cheap to read, and one block = one SM
+        a.trace[role * 1024 + slot] = c;
+        a.trace[(4 + role) * 1024 + slot] = c;              // the trace buffer holds 12 x 1024 words
+    }
 }
 #else
 __device__ __forceinline__ void trace_mark(const DecodeArgs&, int, int) {}
@@ -254,7 +257,8 @@ __device__ __forceinline__ void dequant4(uint32_t w, __nv_bfloat162 scale2, uint
 
 // Four FP8 e4m3 (one 32-bit word) times the block scale -> 4 FP16 (two packed words).
 __device__ __forceinline__ void dequant4_f16(uint32_t w, __half2 scale2, uint32_t& lo, uint32_t& hi) {
-    const uint32_t a = ptx::e4m3x2_to_f16x2(w & 0xFFFFu), b = ptx::e4m3x2_to_f16x2(w >> 16);
+    uint32_t a, b;
+    ptx::e4m3x4_to_f16x4(w, a, b);
     const __half2 x = __hmul2(*reinterpret_cast<const __half2*>(&a), scale2);
     const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&b), scale2);
     lo = *reinterpret_cast<const uint32_t*>(&x);
@@ -262,18 +266,24 @@ __device__ __forceinline__ void dequant4_f16(uint32_t w, __half2 scale2, uint32_
 }
 
 // Registers one loader thread holds for one tile.  A loader warp owns 8
-// consecutive entries of the tile, as two groups of 4: lane/8 picks the entry of
-// a group and lane%8 one 16-byte piece of a 128-byte span (two 64-element latent
-// chunks, or the RoPE tail).  One load instruction then covers 4 entries x 128
-// contiguous bytes: measured on this part, an SM pulls records about 1.6 times
-// faster in this shape than with 64 bytes per entry per instruction, and the
-// record fetch is what the loader warps spend most of their time on.
+// consecutive entries of the tile, as two groups of 4.  lane%8 picks one 16-byte piece of a 128-byte span
+// (two 64-element latent chunks, or the RoPE tail); lane/8, with its lowest bit flipped in the lanes of
+// the span's second chunk (loader_entry), picks the entry of a group.  One load instruction then covers
+// 4 entries x 128 contiguous bytes: measured on this part, an SM pulls records about 1.6 times
+// faster in this shape than with 64 bytes per entry per instruction.  The flip is for the stores: the 8
+// lanes of a quarter-warp then write two neighbouring rows of the tile, whose swizzles differ in the lowest
+// bit, and every store instruction covers all eight 16-byte bank groups without any lane-dependent choice
+// of what to store.
+__device__ __forceinline__ int loader_entry(int lane, int g) { return 4 * g + ((lane >> 3) ^ ((lane >> 2) & 1)); }
+
 template <int SRC>
 struct LoaderRegs {
-    uint4 lat[2][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry 4 group + lane/8
+    uint4 lat[2][4];         // [group][span j]: bytes [128 j + 16 (lane%8), +16) of the latent of entry loader_entry(lane, group)
     uint4 rope[2];           // [group]: RoPE 16-byte column lane%8 of that entry
     uint32_t sc[2][4];       // [group]: packed layout: the 4 FP32 scales; reference layout: the 7 UE8M0 bytes (2 words)
     uint32_t vmask;          // bit i = entry i of this warp takes part (same in all lanes)
+    // An entry that does not take part holds zeros here (latent, RoPE and scales), so that the stores
+    // need no validity test: a zero row stays finite under the MMA whatever its probability column holds.
 };
 
 // Where an entry lives, as a 32-bit record number with bit 31 = "takes part" and bit 30 = "second pool"
@@ -389,8 +399,13 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, const uint32_t
     const int piece = lane & 7;
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
-        const int i = 4 * g + (lane >> 3);
-        if (!((vmask >> i) & 1u)) continue;
+        const int i = loader_entry(lane, g);
+        if (!((vmask >> i) & 1u)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { r.lat[g][j] = make_uint4(0, 0, 0, 0);  r.sc[g][j] = 0u; }
+            r.rope[g] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
         const uint32_t num = id[g] & kIdNumber;
         const bool second = (id[g] & kIdSecond) != 0u;
         if constexpr (!is_ref_layout(SRC)) {
@@ -448,73 +463,81 @@ __device__ __forceinline__ void prefetch_record_l2(const DecodeArgs& a, uint32_t
     }
 }
 
-// Dequantise and write span j (latent chunks 2j and 2j+1) of this warp's 8 entries
-// (tile rows t0 .. t0+7, t0 a multiple of 8) into the KV stage at kv_st.  Row t of a
-// chunk is 128 bytes; 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
-// One store instruction writes 4 rows x 2 chunks x 4 column positions, arranged
-// (see the end of the function) so that it needs as few shared-memory wavefronts
-// as 512 bytes can: four.
-template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store_span(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r, int j) {
+// Where this lane's stores of one tile go: for each of its two entries the shared-memory address of the first
+// of the two 16-byte columns its 16 latent bytes of span 0 expand to (the second column is that address ^ 16;
+// span j lies 2 j chunks further on), and the address of its RoPE column.  Row t of a chunk is 128 bytes;
+// 16-byte column c16 of row t lives at ((c16 ^ (t & 7)) << 4).
+struct LoaderAddr {
+    uint32_t lat[2];
+};
+template <int NCHUNK>
+__device__ __forceinline__ LoaderAddr loader_addresses(uint32_t kv_st, int t0, int lane) {
+    LoaderAddr r;
     const uint32_t piece = uint32_t(lane & 7);
-    const uint32_t c = 2u * uint32_t(j) + (piece >> 2);        // this lane's chunk
+    const uint32_t flip = piece >> 2;                          // this lane's chunk within a span
     const uint32_t p = piece & 3u;                             // 16 latent bytes -> 16-byte columns 2p, 2p+1
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
-        const int i = 4 * g + (lane >> 3);
-        const int t = t0 + i;
-        const bool valid = (r.vmask >> i) & 1u;
-        const uint32_t base = kv_st + c * kKvChunkBytes + uint32_t(t) * 128u;
-        const uint32_t sw = uint32_t(t & 7);
-        if (is_ref_layout(SRC) && c >= uint32_t(NCHUNK - 1)) continue;   // reference layout: span 3 ends with chunk 6
-        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-        if (valid) {
-            const uint4 x = r.lat[g][j];
-            if constexpr (use_f16(SRC)) {
-                // scales above 146 would take 448 x scale past FP16's largest finite value: such blocks saturate
-                const __half2 scale2 = __float2half2_rn(fminf(__uint_as_float(r.sc[g][j]), 146.f));
-                dequant4_f16(x.x, scale2, w0.x, w0.y);
-                dequant4_f16(x.y, scale2, w0.z, w0.w);
-                dequant4_f16(x.z, scale2, w1.x, w1.y);
-                dequant4_f16(x.w, scale2, w1.z, w1.w);
-            } else {
-                // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
-                // scale, as in the reference's dequantiser
-                const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
-                const float s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
-                const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
-                dequant4(x.x, scale2, w0.x, w0.y);
-                dequant4(x.y, scale2, w0.z, w0.w);
-                dequant4(x.z, scale2, w1.x, w1.y);
-                dequant4(x.w, scale2, w1.z, w1.w);
-            }
+        const uint32_t t = uint32_t(t0 + loader_entry(lane, g));
+        const uint32_t row = kv_st + t * 128u;
+        r.lat[g] = row + flip * kKvChunkBytes + (((2u * p) ^ (t & 7u)) << 4);
+    }
+    return r;
+}
+
+// Dequantise and write span j (latent chunks 2j and 2j+1) of this warp's 8 entries.  A 16-byte store is
+// served per quarter-warp: its 8 lanes write the even columns of one row of chunk 2j and - one row further,
+// where the swizzle turns them into the odd bank groups - the even columns of chunk 2j+1 (the chunks are
+// 8 KB apart: same banks), then the odd ones: all eight 16-byte bank groups once per instruction, four
+// shared-memory wavefronts per 512 bytes.
+template <int NCHUNK, int SRC>
+__device__ __forceinline__ void loader_store_span(const LoaderAddr& ad, int lane, const LoaderRegs<SRC>& r, int j) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const uint4 x = r.lat[g][j];
+        uint4 w0, w1;
+        if constexpr (use_f16(SRC)) {
+            // scales above 146 would take 448 x scale past FP16's largest finite value: such blocks saturate
+            const __half2 scale2 = __float2half2_rn(fminf(__uint_as_float(r.sc[g][j]), 146.f));
+            dequant4_f16(x.x, scale2, w0.x, w0.y);
+            dequant4_f16(x.y, scale2, w0.z, w0.w);
+            dequant4_f16(x.z, scale2, w1.x, w1.y);
+            dequant4_f16(x.w, scale2, w1.z, w1.w);
+        } else {
+            const uint32_t c = 2u * uint32_t(j) + (uint32_t(lane >> 2) & 1u);      // this lane's chunk
+            if (c >= uint32_t(NCHUNK - 1)) continue;               // reference layout: span 3 ends with chunk 6
+            // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
+            // scale, as in the reference's dequantiser
+            const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
+            const float s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
+            const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
+            dequant4(x.x, scale2, w0.x, w0.y);
+            dequant4(x.y, scale2, w0.z, w0.w);
+            dequant4(x.z, scale2, w1.x, w1.y);
+            dequant4(x.w, scale2, w1.z, w1.w);
         }
-        // A 16-byte store is served per quarter-warp: 8 lanes = one row, both chunks.  The two
-        // chunks are 8 KB apart (same banks), so the lanes of the second chunk write their
-        // odd column first and the even one second: every quarter-warp then covers all eight
-        // 16-byte bank groups once per instruction.
-        const uint32_t flip = piece >> 2;
-        ptx::sts_v4(base + (((2u * p + flip) ^ sw) << 4), flip ? w1 : w0);
-        ptx::sts_v4(base + (((2u * p + (flip ^ 1u)) ^ sw) << 4), flip ? w0 : w1);
+        const uint32_t at = ad.lat[g] + uint32_t(j) * 2u * kKvChunkBytes;
+        ptx::sts_v4(at, w0);
+        ptx::sts_v4(at ^ 16u, w1);
     }
 }
 
 // The RoPE tail (chunk NCHUNK-1, a plain copy): 4 rows x 8 columns per store instruction.
 template <int NCHUNK, int SRC>
-__device__ __forceinline__ void loader_store_rope(uint32_t kv_st, int t0, int lane, const LoaderRegs<SRC>& r) {
-    const uint32_t piece = uint32_t(lane & 7);
+__device__ __forceinline__ void loader_store_rope(const LoaderAddr& ad, int lane, const LoaderRegs<SRC>& r) {
+    // the RoPE column of this lane from the address of its first latent column: same row, chunk NCHUNK-1,
+    // column lane%8 instead of 2 (lane%4)   (both swizzled by the same row bits: the XOR of the two columns)
+    const uint32_t piece = uint32_t(lane & 7), flip = piece >> 2;
+    const uint32_t delta = (uint32_t(NCHUNK - 1) - flip) * kKvChunkBytes;
+    const uint32_t colx = (piece ^ (2u * (piece & 3u))) << 4;
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
-        const int i = 4 * g + (lane >> 3);
-        const int t = t0 + i;
-        const bool valid = (r.vmask >> i) & 1u;
-        const uint32_t base = kv_st + uint32_t(NCHUNK - 1) * kKvChunkBytes + uint32_t(t) * 128u;
-        uint4 w = valid ? r.rope[g] : make_uint4(0, 0, 0, 0);
+        uint4 w = r.rope[g];
         if constexpr (use_f16(SRC)) {
             w.x = ptx::bf16x2_to_f16x2(w.x);  w.y = ptx::bf16x2_to_f16x2(w.y);
             w.z = ptx::bf16x2_to_f16x2(w.z);  w.w = ptx::bf16x2_to_f16x2(w.w);
         }
-        ptx::sts_v4(base + ((piece ^ uint32_t(t & 7)) << 4), w);
+        ptx::sts_v4((ad.lat[g] ^ colx) + delta, w);
     }
 }
 
@@ -727,8 +750,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
             // probe fails, wait and read again.
             bool ready = ptx::mbar_test_wait(bar_res_full + 8 * slot, (t / kRing) & 1u);
             ti.meta = ts.meta;
-            ti.id[0] = ts.id[row0 + (lane >> 3)];
-            ti.id[1] = ts.id[row0 + 4 + (lane >> 3)];
+            ti.id[0] = ts.id[row0 + loader_entry(lane, 0)];
+            ti.id[1] = ts.id[row0 + loader_entry(lane, 1)];
             uint64_t mask = ts.mask;
             if (!__all_sync(0xFFFFFFFFu, ready)) {
                 ready = ptx::mbar_wait(bar_res_full + 8 * slot, (t / kRing) & 1u, wait_ns);
@@ -739,8 +762,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                     return ti;
                 }
                 ti.meta = *reinterpret_cast<const volatile uint32_t*>(&ts.meta);
-                ti.id[0] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + (lane >> 3)]);
-                ti.id[1] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + 4 + (lane >> 3)]);
+                ti.id[0] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + loader_entry(lane, 0)]);
+                ti.id[1] = *reinterpret_cast<const volatile uint32_t*>(&ts.id[row0 + loader_entry(lane, 1)]);
                 mask = *reinterpret_cast<const volatile uint64_t*>(&ts.mask);
             }
             if (!(ti.meta & kMetaTile)) return ti;       // end of the stream (nothing to release: the resolver has stopped)
@@ -843,12 +866,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) decode_mma_kernel(const __grid
                 __syncwarp();
                 if (lane == 0 && !drop) ptx::mbar_arrive(bar_kv_full + kKvFullStride * st + 8 * grp);
             };
-            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 0);
-            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 1);
+            const LoaderAddr ad = loader_addresses<NCHUNK>(kv_st, row0, lane);
+            loader_store_span<NCHUNK, SRC>(ad, lane, regs, 0);
+            loader_store_span<NCHUNK, SRC>(ad, lane, regs, 1);
             group_done(0);
-            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 2);
-            loader_store_span<NCHUNK, SRC>(kv_st, row0, lane, regs, 3);
-            loader_store_rope<NCHUNK, SRC>(kv_st, row0, lane, regs);
+            loader_store_span<NCHUNK, SRC>(ad, lane, regs, 2);
+            loader_store_span<NCHUNK, SRC>(ad, lane, regs, 3);
+            loader_store_rope<NCHUNK, SRC>(ad, lane, regs);
             group_done(1);
             if (lw == 0 && lane == 0) trace_mark(a, 2, 4 * int(g) + 2);
             if (mt & kMetaLast) {

@@ -406,5 +406,11 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
     return r;
 }
 
+// four FP8 e4m3 in one word -> four FP16 (exact), element order kept: lo = elements 0, 1; hi = elements 2, 3
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+        : "=r"(lo), "=r"(hi) : "r"(w));
+}
+
 }  // namespace ptx
 }  // namespace dsv4
