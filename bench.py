@@ -738,6 +738,10 @@ def run_ours(args):
         iso = time_steps(fn0, max(3, min(steps, 10)), 3, flush, barrier)
         res = {"kind": kind, "kv_bytes": w0.kv_bytes, "total_ms": total_ms, "mode": tmode, "instances": R,
                "isolated_ms": iso, "launches": launches, "splits": desc, "plan_us": None if plan_ms is None else plan_ms * 1e3}
+        if plan is not None:
+            # what the scheduler made of the request: pieces of a row that fell to the same pair of SMs run as one item
+            items, slots, over, _ = plan.info()
+            res["plan"] = {"rows_x_head_groups": B * s_q * ((H + 127) // 128), "items": items, "partial_slots": slots}
         if with_e2e:
             et, h2d, d2h, copies = e2e_steps(kind, insts, steps, warmup, flush, barrier)
             res.update(e2e_total_ms=et, h2d=h2d, d2h=d2h, copies=copies)
@@ -904,7 +908,7 @@ def run_ours(args):
             ms = r["total_ms"] / osteps
             others[name] = {"us_per_layer": ms * 1e3, "kv_tb_per_s": r["kv_bytes"] / (ms * 1e-3) / 1e12,
                             "hbm_frac": r["kv_bytes"] / (ms * 1e-3) / 1e9 / peak, "kv_bytes": r["kv_bytes"],
-                            "split_mode": r["splits"], "plan_us": r["plan_us"], "isolated_us": statistics.mean(r["isolated_ms"]) * 1e3,
+                            "split_mode": r["splits"], "plan_us": r["plan_us"], "plan": r.get("plan"), "isolated_us": statistics.mean(r["isolated_ms"]) * 1e3,
                             "timing": r["mode"], "instances": r["instances"], "parity": r["parity"],
                             "traffic": NCU_DRAM_TRAFFIC.get(name)}
 

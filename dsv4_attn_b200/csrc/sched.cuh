@@ -8,7 +8,8 @@
 // of its own with a partial-output slot, and the merge kernel adds the pieces up; a unit inside one
 // part is a single item that writes the final output directly.  With `fixed_splits` >= 1 every unit is
 // instead cut into that many equal pieces (the split count a caller asks for) and the pieces are dealt
-// to the pairs in order.  The plan depends on the lengths only: one plan serves every layer of a step.
+// to the pairs in order; consecutive pieces of a unit that fall to the same pair run there as one item.
+// The plan depends on the lengths only: one plan serves every layer of a step.
 //
 // Replaces the static "tile index = split index" bookkeeping of the reference
 // (hca/sm100/helpers.h:831-869, hca/sm100/kernel.cu:99-102,248-257).
@@ -105,10 +106,15 @@ struct PieceWalk {
         }
         if (fixed > 1) {
             if (t >= tiles) { done = true;  return false; }
-            nt = tps < tiles - t ? tps : tiles - t;
-            pair = pair_of(at);  t0 = t;
-            at += plan_piece_cost(nt);
-            t += nt;
+            // consecutive pieces of the unit that fall to the same pair run as one item: their partial results
+            // would only be added up again
+            pair = pair_of(at);  t0 = t;  nt = 0;
+            do {
+                const int n = tps < tiles - t ? tps : tiles - t;
+                nt += n;
+                at += plan_piece_cost(n);
+                t += n;
+            } while (t < tiles && pair_of(at) == pair);
             return true;
         }
         const int p0 = pair_of(C);

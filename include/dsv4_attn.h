@@ -222,8 +222,10 @@ int64_t dsv4_attn_workspace_bytes(int rows, int H, int num_splits, int64_t* lse_
  * of the list, keep tensor memory and barriers alive between items and fetch the next item's
  * queries and first tiles while the current one finishes.  A plan depends only on B, s_q, H and
  * the length arrays, so one plan serves every layer of a decode step that shares them.
- * num_splits = 0 lets the planner balance; num_splits >= 1 cuts every unit into exactly that many
- * equal pieces (what a caller that fixes the split count asks for) and deals the pieces out.
+ * num_splits = 0 lets the planner balance; num_splits >= 1 cuts every unit into that many equal
+ * pieces (what a caller that fixes the split count asks for) and deals the pieces out in order;
+ * consecutive pieces of a unit that fall to the same pair of SMs run there as one item (their
+ * partial results would only be added up again), so a unit ends up with at most num_splits items.
  * Replaces the reference's static one-tile-per-split rule (hca/sm100/helpers.h:831-869,
  * hca/sm100/kernel.cu:99-102,248-257).
  *
@@ -238,7 +240,7 @@ typedef struct Dsv4PlanParams {
     int32_t s_q;
     int32_t H;
     int32_t topk;               /* CSA: length of each index list */
-    int32_t num_splits;         /* 0 = balance over the SMs, >= 1 = that many pieces per unit */
+    int32_t num_splits;         /* 0 = balance over the SMs, >= 1 = that many pieces per unit (see above) */
     int32_t num_sms;            /* 0 = all SMs of the current device (fewer may be given, never more) */
     int32_t reserved0;
     const int32_t* topk_len;    /* CSA, optional int32 [B, s_q] */

@@ -50,7 +50,8 @@ def test_planner_kernel_covers_every_row_once(lib):
     torch.cuda.synchronize()
     v8 = device_plan_view(plan8, sms)
     check_cover(v8, [2048] * 10)
-    assert (v8["nsplits"] == 8).all()
+    # 80 pieces on 74 pairs: where two consecutive pieces of a unit fall to one pair they run as one item
+    assert (v8["nsplits"] <= 8).all() and (v8["nsplits"] >= 6).all()
 
 
 def run(lib, kind, case, plan):

@@ -112,9 +112,21 @@ def test_few_long_rows_are_cut_over_all_pairs():
 
 def test_fixed_split_count_is_honoured():
     tk = np.array([[2048, 2047], [100, 0], [64, 65]])
+    # few units on many pairs: every piece falls to a pair of its own
     pl = plan(0, 3, 2, 128, topk=2048, topk_len=tk, splits=8)
     check_cover(pl, tk.reshape(-1).tolist())
     assert pl["nsplits"].tolist() == [8, 8, 2, 1, 1, 2]
+
+
+def test_fixed_pieces_on_one_pair_run_as_one_item():
+    # many units on few pairs: consecutive pieces of a unit on the same pair are one item, so a unit has at most
+    # as many items as pairs it touches, never more than the split count, and the tiles are still covered once
+    B = 64
+    pl = plan(0, B, 1, 128, topk=2048, splits=8, sms=16)
+    check_cover(pl, [2048] * B)
+    ns = pl["nsplits"]
+    assert ns.max() <= 2 and ns.min() == 1          # 8 units per pair: a unit is whole or cut once at a pair boundary
+    assert len(pl["items"]) <= B + pl["pairs"]      # items: units plus at most one cut per pair
 
 
 def test_two_head_groups_and_empty_rows():
