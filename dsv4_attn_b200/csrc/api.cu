@@ -797,6 +797,8 @@ extern "C" int dsv4_indexer_topk_fwd(const Dsv4IndexerTopkParams* p, void* strea
     a.B = p->B;  a.s_q = p->s_q;  a.max_pages = p->max_pages;  a.num_pages = p->num_pages;
     a.q_weight = p->q_weight;  a.block_table = p->block_table;  a.n_vis = p->n_vis;
     a.scores = p->scores;  a.score_stride = p->score_stride;  a.status = p->status;
+    a.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+    a.dbg_drop_tile = g_drop_tile.load(std::memory_order_relaxed);
     static std::atomic<bool> done[kMaxDevices];
     e = ensure_smem(indexer_logits_kernel, kIdxSmemBytes, done);
     if (e != cudaSuccess) return int(e);

@@ -53,6 +53,8 @@ struct IndexerArgs {
     float* scores;                       // [B*s_q, score_stride]
     int64_t score_stride;
     int32_t* status;
+    unsigned long long wait_ns;          // limit of every barrier wait
+    int dbg_drop_tile;                   // >= 0: the "accumulator full" signal of that tile of every block is left out (tests the limit)
 };
 
 struct IdxSmem {
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
             const int pages_vis = (vis_max + kIdxPageKeys - 1) / kIdxPageKeys;
             for (int i = 0; i < ntiles && ok; ++i) {
                 const int st = i % kIdxStages;
-                if (i >= kIdxStages && !ptx::mbar_wait(bar_empty + 8 * st, uint32_t(i / kIdxStages - 1) & 1u, kDefaultWaitNs)) {
+                if (i >= kIdxStages && !ptx::mbar_wait(bar_empty + 8 * st, uint32_t(i / kIdxStages - 1) & 1u, a.wait_ns)) {
                     report_status(a.status, kStatusWaitIndexer, 0, tile0 + i);
                     ok = false;
                     break;
@@ -167,11 +169,11 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
         // ───────────── MMA issue: S^T[128 keys x N] = K[128 x 128] . Q[N x 128]^T, four K steps of 32 ─────────────
         if (lane == 0) {
             const uint32_t idesc = make_idesc_e4m3(kIdxTileKeys, N);
-            if (!ptx::mbar_wait(bar_q, 0u, kDefaultWaitNs)) { report_status(a.status, kStatusWaitIndexer, 1, -1);  ok = false; }
+            if (!ptx::mbar_wait(bar_q, 0u, a.wait_ns)) { report_status(a.status, kStatusWaitIndexer, 1, -1);  ok = false; }
             for (int i = 0; i < ntiles && ok; ++i) {
                 const int st = i % kIdxStages, d = i & 1;
-                if (!ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kDefaultWaitNs) ||
-                    (i >= 2 && !ptx::mbar_wait(bar_acc_empty + 8 * d, uint32_t(i / 2 - 1) & 1u, kDefaultWaitNs))) {
+                if (!ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, a.wait_ns) ||
+                    (i >= 2 && !ptx::mbar_wait(bar_acc_empty + 8 * d, uint32_t(i / 2 - 1) & 1u, a.wait_ns))) {
                     report_status(a.status, kStatusWaitIndexer, 1, tile0 + i);
                     ok = false;
                     break;
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
                     mma_f8_ss(tmem + d * 128, ad, bd, idesc, k ? 1u : 0u);
                 }
                 ptx::mma_commit(bar_empty + 8 * st);
-                ptx::mma_commit(bar_acc_full + 8 * d);
+                if (a.dbg_drop_tile < 0 || i != a.dbg_drop_tile) ptx::mma_commit(bar_acc_full + 8 * d);
             }
         }
     } else {
@@ -197,8 +199,8 @@ __global__ void __launch_bounds__(kIdxThreads, 2) indexer_logits_kernel(const __
         vis[1] = (a.s_q > 1) ? min(__ldg(a.n_vis + b * a.s_q + 1), a.max_pages * kIdxPageKeys) : 0;
         for (int i = 0; i < ntiles && ok; ++i) {
             const int st = i % kIdxStages, d = i & 1;
-            const bool w = ptx::mbar_wait(bar_acc_full + 8 * d, uint32_t(i / 2) & 1u, kDefaultWaitNs) &&
-                           ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, kDefaultWaitNs);
+            const bool w = ptx::mbar_wait(bar_acc_full + 8 * d, uint32_t(i / 2) & 1u, a.wait_ns) &&
+                           ptx::mbar_wait(bar_full + 8 * st, uint32_t(i / kIdxStages) & 1u, a.wait_ns);
             if (!__all_sync(0xFFFFFFFFu, w)) {
                 report_status(a.status, kStatusWaitIndexer, 2, tile0 + i);
                 ok = false;

@@ -513,10 +513,11 @@ int dsv4_hca_dense_decode_simt(const Dsv4HcaDenseDecodeParams* p, void* stream);
 void dsv4_debug_set_flags(int flags);
 
 /* Test aid for the error path of the bounded waits.  wait_ns: limit of every wait inside the decode
- * kernels (0 = the default, 2 s).  drop_tile >= 0: in every decode block the loaders withhold the
- * hand-over of the tile with that running number, so that the waits behind it run out; the kernel
- * must then return with `status` naming the wait (no trap, no fault) and the next launch must be
- * unaffected.  drop_tile = -1 switches it off.  The reference's counterpart is the trap after a
+ * kernels and the indexer's scoring kernel (0 = the default, 2 s).  drop_tile >= 0: in every decode
+ * block the loaders withhold the hand-over of the tile with that running number (in every block of the
+ * scoring kernel the MMA warp withholds the "accumulator full" signal of that tile), so that the waits
+ * behind it run out; the kernel must then return with `status` naming the wait (no trap, no fault) and
+ * the next launch must be unaffected.  drop_tile = -1 switches it off.  The reference's counterpart is the trap after a
  * cycle budget in hca/sm100/helpers.h:183-206. */
 void dsv4_debug_set_wait(unsigned long long wait_ns, int drop_tile);
 

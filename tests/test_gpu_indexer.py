@@ -135,3 +135,23 @@ def test_topk_with_many_equal_scores(lib):
         taken = idx[b, 0]
         assert (taken >= 0).all() and (taken < 6000).all() and len(np.unique(taken)) == 100
         assert np.ptp(scores[b, :6000]) <= 1e-5 * np.abs(scores[b, :6000]).max() + 1e-6
+
+
+def test_indexer_bounded_wait_runs_out_and_kernel_returns(lib):
+    """With the limit of the barrier waits set to 200 us and one "accumulator full" signal withheld in every
+    block of the scoring kernel, the launch returns (no trap, no fault, no hang) with the status naming the
+    wait, and the next launch is an ordinary one."""
+    c = orc.make_indexer_case(seed=171, B=2, s_q=1, n=1500, n_vis=None)
+    pages, bt, qw = indexer_inputs(c, np.random.default_rng(5))
+    status = lib.new_status("cuda")
+    lib.LIB.dsv4_debug_set_wait(200_000, 0)
+    try:
+        lib.indexer_topk(gu.dev(c.q_fp8), gu.dev(qw), gu.dev(pages), gu.dev(bt), gu.dev(c.n_vis), 256, status=status)
+        torch.cuda.synchronize()
+    finally:
+        lib.LIB.dsv4_debug_set_wait(0, -1)
+    code, block, role, tile = status.cpu().tolist()
+    assert code == 32, f"expected the indexer's wait code, got {status.cpu().tolist()}"
+    assert role in (0, 1, 2)
+    idx, scores = run(lib, c, pages, bt, qw, c.n_vis, 256)
+    check_selection(idx, scores, orc.indexer_scores(c.q_fp8, qw, pages, bt, c.n_vis), c.n_vis, 256)
