@@ -19,7 +19,7 @@ reference's own graph candidate is timed).  Step i works on instance i mod R of
 the workload - R independent copies with their own KV pools, queries and outputs,
 R chosen so that the copies together are several times larger than L2 - so every
 step finds its inputs in HBM, not in L2, without a flush inside the timed region.
-The same step timed alone (L2 flushed by a 512 MiB write before each launch, one
+The same step timed alone (L2 emptied by a 512 MiB write and a read of the same buffer before each launch, one
 event pair per launch, eager launch) is reported beside it as "isolated".
 `--impl reference` times the reference's own PyTorch decode path
 (bench/bench/reference.py, hca_decode_forward in fp32 mode on exactly dequantised,
@@ -246,6 +246,22 @@ def parity_sample(kind, w, out, lse, count=PARITY_ROWS):
     if not sc.within_tolerance(r, **TOL):
         raise RuntimeError(f"result out of tolerance against the oracle: {r}")
     return {k: r[k] for k in ("parity_checked_rows", "max_abs", "mean_abs", "lse_rel")}
+
+
+class L2Flush:
+    """Empties L2 before an isolated launch: a write of a buffer four times the size of L2, then a read of it.  The
+    write alone would leave L2 full of DIRTY lines, which the launch under test then has to write back while it
+    runs (up to 126 MB of extra DRAM writes: 6-10 us on the short streaming kernels, against their times under the
+    profiler); after the read what is left in L2 is clean."""
+
+    def __init__(self, device):
+        import torch
+        self.buf = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=device)
+        self.sink = torch.empty((), dtype=torch.int64, device=device)
+
+    def zero_(self):
+        self.buf.zero_()
+        self.sink.copy_(self.buf.sum())
 
 
 def time_steps(fn, steps, warmup, flush, barrier):
@@ -670,7 +686,7 @@ def run_single(args):
     import torch
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush = L2Flush(dev)
     name = args.single
     parity = None
     if name in AUX_CASES:
@@ -712,7 +728,7 @@ def run_ours(args):
         barrier = lambda: dist.barrier()
     else:
         barrier = lambda: None
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush = L2Flush(dev)
 
     l2_bytes = int(torch.cuda.get_device_properties(dev).L2_cache_size)
 
@@ -928,8 +944,8 @@ def run_ours(args):
                    "split_mode": head["splits"], "entry_bytes": ENTRY_BYTES,
                    "timing": f"{head['mode']} replay of the K steps" if head["mode"] == "graph" else "eager back-to-back launches",
                    "l2": f"inputs larger than L2: the steps rotate over {head['instances']} independent instances of the workload "
-                         f"({head['instances']} KV pools, queries and outputs; L2 = {l2_bytes >> 20} MiB); the isolated figure flushes L2 "
-                         f"with a {L2_FLUSH_BYTES >> 20} MiB write before each launch",
+                         f"({head['instances']} KV pools, queries and outputs; L2 = {l2_bytes >> 20} MiB); the isolated figure empties L2 "
+                         f"with a {L2_FLUSH_BYTES >> 20} MiB write followed by a read of the same buffer before each launch",
                    "kv_bytes_per_gpu_step": head["kv_bytes"], "parallelism": f"dp{world} over requests, no collective"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"],
                 "ms_per_step": e2e_ms, "host_link": link,
