@@ -93,7 +93,7 @@ struct HcaCompressArgs {
 constexpr int kHcaVecsPerBlock = 72;            // 72 x 8 = 576 channels
 constexpr int kHcaRowGroups = 4;
 constexpr int kHcaCompressThreads = kHcaVecsPerBlock * kHcaRowGroups;   // 288
-constexpr int kHcaBatch = 2;                    // rows per online-softmax step (two steps' rows are held: one being folded, one on its way)
+constexpr int kHcaBatch = 4;                    // rows per online-softmax step
 
 // One block per (request, output row, 576-channel slab).  Thread t owns the 8
 // channels of vector t % 72 and the rows of row group t / 72 (a quarter of the m
@@ -126,23 +126,18 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
     for (int k = 0; k < 8; ++k) { mx[k] = kLowest;  l[k] = 0.f;  acc[k] = 0.f; }
     if (active) {
         const int64_t base = int64_t(b) * a.stride_b + int64_t(blk) * a.m * a.stride_n + ch;
-        // One step = kHcaBatch rows, in two halves: `load` requests the rows, `fold` takes them into the online
-        // softmax state.  Two register sets alternate, so that the rows of the next step are on their way while
-        // the current ones are folded.  FULL: all rows of the step exist (no per-row predicates in the code).
-        struct Rows { uint4 z[kHcaBatch], c[kHcaBatch], u[kHcaBatch]; };
-        auto load = [&](int r, Rows& w, auto full_tag) {
+        // one step = kHcaBatch rows; FULL: all of them exist (no per-row predicates in the code)
+        auto step = [&](int r, auto full_tag) {
             constexpr bool FULL = decltype(full_tag)::value;
+            uint4 zv[kHcaBatch], cv[kHcaBatch], bv[kHcaBatch];
 #pragma unroll
             for (int j = 0; j < kHcaBatch; ++j) {
                 if (FULL || r + j < r1) {
-                    w.z[j] = ptx::ldg_nc_v4(a.Z + base + int64_t(r + j) * a.stride_n);
-                    w.c[j] = ptx::ldg_nc_v4(a.C + base + int64_t(r + j) * a.stride_n);
-                    w.u[j] = __ldg(reinterpret_cast<const uint4*>(a.bias + int64_t(r + j) * a.c + ch));
+                    zv[j] = ptx::ldg_nc_v4(a.Z + base + int64_t(r + j) * a.stride_n);
+                    cv[j] = ptx::ldg_nc_v4(a.C + base + int64_t(r + j) * a.stride_n);
+                    bv[j] = __ldg(reinterpret_cast<const uint4*>(a.bias + int64_t(r + j) * a.c + ch));
                 }
             }
-        };
-        auto fold = [&](int r, const Rows& w, auto full_tag) {
-            constexpr bool FULL = decltype(full_tag)::value;
             // The reference maximum of the step is found in packed BF16 arithmetic (one add and
             // one max per two elements): any value close to the true maximum serves, as long as
             // the same one is used for every weight of the step.  Only the raw vectors stay in
@@ -153,8 +148,8 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
 #pragma unroll
             for (int j = 0; j < kHcaBatch; ++j) {
                 if (FULL || r + j < r1) {
-                    const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&w.z[j]);
-                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&w.u[j]);
+                    const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&zv[j]);
+                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&bv[j]);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) pm[k] = __hmax2(pm[k], __hadd2(z2[k], u2[k]));
                 }
@@ -171,9 +166,9 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
             for (int j = 0; j < kHcaBatch; ++j) {
                 if (FULL || r + j < r1) {
                     float z[8], u[8], cf[8];
-                    unpack8(w.z[j], z);
-                    unpack8(w.u[j], u);
-                    unpack8(w.c[j], cf);
+                    unpack8(zv[j], z);
+                    unpack8(bv[j], u);
+                    unpack8(cv[j], cf);
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const float e = ptx::ex2(fmaf(z[k] + u[k], kLog2e, nref[k]));
@@ -183,23 +178,9 @@ __global__ void __launch_bounds__(kHcaCompressThreads, 2) hca_compress_kernel(co
                 }
             }
         };
-        const int n_full = (r1 - r0) / kHcaBatch;
-        const std::true_type full{};
-        Rows ra, rb;
-        if (n_full > 0) load(r0, ra, full);
-        int i = 0;
-        for (; i + 1 < n_full; i += 2) {
-            load(r0 + (i + 1) * kHcaBatch, rb, full);
-            fold(r0 + i * kHcaBatch, ra, full);
-            if (i + 2 < n_full) load(r0 + (i + 2) * kHcaBatch, ra, full);
-            fold(r0 + (i + 1) * kHcaBatch, rb, full);
-        }
-        if (i < n_full) fold(r0 + i * kHcaBatch, ra, full);
-        const int r_full = r0 + n_full * kHcaBatch;
-        if (r_full < r1) {
-            load(r_full, ra, std::false_type{});
-            fold(r_full, ra, std::false_type{});
-        }
+        const int r_full = r0 + ((r1 - r0) / kHcaBatch) * kHcaBatch;
+        for (int r = r0; r < r_full; r += kHcaBatch) step(r, std::true_type{});
+        if (r_full < r1) step(r_full, std::false_type{});
     }
     if (rg > 0) {
 #pragma unroll
