@@ -80,7 +80,9 @@ DEFAULT_WORKLOAD = "hca_b64_h128_ctx100k"
 # DRAM bytes (read + write) of ONE launch of the decode kernel on the workload, from an ncu
 # capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum); the summaries
 # under profiles/ hold the figures and the command lines.
-NCU_DRAM_TRAFFIC = {"hca_b64_h128_ctx100k": 47.79e6, "csa_b64_h128_topk512_ctx3072": 32.38e6}
+NCU_DRAM_TRAFFIC = {"hca_b64_h128_ctx100k": 47.79e6, "csa_b64_h128_topk512_ctx3072": 32.43e6,
+                    # captured on the B = 16 slice of the same shape (27.51 MB per launch) and scaled by the rows
+                    "csa_b64_h128_topk2048_ctx100k": 4 * 27.51e6}
 NCU_TRAFFIC_SOURCE = "ncu capture of one launch (profiles/decode_mma_kernel_*.md)"
 
 
