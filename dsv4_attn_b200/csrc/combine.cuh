@@ -1,7 +1,8 @@
 // LSE-weighted merge of split-KV partial outputs.  One warp per (row, head):
 // the per-split log2 LSEs are reduced with warp shuffles, each lane then owns
 // 2 x 8 consecutive value columns, reads partials with 128-bit loads (two splits
-// in flight per lane) and writes BF16 with 128-bit stores.
+// in flight per lane, issued without waiting for the weights) and writes BF16 with
+// 128-bit stores.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -75,13 +76,17 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
         po_stride = a.stride_po_split;
     }
 
-    // pass 1: maximum and sum over splits, 32 splits per step
-    float mx = -CUDART_INF_F;
-    for (int s = lane; s < S; s += 32) mx = fmaxf(mx, __ldg(pl + int64_t(s) * pl_stride));
+    // pass 1: maximum and sum over splits.  The first 32 LSEs are loaded once (one per lane) and serve the maximum,
+    // the sum and the weights; only rows with more than 32 splits go back to memory.
+    const float l_first = (lane < S) ? __ldg(pl + int64_t(lane) * pl_stride) : -CUDART_INF_F;
+    float mx = l_first;
+    for (int s = lane + 32; s < S; s += 32) mx = fmaxf(mx, __ldg(pl + int64_t(s) * pl_stride));
     mx = warp_max(mx);
     float sum = 0.f;
-    if (mx != -CUDART_INF_F)
-        for (int s = lane; s < S; s += 32) sum += exp2f(__ldg(pl + int64_t(s) * pl_stride) - mx);
+    if (mx != -CUDART_INF_F) {
+        sum = exp2f(l_first - mx);
+        for (int s = lane + 32; s < S; s += 32) sum += exp2f(__ldg(pl + int64_t(s) * pl_stride) - mx);
+    }
     sum = warp_sum(sum);
     const bool has = sum != 0.f;
     const float glse = has ? log2f(sum) + mx : -CUDART_INF_F;
@@ -103,7 +108,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
         // each lane computes the weight of one split of this group; broadcast by shuffle
         float w_mine = 0.f;
         if (s0 + lane < S) {
-            const float l = __ldg(pl + int64_t(s0 + lane) * pl_stride);
+            const float l = (s0 == 0) ? l_first : __ldg(pl + int64_t(s0 + lane) * pl_stride);
             w_mine = (l == -CUDART_INF_F || denom == -CUDART_INF_F) ? 0.f : exp2f(l - denom);
         }
         const int cnt = min(32, S - s0);
@@ -113,7 +118,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const float x = __shfl_sync(0xFFFFFFFFu, w_mine, (k0 + j) & 31);
-                w[j] = (k0 + j < cnt) ? x : 0.f;      // an empty split has weight 0: its partial may hold anything and is not read
+                w[j] = (k0 + j < cnt) ? x : 0.f;      // an empty split has weight 0: what its partial holds is loaded but not used
             }
             if (a.partial_bf16) {
                 const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(a.partial_o) + po_off + int64_t(s0 + k0) * po_stride;
@@ -122,12 +127,12 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
-                        v[j][i] = (w[j] != 0.f) ? __ldg(reinterpret_cast<const uint4*>(sb + int64_t(j) * po_stride + i * 256))
-                                                : make_uint4(0, 0, 0, 0);
+                        v[j][i] = __ldg(reinterpret_cast<const uint4*>(sb + int64_t(k0 + j < cnt ? j : 0) * po_stride + i * 256));
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
+                        if (w[j] == 0.f) v[j][i] = make_uint4(0, 0, 0, 0);      // whatever an empty split's slot holds is discarded
                         const uint32_t u[4] = {v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -142,15 +147,19 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
-                        const float4* q = reinterpret_cast<const float4*>(src + int64_t(j) * po_stride + i * 256);
-                        v[j][2 * i] = (w[j] != 0.f) ? __ldg(q) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        v[j][2 * i + 1] = (w[j] != 0.f) ? __ldg(q + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        // not predicated on the weight: the loads go out before the weights are known; what an
+                        // empty split's slot holds is discarded below
+                        const float4* q = reinterpret_cast<const float4*>(src + int64_t(k0 + j < cnt ? j : 0) * po_stride + i * 256);
+                        v[j][2 * i] = __ldg(q);
+                        v[j][2 * i + 1] = __ldg(q + 1);
                     }
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
-                        const float4 v0 = v[j][2 * i], v1 = v[j][2 * i + 1];
+                        const bool use = w[j] != 0.f;
+                        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                        const float4 v0 = use ? v[j][2 * i] : z, v1 = use ? v[j][2 * i + 1] : z;
                         acc[i][0] = fmaf(w[j], v0.x, acc[i][0]);  acc[i][1] = fmaf(w[j], v0.y, acc[i][1]);
                         acc[i][2] = fmaf(w[j], v0.z, acc[i][2]);  acc[i][3] = fmaf(w[j], v0.w, acc[i][3]);
                         acc[i][4] = fmaf(w[j], v1.x, acc[i][4]);  acc[i][5] = fmaf(w[j], v1.y, acc[i][5]);

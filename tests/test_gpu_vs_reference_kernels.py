@@ -1,8 +1,10 @@
 """Timing beside the reference project's own Blackwell-built kernels (the two
 that are safe to run: the split-KV merge and the CSA compressor reduce, built
 from the reference sources into oracle/_ref).  Same buffers, same L2 discipline
-(a 512 MiB write between launches), CUDA events.  Prints the numbers that
-profiles/ quotes and checks that this library is not slower."""
+(before every launch a 512 MiB write and then a read of the same buffer, so that
+L2 holds neither the inputs nor dirty lines to write back), CUDA events.  Prints
+the numbers that profiles/ quotes and checks that this library is not slower
+(the merge kernels both sit at the DRAM ceiling on FP32 partials: within 5 %)."""
 import ctypes as C
 from pathlib import Path
 
@@ -31,7 +33,15 @@ def env():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import dsv4_attn_b200 as lib
-    return lib, torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    class Flush:
+        def __init__(self):
+            self.buf = torch.empty(128 << 20, dtype=torch.int32, device="cuda")
+            self.sink = torch.empty((), dtype=torch.int64, device="cuda")
+
+        def zero_(self):
+            self.buf.zero_()
+            self.sink.copy_(self.buf.sum())
+    return lib, Flush()
 
 
 def test_merge_kernel_speed(env):
@@ -51,7 +61,7 @@ def test_merge_kernel_speed(env):
     gb = (po.numel() * 4 + pl.numel() * 4 + out.numel() * 2 + lse.numel() * 4) / 1e9
     print(f"\nmerge S={S} N={N} H={H}: ours {ours:.1f} us ({gb / ours * 1e6:.0f} GB/s), reference kernel {theirs:.1f} us "
           f"({gb / theirs * 1e6:.0f} GB/s)")
-    assert ours <= theirs * 1.10
+    assert ours <= theirs * 1.05
 
 
 def test_compress_reduce_kernel_speed(env):
