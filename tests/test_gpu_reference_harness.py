@@ -16,7 +16,6 @@ import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
 PYREF = ROOT / "oracle" / "_ref" / "pyref"
-OUT = ROOT / "gpurun_out"
 
 pytestmark = pytest.mark.gpu
 
@@ -54,8 +53,10 @@ def test_reference_harness_accepts_the_library(module, overrides):
     assert p.returncode == 0, p.stderr[-2000:]
     line = [x for x in p.stdout.splitlines() if x.startswith("RESULT ")][-1]
     res = json.loads(line[len("RESULT "):])
-    OUT.mkdir(exist_ok=True)
-    (OUT / f"reference_harness_{res['candidate']}.json").write_text(json.dumps(res, indent=1) + "\n")
+    keep = os.environ.get("DSV4_HARNESS_RESULTS")          # a folder to keep the harness's result records in
+    if keep:
+        Path(keep).mkdir(parents=True, exist_ok=True)
+        (Path(keep) / f"reference_harness_{res['candidate']}.json").write_text(json.dumps(res, indent=1) + "\n")
     print(res)
     assert res["correct"], res
     assert res["message"] == ""
