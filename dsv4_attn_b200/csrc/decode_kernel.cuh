@@ -435,12 +435,10 @@ __device__ __forceinline__ void loader_fetch(const DecodeArgs& a, const uint32_t
             for (int j = 0; j < 3; ++j) r.lat[g][j] = ptx::ldg_nc_v4(lp + j * 128 + piece * 16);
             // the last span holds only chunk 6 (bytes 384..447 of the 448-byte row)
             if (piece < 4) r.lat[g][3] = ptx::ldg_nc_v4(lp + 384 + piece * 16);
-            uint32_t s0 = 0, s1 = 0;
+            // this lane dequantises chunk 2 j + (lane / 4) % 2 of span j: only those scale bytes are fetched
+            const int flip = (lane >> 2) & 1;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) s0 |= uint32_t(__ldg(sp + j)) << (8 * j);
-#pragma unroll
-            for (int j = 0; j < 3; ++j) s1 |= uint32_t(__ldg(sp + 4 + j)) << (8 * j);
-            r.sc[g][0] = s0;  r.sc[g][1] = s1;
+            for (int j = 0; j < 4; ++j) r.sc[g][j] = (2 * j + flip < 7) ? uint32_t(__ldg(sp + 2 * j + flip)) : 0u;
             r.rope[g] = ptx::ldg_nc_v4(rp + piece * 16);
         }
     }
@@ -508,7 +506,8 @@ __device__ __forceinline__ void loader_store_span(const LoaderAddr& ad, int lane
             if (c >= uint32_t(NCHUNK - 1)) continue;               // reference layout: span 3 ends with chunk 6
             // one UE8M0 byte per 64 elements: 2^(byte-127) * 2^120; a zero byte means a zero
             // scale, as in the reference's dequantiser
-            const uint32_t byte = ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
+            const uint32_t byte = (SRC == kSrcRef) ? r.sc[g][j]
+                                                   : ((c < 4u ? r.sc[g][0] >> (8u * c) : r.sc[g][1] >> (8u * (c - 4u))) & 0xFFu);
             const float s120 = byte ? __uint_as_float((byte + 120u) << 23) : 0.f;
             const __nv_bfloat162 scale2 = __float2bfloat162_rn(s120);
             dequant4(x.x, scale2, w0.x, w0.y);
